@@ -1,0 +1,97 @@
+/* swiglu_b200 -- C ABI of the B200 (sm_100a) SwiGLU activation library.
+ *
+ * The reference (Forge-researchlab/kernel-POCs) has no native boundary for this path: its
+ * Python launch wrappers start Triton kernels directly.  Each entry point below replaces one
+ * such wrapper-to-kernel hand-off and is what a binding of the reference would call instead:
+ *
+ *   swiglu_b200_fwd   <- kernels/swiglu/swiglu.py:219-228 (_swiglu_forward_kernel launch in
+ *                        swiglu_forward) and :282-291 (_swiglu_packed_forward_kernel launch)
+ *   swiglu_b200_bwd   <- kernels/swiglu/swiglu.py:250-261 (_swiglu_backward_kernel launch in
+ *                        swiglu_backward) and :312-322 (_swiglu_packed_backward_kernel launch)
+ *
+ * All pointers are device pointers owned by the caller.  The library allocates nothing, keeps
+ * no per-call state, never synchronises the stream and never aborts: every failure is a
+ * non-zero return code.  Calls are asynchronous on `stream` and may be made concurrently
+ * from several host threads (for example one per device).
+ *
+ * Layouts.  A tensor is `rows` x `cols` elements with a row stride given in ELEMENTS.
+ *   separate gate/up  : in_row_stride == out_row_stride == cols
+ *   packed gate|up    : gate = base, up = base + cols, in_row_stride = 2*cols,
+ *                       out_row_stride = cols (and dup = dgate + cols in the backward)
+ * The widest access that the base addresses, strides and `cols` allow is chosen per call
+ * (16 bytes when everything is 16-byte compatible, down to one element).
+ *
+ * Aliasing.  In the backward, dgate may equal gate and dup may equal up exactly (same address,
+ * same stride): the in-place mode of the reference (swiglu.py:247-248, 310).  No other
+ * overlap between an output and any input is allowed.
+ */
+#ifndef SWIGLU_B200_H_
+#define SWIGLU_B200_H_
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define SWIGLU_B200_API __attribute__((visibility("default")))
+#else
+#define SWIGLU_B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element types (the three the reference accepts, swiglu.py:48-50). */
+#define SWIGLU_B200_F32 0
+#define SWIGLU_B200_F16 1
+#define SWIGLU_B200_BF16 2
+
+/* Return codes. */
+#define SWIGLU_B200_OK 0
+#define SWIGLU_B200_ERR_DTYPE 1       /* dtype is not one of the three codes above            */
+#define SWIGLU_B200_ERR_NULL 2        /* a required pointer is NULL while rows*cols > 0        */
+#define SWIGLU_B200_ERR_SHAPE 3       /* negative size, or a row stride smaller than cols      */
+#define SWIGLU_B200_ERR_ALIGN 4       /* a pointer is not aligned to its element size          */
+#define SWIGLU_B200_ERR_ALIAS 5       /* outputs overlap inputs in a way other than exact alias */
+#define SWIGLU_B200_ERR_DEVICE 6      /* cudaSetDevice / attribute query failed                */
+#define SWIGLU_B200_ERR_LAUNCH 7      /* the kernel launch was rejected by the runtime          */
+#define SWIGLU_B200_ERR_COPY 8        /* a host<->device copy of the host-buffer entry failed  */
+
+/* ABI version of this header: major*1000 + minor. */
+SWIGLU_B200_API int swiglu_b200_version(void);
+
+/* Static, human-readable text for a return code. */
+SWIGLU_B200_API const char* swiglu_b200_strerror(int code);
+
+/* The CUDA runtime error (cudaError_t as int) behind the calling thread's most recent
+ * ERR_DEVICE / ERR_LAUNCH / ERR_COPY, 0 if none. */
+SWIGLU_B200_API int swiglu_b200_last_cuda_error(void);
+
+/* Number of kernels this library has launched in this process (all threads, all devices).
+ * Monotonic; used by benchmarks to report how many launches a timed region contained. */
+SWIGLU_B200_API uint64_t swiglu_b200_launch_count(void);
+
+/* Forward: out[r][c] = silu(gate[r][c] * gm) * up[r][c] * dm, computed in fp32 and rounded
+ * once to `dtype`.
+ *   out            rows x cols, row stride out_row_stride
+ *   gate, up       rows x cols, row stride in_row_stride (both)
+ *   device         CUDA device ordinal owning the buffers, or -1 for the current device
+ *   stream         cudaStream_t (0 = legacy default stream)
+ * rows*cols == 0 succeeds without a launch. */
+SWIGLU_B200_API int swiglu_b200_fwd(void* out, const void* gate, const void* up, int64_t rows, int64_t cols, int64_t in_row_stride,
+                    int64_t out_row_stride, int dtype, float gm, float dm, int device, void* stream);
+
+/* Backward: with z = gate*gm, s = sigmoid(z), d = dout*dm
+ *   dup   = d * z * s
+ *   dgate = d * up * s * (1 + z*(1 - s)) * gm
+ *   dgate, dup     rows x cols, row stride grad_row_stride; may alias gate, up exactly
+ *   dout           rows x cols, row stride dout_row_stride
+ *   gate, up       rows x cols, row stride in_row_stride */
+SWIGLU_B200_API int swiglu_b200_bwd(void* dgate, void* dup, const void* dout, const void* gate, const void* up, int64_t rows,
+                    int64_t cols, int64_t in_row_stride, int64_t grad_row_stride, int64_t dout_row_stride, int dtype,
+                    float gm, float dm, int device, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* SWIGLU_B200_H_ */

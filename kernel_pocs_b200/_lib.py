@@ -1,0 +1,75 @@
+"""ctypes binding of libswiglu_b200.so (the C ABI declared in include/swiglu_b200.h).
+
+There is no fallback: if the shared library is missing or does not export a declared symbol,
+importing this module raises.  Build it with ``python -m kernel_pocs_b200.build``.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libswiglu_b200.so"
+
+F32, F16, BF16 = 0, 1, 2
+OK = 0
+
+_c_i64 = ctypes.c_int64
+_c_ptr = ctypes.c_void_p
+
+# name -> (restype, argtypes); one entry per declaration in include/swiglu_b200.h
+SIGNATURES = {
+    "swiglu_b200_version": (ctypes.c_int, []),
+    "swiglu_b200_strerror": (ctypes.c_char_p, [ctypes.c_int]),
+    "swiglu_b200_last_cuda_error": (ctypes.c_int, []),
+    "swiglu_b200_launch_count": (ctypes.c_uint64, []),
+    "swiglu_b200_fwd": (
+        ctypes.c_int,
+        [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_i64, ctypes.c_int, ctypes.c_float, ctypes.c_float,
+         ctypes.c_int, _c_ptr],
+    ),
+    "swiglu_b200_bwd": (
+        ctypes.c_int,
+        [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, ctypes.c_int,
+         ctypes.c_float, ctypes.c_float, ctypes.c_int, _c_ptr],
+    ),
+}
+
+
+def _load() -> ctypes.CDLL:
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: the SwiGLU CUDA library has not been built "
+            "(run `python -m kernel_pocs_b200.build`); there is no non-CUDA fallback"
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as exc:
+            raise ImportError(f"{LIB_PATH} does not export {name}; rebuild it") from exc
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
+lib = _load()
+
+
+class SwigluB200Error(RuntimeError):
+    """A non-zero return code from the C ABI."""
+
+    def __init__(self, where: str, code: int):
+        text = lib.swiglu_b200_strerror(code).decode()
+        cuda = lib.swiglu_b200_last_cuda_error()
+        super().__init__(f"{where}: swiglu_b200 error {code} ({text}); last CUDA error {cuda}")
+        self.code = code
+        self.cuda_error = cuda
+
+
+def check(where: str, code: int) -> None:
+    if code != OK:
+        raise SwigluB200Error(where, code)
+
+
+def launch_count() -> int:
+    return int(lib.swiglu_b200_launch_count())

@@ -1,0 +1,387 @@
+// C ABI of the SwiGLU library: argument checking, access-width selection and launch.
+// Declarations and the contract of every entry point are in include/swiglu_b200.h.
+#include "swiglu_b200.h"
+
+#include <atomic>
+
+#include "swiglu_kernels.cuh"
+
+namespace {
+
+using namespace swiglu_b200;
+
+// Launch shape of the streaming kernels; see the tuning notes beside each value.
+#ifndef SWIGLU_THREADS
+#define SWIGLU_THREADS 256
+#endif
+#ifndef SWIGLU_FWD_UNROLL
+#define SWIGLU_FWD_UNROLL 4
+#endif
+#ifndef SWIGLU_BWD_UNROLL
+#define SWIGLU_BWD_UNROLL 2
+#endif
+#ifndef SWIGLU_LD_RO
+#define SWIGLU_LD_RO LD_NC_NOALLOC  // inputs that this launch never writes
+#endif
+#ifndef SWIGLU_LD_ALIASED
+#define SWIGLU_LD_ALIASED LD_PLAIN  // gate/up when dgate/dup overwrite them
+#endif
+#ifndef SWIGLU_ST
+#define SWIGLU_ST ST_CS
+#endif
+#ifndef SWIGLU_WAVES
+#define SWIGLU_WAVES 1              // resident-CTA waves the grid is capped at
+#endif
+
+constexpr int kMaxDevices = 64;
+
+std::atomic<uint64_t> g_launches{0};
+thread_local int t_last_cuda_error = 0;
+
+int fail_cuda(int code, cudaError_t e) {
+  t_last_cuda_error = (int)e;
+  return code;
+}
+
+struct DeviceScope {
+  // Makes `device` current for the duration of a call (no-op for -1 or when it already is).
+  int prev = -1;
+  bool switched = false;
+  cudaError_t err = cudaSuccess;
+  explicit DeviceScope(int device) {
+    if (device < 0) return;
+    err = cudaGetDevice(&prev);
+    if (err != cudaSuccess) return;
+    if (prev != device) {
+      err = cudaSetDevice(device);
+      switched = (err == cudaSuccess);
+    }
+  }
+  ~DeviceScope() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
+
+int sm_count(cudaError_t* err) {
+  static std::atomic<int> cache[kMaxDevices];
+  int dev = 0;
+  *err = cudaGetDevice(&dev);
+  if (*err != cudaSuccess) return 0;
+  if (dev < kMaxDevices) {
+    int c = cache[dev].load(std::memory_order_relaxed);
+    if (c > 0) return c;
+  }
+  int n = 0;
+  *err = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  if (*err != cudaSuccess) return 0;
+  if (dev < kMaxDevices) cache[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
+
+// Resident CTAs per SM of one kernel instantiation, queried once per device.
+template <class K>
+int ctas_per_sm(K kernel, int threads, cudaError_t* err) {
+  static std::atomic<int> cache[kMaxDevices];
+  int dev = 0;
+  *err = cudaGetDevice(&dev);
+  if (*err != cudaSuccess) return 0;
+  if (dev < kMaxDevices) {
+    int c = cache[dev].load(std::memory_order_relaxed);
+    if (c > 0) return c;
+  }
+  int n = 0;
+  *err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0);
+  if (*err != cudaSuccess) return 0;
+  if (n < 1) n = 1;
+  if (dev < kMaxDevices) cache[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
+
+template <class K>
+int grid_for(K kernel, long long n_vec, int threads, int unroll, unsigned* grid, cudaError_t* err) {
+  const long long tile = (long long)threads * unroll;
+  long long tiles = (n_vec + tile - 1) / tile;
+  if (tiles < 1) tiles = 1;  // an edge-only launch still needs one CTA
+  const int sms = sm_count(err);
+  if (*err != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
+  const int occ = ctas_per_sm(kernel, threads, err);
+  if (*err != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
+  const long long cap = (long long)sms * occ * SWIGLU_WAVES;
+  *grid = (unsigned)(tiles < cap ? tiles : cap);
+  return SWIGLU_B200_OK;
+}
+
+inline int elem_size(int dtype) { return dtype == SWIGLU_B200_F32 ? 4 : 2; }
+
+// Largest power of two <= limit that divides v (v == 0 divides everything).
+inline int pow2_divisor(unsigned long long v, int limit) {
+  int b = limit;
+  while (b > 1 && (v % (unsigned long long)b) != 0) b >>= 1;
+  return b;
+}
+
+struct Plan {
+  bool rows;   // 2-D addressing
+  int bytes;   // access width of the body
+  Shape shape;
+  long long skip;  // bytes by which every base pointer is advanced (flat head)
+};
+
+// Chooses addressing and access width for tensors at addresses `addr[0..n_addr)`, where
+// pitch[k] (elements) are the row strides in play.
+Plan make_plan(const unsigned long long* addr, int n_addr, const long long* pitch, int n_pitch, long long rows,
+               long long cols, int es) {
+  constexpr int kWide = 16;
+  Plan p{};
+  bool flat = true;
+  if (rows != 1)
+    for (int k = 0; k < n_pitch; ++k) flat = flat && (pitch[k] == cols);
+  p.rows = !flat;
+  const long long n = rows * cols;
+  if (flat) {
+    bool congruent = true;
+    for (int k = 1; k < n_addr; ++k) congruent = congruent && ((addr[k] % kWide) == (addr[0] % kWide));
+    if (congruent) {
+      long long head = (long long)((kWide - addr[0] % kWide) % kWide) / es;
+      if (head > n) head = n;
+      const int epv = kWide / es;
+      p.bytes = kWide;
+      p.shape.n_vec = (n - head) / epv;
+      p.shape.head = (int)head;
+      p.shape.edge = (int)(n - p.shape.n_vec * epv);
+      p.skip = head * es;
+    } else {
+      int b = kWide;
+      for (int k = 0; k < n_addr; ++k) b = pow2_divisor(addr[k], b);
+      const int epv = b / es;
+      p.bytes = b;
+      p.shape.n_vec = n / epv;
+      p.shape.head = 0;
+      p.shape.edge = (int)(n - p.shape.n_vec * epv);
+      p.skip = 0;
+    }
+  } else {
+    int b = kWide;
+    for (int k = 0; k < n_addr; ++k) b = pow2_divisor(addr[k], b);
+    b = pow2_divisor((unsigned long long)cols * es, b);
+    for (int k = 0; k < n_pitch; ++k) b = pow2_divisor((unsigned long long)pitch[k] * es, b);
+    p.bytes = b;
+    p.shape.vecs_per_row = cols * es / b;
+    p.shape.n_vec = rows * p.shape.vecs_per_row;
+    p.skip = 0;
+  }
+  return p;
+}
+
+// ------------------------------------------------------------------ forward dispatch
+
+template <class T, int BYTES, bool ROWS>
+int launch_fwd(void* out, const void* gate, const void* up, const Shape& s, float gm, float dm, cudaStream_t st) {
+  constexpr bool FAST = (sizeof(T) == 2);
+  auto kernel = swiglu_fwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, SWIGLU_FWD_UNROLL, SWIGLU_LD_RO, SWIGLU_ST>;
+  unsigned grid = 1;
+  cudaError_t err = cudaSuccess;
+  int rc = grid_for(kernel, s.n_vec, SWIGLU_THREADS, SWIGLU_FWD_UNROLL, &grid, &err);
+  if (rc != SWIGLU_B200_OK) return fail_cuda(rc, err);
+  kernel<<<grid, SWIGLU_THREADS, 0, st>>>(out, gate, up, s, gm, dm);
+  err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda(SWIGLU_B200_ERR_LAUNCH, err);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return SWIGLU_B200_OK;
+}
+
+template <class T, bool ROWS>
+int fwd_by_width(int bytes, void* out, const void* gate, const void* up, const Shape& s, float gm, float dm,
+                 cudaStream_t st) {
+  switch (bytes) {
+    case 16: return launch_fwd<T, 16, ROWS>(out, gate, up, s, gm, dm, st);
+    case 8: return launch_fwd<T, 8, ROWS>(out, gate, up, s, gm, dm, st);
+    case 4: return launch_fwd<T, 4, ROWS>(out, gate, up, s, gm, dm, st);
+    case 2:
+      if constexpr (sizeof(T) == 2) return launch_fwd<T, 2, ROWS>(out, gate, up, s, gm, dm, st);
+  }
+  return SWIGLU_B200_ERR_ALIGN;
+}
+
+template <class T>
+int fwd_typed(const Plan& p, void* out, const void* gate, const void* up, float gm, float dm, cudaStream_t st) {
+  return p.rows ? fwd_by_width<T, true>(p.bytes, out, gate, up, p.shape, gm, dm, st)
+                : fwd_by_width<T, false>(p.bytes, out, gate, up, p.shape, gm, dm, st);
+}
+
+// ------------------------------------------------------------------ backward dispatch
+
+template <class T, int BYTES, bool ROWS, bool INPLACE>
+int launch_bwd(void* dgate, void* dup, const void* dout, const void* gate, const void* up, const Shape& s, float gm,
+               float dm, cudaStream_t st) {
+  constexpr bool FAST = (sizeof(T) == 2);
+  constexpr int LD_IO = INPLACE ? SWIGLU_LD_ALIASED : SWIGLU_LD_RO;
+  auto kernel =
+      swiglu_bwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, SWIGLU_BWD_UNROLL, SWIGLU_LD_RO, LD_IO, SWIGLU_ST>;
+  unsigned grid = 1;
+  cudaError_t err = cudaSuccess;
+  int rc = grid_for(kernel, s.n_vec, SWIGLU_THREADS, SWIGLU_BWD_UNROLL, &grid, &err);
+  if (rc != SWIGLU_B200_OK) return fail_cuda(rc, err);
+  kernel<<<grid, SWIGLU_THREADS, 0, st>>>(dgate, dup, dout, gate, up, s, gm, dm);
+  err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda(SWIGLU_B200_ERR_LAUNCH, err);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return SWIGLU_B200_OK;
+}
+
+template <class T, bool ROWS, bool INPLACE>
+int bwd_by_width(int bytes, void* dgate, void* dup, const void* dout, const void* gate, const void* up,
+                 const Shape& s, float gm, float dm, cudaStream_t st) {
+  switch (bytes) {
+    case 16: return launch_bwd<T, 16, ROWS, INPLACE>(dgate, dup, dout, gate, up, s, gm, dm, st);
+    case 8: return launch_bwd<T, 8, ROWS, INPLACE>(dgate, dup, dout, gate, up, s, gm, dm, st);
+    case 4: return launch_bwd<T, 4, ROWS, INPLACE>(dgate, dup, dout, gate, up, s, gm, dm, st);
+    case 2:
+      if constexpr (sizeof(T) == 2) return launch_bwd<T, 2, ROWS, INPLACE>(dgate, dup, dout, gate, up, s, gm, dm, st);
+  }
+  return SWIGLU_B200_ERR_ALIGN;
+}
+
+template <class T>
+int bwd_typed(const Plan& p, bool inplace, void* dgate, void* dup, const void* dout, const void* gate,
+              const void* up, float gm, float dm, cudaStream_t st) {
+  if (p.rows) {
+    return inplace ? bwd_by_width<T, true, true>(p.bytes, dgate, dup, dout, gate, up, p.shape, gm, dm, st)
+                   : bwd_by_width<T, true, false>(p.bytes, dgate, dup, dout, gate, up, p.shape, gm, dm, st);
+  }
+  return inplace ? bwd_by_width<T, false, true>(p.bytes, dgate, dup, dout, gate, up, p.shape, gm, dm, st)
+                 : bwd_by_width<T, false, false>(p.bytes, dgate, dup, dout, gate, up, p.shape, gm, dm, st);
+}
+
+inline unsigned long long addr_of(const void* p) { return (unsigned long long)(uintptr_t)p; }
+inline const void* advance(const void* p, long long bytes) { return static_cast<const char*>(p) + bytes; }
+inline void* advance(void* p, long long bytes) { return static_cast<char*>(p) + bytes; }
+
+// Byte extent [lo, hi) touched by a rows x cols tensor with the given row stride.
+struct Extent {
+  unsigned long long lo, hi;
+};
+inline Extent extent(const void* p, long long rows, long long cols, long long stride, int es) {
+  const unsigned long long lo = addr_of(p);
+  return Extent{lo, lo + (unsigned long long)(((rows - 1) * stride + cols) * es)};
+}
+inline bool overlaps(const Extent& a, const Extent& b) { return a.lo < b.hi && b.lo < a.hi; }
+
+}  // namespace
+
+extern "C" {
+
+int swiglu_b200_version(void) { return 1000; }
+
+const char* swiglu_b200_strerror(int code) {
+  switch (code) {
+    case SWIGLU_B200_OK: return "success";
+    case SWIGLU_B200_ERR_DTYPE: return "unsupported dtype code (expected 0=fp32, 1=fp16, 2=bf16)";
+    case SWIGLU_B200_ERR_NULL: return "null pointer for a non-empty tensor";
+    case SWIGLU_B200_ERR_SHAPE: return "negative size or row stride smaller than cols";
+    case SWIGLU_B200_ERR_ALIGN: return "pointer not aligned to the element size";
+    case SWIGLU_B200_ERR_ALIAS: return "output overlaps an input without aliasing it exactly";
+    case SWIGLU_B200_ERR_DEVICE: return "CUDA device selection or attribute query failed";
+    case SWIGLU_B200_ERR_LAUNCH: return "CUDA kernel launch failed";
+    case SWIGLU_B200_ERR_COPY: return "CUDA host<->device copy failed";
+    default: return "unknown swiglu_b200 error code";
+  }
+}
+
+int swiglu_b200_last_cuda_error(void) { return t_last_cuda_error; }
+
+uint64_t swiglu_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int swiglu_b200_fwd(void* out, const void* gate, const void* up, int64_t rows, int64_t cols, int64_t in_row_stride,
+                    int64_t out_row_stride, int dtype, float gm, float dm, int device, void* stream) {
+  if (dtype != SWIGLU_B200_F32 && dtype != SWIGLU_B200_F16 && dtype != SWIGLU_B200_BF16) return SWIGLU_B200_ERR_DTYPE;
+  if (rows < 0 || cols < 0) return SWIGLU_B200_ERR_SHAPE;
+  if (rows == 0 || cols == 0) return SWIGLU_B200_OK;
+  if (in_row_stride < cols || out_row_stride < cols) return SWIGLU_B200_ERR_SHAPE;
+  if (!out || !gate || !up) return SWIGLU_B200_ERR_NULL;
+  const int es = elem_size(dtype);
+  if (addr_of(out) % es || addr_of(gate) % es || addr_of(up) % es) return SWIGLU_B200_ERR_ALIGN;
+  {
+    const Extent eo = extent(out, rows, cols, out_row_stride, es);
+    if (overlaps(eo, extent(gate, rows, cols, in_row_stride, es)) ||
+        overlaps(eo, extent(up, rows, cols, in_row_stride, es)))
+      return SWIGLU_B200_ERR_ALIAS;
+  }
+
+  DeviceScope scope(device);
+  if (scope.err != cudaSuccess) return fail_cuda(SWIGLU_B200_ERR_DEVICE, scope.err);
+
+  const unsigned long long addr[3] = {addr_of(out), addr_of(gate), addr_of(up)};
+  const long long pitch[2] = {in_row_stride, out_row_stride};
+  Plan p = make_plan(addr, 3, pitch, 2, rows, cols, es);
+  p.shape.pitch_in = in_row_stride * es;
+  p.shape.pitch_out = out_row_stride * es;
+  p.shape.pitch_grad = 0;
+  out = advance(out, p.skip);
+  gate = advance(gate, p.skip);
+  up = advance(up, p.skip);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case SWIGLU_B200_F32: return fwd_typed<float>(p, out, gate, up, gm, dm, st);
+    case SWIGLU_B200_F16: return fwd_typed<__half>(p, out, gate, up, gm, dm, st);
+    default: return fwd_typed<__nv_bfloat16>(p, out, gate, up, gm, dm, st);
+  }
+}
+
+int swiglu_b200_bwd(void* dgate, void* dup, const void* dout, const void* gate, const void* up, int64_t rows,
+                    int64_t cols, int64_t in_row_stride, int64_t grad_row_stride, int64_t dout_row_stride, int dtype,
+                    float gm, float dm, int device, void* stream) {
+  if (dtype != SWIGLU_B200_F32 && dtype != SWIGLU_B200_F16 && dtype != SWIGLU_B200_BF16) return SWIGLU_B200_ERR_DTYPE;
+  if (rows < 0 || cols < 0) return SWIGLU_B200_ERR_SHAPE;
+  if (rows == 0 || cols == 0) return SWIGLU_B200_OK;
+  if (in_row_stride < cols || grad_row_stride < cols || dout_row_stride < cols) return SWIGLU_B200_ERR_SHAPE;
+  if (!dgate || !dup || !dout || !gate || !up) return SWIGLU_B200_ERR_NULL;
+  const int es = elem_size(dtype);
+  if (addr_of(dgate) % es || addr_of(dup) % es || addr_of(dout) % es || addr_of(gate) % es || addr_of(up) % es)
+    return SWIGLU_B200_ERR_ALIGN;
+
+  // Either both gradients overwrite their inputs exactly, or no output touches any input.
+  const bool same_g = (dgate == gate), same_u = (dup == up);
+  bool inplace = false;
+  if (same_g || same_u) {
+    if (!(same_g && same_u) || grad_row_stride != in_row_stride) return SWIGLU_B200_ERR_ALIAS;
+    inplace = true;
+  }
+  {
+    const Extent edg = extent(dgate, rows, cols, grad_row_stride, es);
+    const Extent edu = extent(dup, rows, cols, grad_row_stride, es);
+    const Extent ed = extent(dout, rows, cols, dout_row_stride, es);
+    if (overlaps(edg, ed) || overlaps(edu, ed)) return SWIGLU_B200_ERR_ALIAS;
+    if (!inplace) {
+      const Extent eg = extent(gate, rows, cols, in_row_stride, es);
+      const Extent eu = extent(up, rows, cols, in_row_stride, es);
+      // Interleaved rows of a packed buffer make the bounding extents of dgate and dup
+      // overlap each other legitimately; only input/output overlap is an error.
+      if (overlaps(edg, eg) || overlaps(edg, eu) || overlaps(edu, eg) || overlaps(edu, eu))
+        return SWIGLU_B200_ERR_ALIAS;
+    }
+  }
+
+  DeviceScope scope(device);
+  if (scope.err != cudaSuccess) return fail_cuda(SWIGLU_B200_ERR_DEVICE, scope.err);
+
+  const unsigned long long addr[5] = {addr_of(dgate), addr_of(dup), addr_of(dout), addr_of(gate), addr_of(up)};
+  const long long pitch[3] = {in_row_stride, grad_row_stride, dout_row_stride};
+  Plan p = make_plan(addr, 5, pitch, 3, rows, cols, es);
+  p.shape.pitch_in = in_row_stride * es;
+  p.shape.pitch_out = dout_row_stride * es;
+  p.shape.pitch_grad = grad_row_stride * es;
+  dgate = advance(dgate, p.skip);
+  dup = advance(dup, p.skip);
+  dout = advance(dout, p.skip);
+  gate = advance(gate, p.skip);
+  up = advance(up, p.skip);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case SWIGLU_B200_F32: return bwd_typed<float>(p, inplace, dgate, dup, dout, gate, up, gm, dm, st);
+    case SWIGLU_B200_F16: return bwd_typed<__half>(p, inplace, dgate, dup, dout, gate, up, gm, dm, st);
+    default: return bwd_typed<__nv_bfloat16>(p, inplace, dgate, dup, dout, gate, up, gm, dm, st);
+  }
+}
+
+}  // extern "C"

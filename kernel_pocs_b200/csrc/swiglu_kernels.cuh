@@ -1,0 +1,479 @@
+// SwiGLU activation kernels for sm_100a (B200).
+//
+// Replaces the four Triton kernels of the reference
+// (kernels/swiglu/swiglu.py:60-176: _swiglu_forward_kernel, _swiglu_backward_kernel and
+// their packed twins).  The reference gives one program per token row and pads the row
+// to the next power of two; here the problem is a flat stream of 16- or 32-byte vectors
+// walked grid-stride by a fixed-size grid, so no lane is masked except in the last tile
+// and the row width is unlimited (64-bit indexing).
+//
+// Numerics (I/O dtype T, all arithmetic in fp32 registers):
+//   z = f32(gate) * gm          sigma = 1 / (1 + exp(-z))        silu = z * sigma
+//   forward   h     = R( silu * f32(up) * dm )
+//   backward  d     = f32(dh) * dm
+//             dup   = R( d * silu )
+//             dgate = R( d * f32(up) * sigma * (1 + z * (1 - sigma)) * gm )
+// R rounds once, to nearest even, into T.  For fp32 I/O the operation order follows the
+// ATen composite the reference tests compare with (swiglu.py:179-188 and the autograd
+// graph it builds), exp and the division are the accurate ones; for bf16/fp16 I/O the
+// exponential is ex2.approx and the reciprocal rcp.approx, whose error (~1e-6 relative)
+// is far below half an ulp of a 16-bit result.
+//
+// Memory: every kernel is a pure stream.  Algorithmic traffic per element of size s is
+// 3*s bytes forward (read gate, up; write h) and 5*s backward (read dh, gate, up; write
+// dgate, dup).  Nothing is re-read, so loads bypass L1 allocation and stores are
+// streaming.  dgate/dup may alias gate/up exactly (the reference's default in-place
+// backward, swiglu.py:247-248, 310): each thread loads all of a tile's vectors before
+// it stores any, and aliased inputs are never read through the non-coherent path.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace swiglu_b200 {
+
+// ---------------------------------------------------------------------------------------
+// Vector register blocks and global-memory access with explicit cache behaviour.
+// ---------------------------------------------------------------------------------------
+
+enum LdMode : int {
+  LD_PLAIN = 0,      // ld.global                        (coherent; safe when outputs alias inputs)
+  LD_NC_NOALLOC = 1, // ld.global.nc.L1::no_allocate     (read-only data, never written by this launch)
+  LD_CS = 2,         // ld.global.cs                     (coherent, evict-first)
+  LD_NC_EF = 3,      // 32-byte only: .nc + L1::no_allocate + L2::evict_first
+};
+enum StMode : int {
+  ST_PLAIN = 0,      // st.global
+  ST_CS = 1,         // st.global.cs                     (streaming)
+  ST_NOALLOC = 2,    // st.global.L1::no_allocate
+  ST_EF = 3,         // 32-byte only: L1::no_allocate + L2::evict_first
+};
+
+template <int BYTES> struct Vec;  // BYTES of payload held in 32-bit registers (16-bit for BYTES == 2)
+template <> struct Vec<32> { uint32_t w[8]; };
+template <> struct Vec<16> { uint32_t w[4]; };
+template <> struct Vec<8>  { uint32_t w[2]; };
+template <> struct Vec<4>  { uint32_t w[1]; };
+template <> struct Vec<2>  { uint32_t w[1]; };  // low 16 bits used
+
+template <int BYTES, int MODE> struct Ld;
+template <int BYTES, int MODE> struct St;
+
+#define SWIGLU_LD32(MODE, QUAL)                                                                   \
+  template <> struct Ld<32, MODE> {                                                               \
+    static __device__ __forceinline__ Vec<32> ld(const void* p) {                                 \
+      Vec<32> v;                                                                                  \
+      asm volatile("ld.global" QUAL ".v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"                    \
+                   : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]),        \
+                     "=r"(v.w[5]), "=r"(v.w[6]), "=r"(v.w[7])                                     \
+                   : "l"(p) : "memory");                                                          \
+      return v;                                                                                   \
+    }                                                                                             \
+  };
+#define SWIGLU_LD16(MODE, QUAL)                                                                   \
+  template <> struct Ld<16, MODE> {                                                               \
+    static __device__ __forceinline__ Vec<16> ld(const void* p) {                                 \
+      Vec<16> v;                                                                                  \
+      asm volatile("ld.global" QUAL ".v4.u32 {%0,%1,%2,%3}, [%4];"                                \
+                   : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3])                       \
+                   : "l"(p) : "memory");                                                          \
+      return v;                                                                                   \
+    }                                                                                             \
+  };
+#define SWIGLU_LD8(MODE, QUAL)                                                                    \
+  template <> struct Ld<8, MODE> {                                                                \
+    static __device__ __forceinline__ Vec<8> ld(const void* p) {                                  \
+      Vec<8> v;                                                                                   \
+      asm volatile("ld.global" QUAL ".v2.u32 {%0,%1}, [%2];"                                      \
+                   : "=r"(v.w[0]), "=r"(v.w[1]) : "l"(p) : "memory");                             \
+      return v;                                                                                   \
+    }                                                                                             \
+  };
+#define SWIGLU_LD4(MODE, QUAL)                                                                    \
+  template <> struct Ld<4, MODE> {                                                                \
+    static __device__ __forceinline__ Vec<4> ld(const void* p) {                                  \
+      Vec<4> v;                                                                                   \
+      asm volatile("ld.global" QUAL ".u32 %0, [%1];" : "=r"(v.w[0]) : "l"(p) : "memory");         \
+      return v;                                                                                   \
+    }                                                                                             \
+  };
+#define SWIGLU_LD2(MODE, QUAL)                                                                    \
+  template <> struct Ld<2, MODE> {                                                                \
+    static __device__ __forceinline__ Vec<2> ld(const void* p) {                                  \
+      uint16_t h;                                                                                 \
+      asm volatile("ld.global" QUAL ".u16 %0, [%1];" : "=h"(h) : "l"(p) : "memory");              \
+      Vec<2> v;                                                                                   \
+      v.w[0] = h;                                                                                 \
+      return v;                                                                                   \
+    }                                                                                             \
+  };
+#define SWIGLU_LD_ALL(MODE, QUAL) \
+  SWIGLU_LD32(MODE, QUAL) SWIGLU_LD16(MODE, QUAL) SWIGLU_LD8(MODE, QUAL) SWIGLU_LD4(MODE, QUAL) SWIGLU_LD2(MODE, QUAL)
+
+SWIGLU_LD_ALL(LD_PLAIN, "")
+SWIGLU_LD_ALL(LD_NC_NOALLOC, ".nc.L1::no_allocate")
+SWIGLU_LD_ALL(LD_CS, ".cs")
+SWIGLU_LD32(LD_NC_EF, ".nc.L1::no_allocate.L2::evict_first")
+// The L2 eviction qualifier exists for 32-byte accesses only; narrower widths keep the L1 hint.
+SWIGLU_LD16(LD_NC_EF, ".nc.L1::no_allocate")
+SWIGLU_LD8(LD_NC_EF, ".nc.L1::no_allocate")
+SWIGLU_LD4(LD_NC_EF, ".nc.L1::no_allocate")
+SWIGLU_LD2(LD_NC_EF, ".nc.L1::no_allocate")
+
+#define SWIGLU_ST32(MODE, QUAL)                                                                   \
+  template <> struct St<32, MODE> {                                                               \
+    static __device__ __forceinline__ void st(void* p, const Vec<32>& v) {                        \
+      asm volatile("st.global" QUAL ".v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"                    \
+                   :: "l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]), "r"(v.w[4]),    \
+                      "r"(v.w[5]), "r"(v.w[6]), "r"(v.w[7]) : "memory");                          \
+    }                                                                                             \
+  };
+#define SWIGLU_ST16(MODE, QUAL)                                                                   \
+  template <> struct St<16, MODE> {                                                               \
+    static __device__ __forceinline__ void st(void* p, const Vec<16>& v) {                        \
+      asm volatile("st.global" QUAL ".v4.u32 [%0], {%1,%2,%3,%4};"                                \
+                   :: "l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]) : "memory");     \
+    }                                                                                             \
+  };
+#define SWIGLU_ST8(MODE, QUAL)                                                                    \
+  template <> struct St<8, MODE> {                                                                \
+    static __device__ __forceinline__ void st(void* p, const Vec<8>& v) {                         \
+      asm volatile("st.global" QUAL ".v2.u32 [%0], {%1,%2};"                                      \
+                   :: "l"(p), "r"(v.w[0]), "r"(v.w[1]) : "memory");                               \
+    }                                                                                             \
+  };
+#define SWIGLU_ST4(MODE, QUAL)                                                                    \
+  template <> struct St<4, MODE> {                                                                \
+    static __device__ __forceinline__ void st(void* p, const Vec<4>& v) {                         \
+      asm volatile("st.global" QUAL ".u32 [%0], %1;" :: "l"(p), "r"(v.w[0]) : "memory");          \
+    }                                                                                             \
+  };
+#define SWIGLU_ST2(MODE, QUAL)                                                                    \
+  template <> struct St<2, MODE> {                                                                \
+    static __device__ __forceinline__ void st(void* p, const Vec<2>& v) {                         \
+      asm volatile("st.global" QUAL ".u16 [%0], %1;" :: "l"(p), "h"((uint16_t)v.w[0]) : "memory"); \
+    }                                                                                             \
+  };
+#define SWIGLU_ST_ALL(MODE, QUAL) \
+  SWIGLU_ST32(MODE, QUAL) SWIGLU_ST16(MODE, QUAL) SWIGLU_ST8(MODE, QUAL) SWIGLU_ST4(MODE, QUAL) SWIGLU_ST2(MODE, QUAL)
+
+SWIGLU_ST_ALL(ST_PLAIN, "")
+SWIGLU_ST_ALL(ST_CS, ".cs")
+SWIGLU_ST_ALL(ST_NOALLOC, ".L1::no_allocate")
+SWIGLU_ST32(ST_EF, ".L1::no_allocate.L2::evict_first")
+SWIGLU_ST16(ST_EF, ".L1::no_allocate")
+SWIGLU_ST8(ST_EF, ".L1::no_allocate")
+SWIGLU_ST4(ST_EF, ".L1::no_allocate")
+SWIGLU_ST2(ST_EF, ".L1::no_allocate")
+
+// ---------------------------------------------------------------------------------------
+// Element codecs: BYTES of packed T <-> fp32 registers.
+// ---------------------------------------------------------------------------------------
+
+template <class T> struct Codec;
+
+template <> struct Codec<float> {
+  static constexpr int kSize = 4;
+  template <int BYTES> static __device__ __forceinline__ void unpack(const Vec<BYTES>& v, float* f) {
+#pragma unroll
+    for (int i = 0; i < BYTES / 4; ++i) f[i] = __uint_as_float(v.w[i]);
+  }
+  template <int BYTES> static __device__ __forceinline__ void pack(const float* f, Vec<BYTES>& v) {
+#pragma unroll
+    for (int i = 0; i < BYTES / 4; ++i) v.w[i] = __float_as_uint(f[i]);
+  }
+};
+
+template <> struct Codec<__nv_bfloat16> {
+  static constexpr int kSize = 2;
+  template <int BYTES> static __device__ __forceinline__ void unpack(const Vec<BYTES>& v, float* f) {
+    if constexpr (BYTES == 2) {
+      f[0] = __uint_as_float(v.w[0] << 16);
+    } else {
+#pragma unroll
+      for (int i = 0; i < BYTES / 4; ++i) {
+        f[2 * i] = __uint_as_float(v.w[i] << 16);             // bf16 -> fp32 is exact: append 16 zero bits
+        f[2 * i + 1] = __uint_as_float(v.w[i] & 0xffff0000u);
+      }
+    }
+  }
+  template <int BYTES> static __device__ __forceinline__ void pack(const float* f, Vec<BYTES>& v) {
+    if constexpr (BYTES == 2) {
+      v.w[0] = __bfloat16_as_ushort(__float2bfloat16_rn(f[0]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < BYTES / 4; ++i) {
+        __nv_bfloat162 b = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);  // one cvt.rn.bf16x2.f32
+        v.w[i] = *reinterpret_cast<uint32_t*>(&b);
+      }
+    }
+  }
+};
+
+template <> struct Codec<__half> {
+  static constexpr int kSize = 2;
+  template <int BYTES> static __device__ __forceinline__ void unpack(const Vec<BYTES>& v, float* f) {
+    if constexpr (BYTES == 2) {
+      f[0] = __half2float(__ushort_as_half((unsigned short)v.w[0]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < BYTES / 4; ++i) {
+        uint32_t w = v.w[i];
+        float2 p = __half22float2(*reinterpret_cast<__half2*>(&w));
+        f[2 * i] = p.x;
+        f[2 * i + 1] = p.y;
+      }
+    }
+  }
+  template <int BYTES> static __device__ __forceinline__ void pack(const float* f, Vec<BYTES>& v) {
+    if constexpr (BYTES == 2) {
+      v.w[0] = __half_as_ushort(__float2half_rn(f[0]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < BYTES / 4; ++i) {
+        __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+        v.w[i] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+  }
+};
+
+// ---------------------------------------------------------------------------------------
+// The arithmetic.  FAST selects the approximate transcendental pair used for 16-bit I/O.
+// ---------------------------------------------------------------------------------------
+
+template <bool FAST> struct Math;
+
+template <> struct Math<true> {
+  static __device__ __forceinline__ float fwd(float g, float u, float gm, float dm) {
+    float z = g * gm;
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return (z * r) * u * dm;
+  }
+  static __device__ __forceinline__ void bwd(float dh, float g, float u, float gm, float dm, float& dgate,
+                                             float& dup) {
+    float z = g * gm;
+    float e, sig;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(sig) : "f"(1.0f + e));
+    float d = dh * dm;
+    float silu = z * sig;
+    dup = d * silu;
+    dgate = (d * u) * (sig * (1.0f + z * (1.0f - sig))) * gm;
+  }
+};
+
+template <> struct Math<false> {
+  // Same expression tree as ATen's silu / silu_backward, which is what the reference's
+  // torch_swiglu_reference (swiglu.py:179-188) evaluates under autograd.
+  static __device__ __forceinline__ float fwd(float g, float u, float gm, float dm) {
+    float z = g * gm;
+    float silu = z / (1.0f + expf(-z));
+    return (silu * u) * dm;
+  }
+  static __device__ __forceinline__ void bwd(float dh, float g, float u, float gm, float dm, float& dgate,
+                                             float& dup) {
+    float z = g * gm;
+    float den = 1.0f + expf(-z);
+    float sig = 1.0f / den;
+    float silu = z / den;
+    float d = dh * dm;
+    dup = d * silu;
+    dgate = (((d * u) * sig) * (1.0f + z * (1.0f - sig))) * gm;
+  }
+};
+
+// ---------------------------------------------------------------------------------------
+// Work description shared by the forward and backward kernels.
+//
+// The body is `n_vec` vectors of BYTES bytes.  FLAT: vector i of every tensor sits at
+// byte offset i*BYTES from that tensor's base.  ROWS: vector i belongs to row
+// i / vecs_per_row, column-vector i % vecs_per_row; each tensor has its own row pitch in
+// bytes (packed gate|up input of width 2I against an output of width I).
+//
+// FLAT launches also own up to `edge` scalar elements that did not fit the vector body:
+// `head` elements in front of it (peeled so the body starts 16-byte aligned) and the rest
+// behind it.
+// ---------------------------------------------------------------------------------------
+
+struct Shape {
+  long long n_vec;         // vectors in the body
+  long long vecs_per_row;  // ROWS only
+  long long pitch_in;      // bytes between rows of gate / up                (ROWS only)
+  long long pitch_out;     // bytes between rows of h (fwd) or dh (bwd)      (ROWS only)
+  long long pitch_grad;    // bytes between rows of dgate / dup              (ROWS, bwd only)
+  int head;                // scalar elements before the body                (FLAT only)
+  int edge;                // head + tail scalar elements                    (FLAT only)
+};
+
+template <bool ROWS, int BYTES>
+struct Locator {
+  // Byte offsets of vector `i` in the three pitch classes.
+  static __device__ __forceinline__ void at(const Shape& s, long long i, long long& off_in, long long& off_out,
+                                            long long& off_grad) {
+    if constexpr (!ROWS) {
+      off_in = off_out = off_grad = i * BYTES;
+    } else {
+      long long row, cv;
+      if (s.n_vec <= 0xffffffffLL) {  // uniform branch; 32-bit division is several times cheaper
+        unsigned r = (unsigned)i / (unsigned)s.vecs_per_row;
+        row = r;
+        cv = (long long)((unsigned)i - r * (unsigned)s.vecs_per_row);
+      } else {
+        row = i / s.vecs_per_row;
+        cv = i - row * s.vecs_per_row;
+      }
+      off_in = row * s.pitch_in + cv * BYTES;
+      off_out = row * s.pitch_out + cv * BYTES;
+      off_grad = row * s.pitch_grad + cv * BYTES;
+    }
+  }
+};
+
+static __device__ __forceinline__ const char* cbyte(const void* p) { return static_cast<const char*>(p); }
+static __device__ __forceinline__ char* byte(void* p) { return static_cast<char*>(p); }
+
+// ---------------------------------------------------------------------------------------
+// Forward.  One tile = THREADS*UNROLL vectors; thread t owns vectors t, t+THREADS, ... of
+// the tile, so each warp-wide access is one contiguous 512- or 1024-byte segment.
+// ---------------------------------------------------------------------------------------
+
+template <class T, int BYTES, bool FAST, bool ROWS, int THREADS, int UNROLL, int LDM, int STM>
+__global__ void __launch_bounds__(THREADS)
+swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const void* __restrict__ up, Shape s,
+                  float gm, float dm) {
+  constexpr int EPV = BYTES / Codec<T>::kSize;
+  constexpr long long TILE = (long long)THREADS * UNROLL;
+  const long long n_tiles = (s.n_vec + TILE - 1) / TILE;
+
+  for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const long long v0 = tile * TILE + threadIdx.x;
+    const bool full = (tile + 1) * TILE <= s.n_vec;
+    Vec<BYTES> g[UNROLL], u[UNROLL];
+    long long oo[UNROLL];
+#pragma unroll
+    for (int k = 0; k < UNROLL; ++k) {
+      const long long i = v0 + (long long)k * THREADS;
+      if (full || i < s.n_vec) {
+        long long oi, og;
+        Locator<ROWS, BYTES>::at(s, i, oi, oo[k], og);
+        g[k] = Ld<BYTES, LDM>::ld(cbyte(gate) + oi);
+        u[k] = Ld<BYTES, LDM>::ld(cbyte(up) + oi);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < UNROLL; ++k) {
+      const long long i = v0 + (long long)k * THREADS;
+      if (full || i < s.n_vec) {
+        float fg[EPV], fu[EPV], fh[EPV];
+        Codec<T>::template unpack<BYTES>(g[k], fg);
+        Codec<T>::template unpack<BYTES>(u[k], fu);
+#pragma unroll
+        for (int e = 0; e < EPV; ++e) fh[e] = Math<FAST>::fwd(fg[e], fu[e], gm, dm);
+        Vec<BYTES> h;
+        Codec<T>::template pack<BYTES>(fh, h);
+        St<BYTES, STM>::st(byte(out) + oo[k], h);
+      }
+    }
+  }
+
+  if constexpr (!ROWS) {
+    // Ragged edges of a flat stream: at most 2*(16/sizeof(T) - 1) scalar elements.
+    if (blockIdx.x == gridDim.x - 1 && (int)threadIdx.x < s.edge) {
+      constexpr int ES = Codec<T>::kSize;
+      const int t = threadIdx.x;
+      const long long idx = t < s.head ? (long long)t : (long long)t + s.n_vec * EPV;
+      // Element idx of the launch's logical stream; the body pointers were advanced past
+      // the head by the host, so address relative to them is (idx - head).
+      const long long off = (idx - s.head) * ES;
+      Vec<ES> vg = Ld<ES, LD_PLAIN>::ld(cbyte(gate) + off);
+      Vec<ES> vu = Ld<ES, LD_PLAIN>::ld(cbyte(up) + off);
+      float fg[1], fu[1], fh[1];
+      Codec<T>::template unpack<ES>(vg, fg);
+      Codec<T>::template unpack<ES>(vu, fu);
+      fh[0] = Math<FAST>::fwd(fg[0], fu[0], gm, dm);
+      Vec<ES> vh;
+      Codec<T>::template pack<ES>(fh, vh);
+      St<ES, ST_PLAIN>::st(byte(out) + off, vh);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Backward.  LDM_IO is the load mode of gate/up: it must be a coherent mode whenever
+// dgate/dup alias them.  dh is always read-only.
+// ---------------------------------------------------------------------------------------
+
+template <class T, int BYTES, bool FAST, bool ROWS, int THREADS, int UNROLL, int LDM_DH, int LDM_IO, int STM>
+__global__ void __launch_bounds__(THREADS)
+swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const void* gate, const void* up, Shape s,
+                  float gm, float dm) {
+  constexpr int EPV = BYTES / Codec<T>::kSize;
+  constexpr long long TILE = (long long)THREADS * UNROLL;
+  const long long n_tiles = (s.n_vec + TILE - 1) / TILE;
+
+  for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const long long v0 = tile * TILE + threadIdx.x;
+    const bool full = (tile + 1) * TILE <= s.n_vec;
+    Vec<BYTES> d[UNROLL], g[UNROLL], u[UNROLL];
+    long long og[UNROLL];
+#pragma unroll
+    for (int k = 0; k < UNROLL; ++k) {
+      const long long i = v0 + (long long)k * THREADS;
+      if (full || i < s.n_vec) {
+        long long oi, oo;
+        Locator<ROWS, BYTES>::at(s, i, oi, oo, og[k]);
+        d[k] = Ld<BYTES, LDM_DH>::ld(cbyte(dout) + oo);
+        g[k] = Ld<BYTES, LDM_IO>::ld(cbyte(gate) + oi);
+        u[k] = Ld<BYTES, LDM_IO>::ld(cbyte(up) + oi);
+      }
+    }
+    // All loads of the tile are issued (volatile asm keeps program order) before the first
+    // store below, so an in-place launch never reads a vector it has already overwritten.
+#pragma unroll
+    for (int k = 0; k < UNROLL; ++k) {
+      const long long i = v0 + (long long)k * THREADS;
+      if (full || i < s.n_vec) {
+        float fd[EPV], fg[EPV], fu[EPV], fdg[EPV], fdu[EPV];
+        Codec<T>::template unpack<BYTES>(d[k], fd);
+        Codec<T>::template unpack<BYTES>(g[k], fg);
+        Codec<T>::template unpack<BYTES>(u[k], fu);
+#pragma unroll
+        for (int e = 0; e < EPV; ++e) Math<FAST>::bwd(fd[e], fg[e], fu[e], gm, dm, fdg[e], fdu[e]);
+        Vec<BYTES> vdg, vdu;
+        Codec<T>::template pack<BYTES>(fdg, vdg);
+        Codec<T>::template pack<BYTES>(fdu, vdu);
+        St<BYTES, STM>::st(byte(dgate) + og[k], vdg);
+        St<BYTES, STM>::st(byte(dup) + og[k], vdu);
+      }
+    }
+  }
+
+  if constexpr (!ROWS) {
+    if (blockIdx.x == gridDim.x - 1 && (int)threadIdx.x < s.edge) {
+      constexpr int ES = Codec<T>::kSize;
+      const int t = threadIdx.x;
+      const long long idx = t < s.head ? (long long)t : (long long)t + s.n_vec * EPV;
+      const long long off = (idx - s.head) * ES;
+      Vec<ES> vd = Ld<ES, LD_PLAIN>::ld(cbyte(dout) + off);
+      Vec<ES> vg = Ld<ES, LD_PLAIN>::ld(cbyte(gate) + off);
+      Vec<ES> vu = Ld<ES, LD_PLAIN>::ld(cbyte(up) + off);
+      float fd[1], fg[1], fu[1], fdg[1], fdu[1];
+      Codec<T>::template unpack<ES>(vd, fd);
+      Codec<T>::template unpack<ES>(vg, fg);
+      Codec<T>::template unpack<ES>(vu, fu);
+      Math<FAST>::bwd(fd[0], fg[0], fu[0], gm, dm, fdg[0], fdu[0]);
+      Vec<ES> vdg, vdu;
+      Codec<T>::template pack<ES>(fdg, vdg);
+      Codec<T>::template pack<ES>(fdu, vdu);
+      St<ES, ST_PLAIN>::st(byte(dgate) + off, vdg);
+      St<ES, ST_PLAIN>::st(byte(dup) + off, vdu);
+    }
+  }
+}
+
+}  // namespace swiglu_b200

@@ -1,0 +1,138 @@
+"""Writes tests/golden/*.npz by running the REFERENCE ITSELF on the host.
+
+    python tests/golden/make_golden.py [--reference /path/to/kernel-POCs]
+
+Imports ``kernels.swiglu`` from a checkout of Forge-researchlab/kernel-POCs and calls its own
+``swiglu`` / ``swiglu_packed`` on CPU tensors (for which it evaluates torch_swiglu_reference,
+kernels/swiglu/swiglu.py:396-397, with the backward by autograd).  Shapes, seeds, draw order
+and multipliers follow the reference's tests/test_swiglu.py:28-113; the extra cases are the
+benchmark configuration "fp32 [2,128,1024], seed 0" and wide-tailed N(0, 2^2) inputs.
+
+The reference checkout is needed only to regenerate the vectors; the tests read the .npz
+files.  Arrays hold raw storage: float32, or uint16 bit patterns for fp16/bf16.
+"""
+from __future__ import annotations
+
+import argparse
+import hashlib
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+
+DTYPES = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
+
+
+def bits(x: torch.Tensor) -> np.ndarray:
+    x = x.detach().contiguous()
+    if x.dtype == torch.float32:
+        return x.numpy().copy()
+    return x.view(torch.int16).numpy().view(np.uint16).copy()
+
+
+def run_separate(ref, gate, up, dout, gm, dm):
+    g = gate.detach().clone().requires_grad_(True)
+    u = up.detach().clone().requires_grad_(True)
+    h = ref.swiglu(g, u, gm, dm)
+    h.backward(dout)
+    return h.detach(), g.grad, u.grad
+
+
+def run_packed(ref, gate_up, dout, gm, dm):
+    gu = gate_up.detach().clone().requires_grad_(True)
+    h = ref.swiglu_packed(gu, gm, dm)
+    h.backward(dout)
+    return h.detach(), gu.grad
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    sys.path.insert(0, args.reference)
+    import kernels.swiglu as ref  # the reference package, not this repository's drop-in
+
+    assert Path(ref.__file__).resolve().is_relative_to(Path(args.reference).resolve()), ref.__file__
+    torch.set_num_threads(1)
+
+    # --- separate layout: reference tests/test_swiglu.py:28-65 (smaller last shape) ----------
+    out = {}
+    for dname, dtype in DTYPES.items():
+        for shape in [(2, 8, 128), (1, 3, 257), (3, 5, 200)]:
+            for gm, dm in [(1.0, 1.0), (0.7, 1.3)]:
+                torch.manual_seed(0)
+                gate = torch.randn(*shape, dtype=dtype)
+                up = torch.randn(*shape, dtype=dtype)
+                dout = torch.randn(*shape, dtype=dtype)  # randn_like(out_ref) in the reference test
+                h, dgate, dup = run_separate(ref, gate, up, dout, gm, dm)
+                key = f"{dname}|{'x'.join(map(str, shape))}|{gm}|{dm}"
+                for name, t in dict(gate=gate, up=up, dout=dout, h=h, dgate=dgate, dup=dup).items():
+                    out[f"{key}|{name}"] = bits(t)
+    np.savez_compressed(HERE / "separate.npz", **out)
+
+    # --- packed layout: reference tests/test_swiglu.py:68-99 ----------------------------------
+    out = {}
+    for dname, dtype in DTYPES.items():
+        for shape in [(2, 8, 256), (1, 3, 514)]:
+            for gm, dm in [(1.0, 1.0), (1.5, 0.5)]:
+                torch.manual_seed(1)
+                gate_up = torch.randn(*shape, dtype=dtype)
+                dout = torch.randn(*shape[:-1], shape[-1] // 2, dtype=dtype)
+                h, dgate_up = run_packed(ref, gate_up, dout, gm, dm)
+                key = f"{dname}|{'x'.join(map(str, shape))}|{gm}|{dm}"
+                for name, t in dict(gate_up=gate_up, dout=dout, h=h, dgate_up=dgate_up).items():
+                    out[f"{key}|{name}"] = bits(t)
+    np.savez_compressed(HERE / "packed.npz", **out)
+
+    # --- special values: reference tests/test_swiglu.py:102-113, in all three dtypes ---------
+    out = {}
+    inf, nan = float("inf"), float("nan")
+    for dname, dtype in DTYPES.items():
+        gate = torch.tensor([[[0.0, inf, -inf, nan, 20.0, -20.0, 88.0, -88.0, 1e-30, -0.0]]], dtype=dtype)
+        up = torch.tensor([[[1.0, 2.0, 3.0, 4.0, -1.0, -2.0, 0.5, 0.5, 1.0, 1.0]]], dtype=dtype)
+        h = ref.swiglu(gate, up)
+        out[f"{dname}|gate"], out[f"{dname}|up"], out[f"{dname}|h"] = bits(gate), bits(up), bits(h)
+    np.savez_compressed(HERE / "special.npz", **out)
+
+    # --- wide tails: N(0, 2^2) inputs, odd width, as in the var-len benchmark configuration --
+    out = {}
+    for dname, dtype in DTYPES.items():
+        g = torch.Generator().manual_seed(2)
+        shape = (7, 1101)
+        gate = (2.0 * torch.randn(*shape, generator=g)).to(dtype)
+        up = (2.0 * torch.randn(*shape, generator=g)).to(dtype)
+        dout = (2.0 * torch.randn(*shape, generator=g)).to(dtype)
+        h, dgate, dup = run_separate(ref, gate, up, dout, 1.0, 1.0)
+        for name, t in dict(gate=gate, up=up, dout=dout, h=h, dgate=dgate, dup=dup).items():
+            out[f"{dname}|{name}"] = bits(t)
+    np.savez_compressed(HERE / "tails.npz", **out)
+
+    # --- benchmark configuration 1: fp32 [2,128,1024], seed 0, draw order gate, up, dh --------
+    torch.manual_seed(0)
+    gate = torch.randn(2, 128, 1024)
+    up = torch.randn(2, 128, 1024)
+    dout = torch.randn(2, 128, 1024)
+    h, dgate, dup = run_separate(ref, gate, up, dout, 1.0, 1.0)
+    rows = np.array([0, 37, 255])
+    out = {
+        "rows": rows,
+        "inputs_sha256": np.frombuffer(
+            hashlib.sha256(bits(gate).tobytes() + bits(up).tobytes() + bits(dout).tobytes()).digest(), dtype=np.uint8
+        ),
+    }
+    for name, t in dict(gate=gate, up=up, dout=dout, h=h, dgate=dgate, dup=dup).items():
+        flat = t.reshape(256, 1024)
+        out[f"{name}_rows"] = bits(flat[rows])
+        out[f"{name}_sum"] = np.array(flat.double().sum().item())
+        out[f"{name}_meanabs"] = np.array(flat.double().abs().mean().item())
+    np.savez_compressed(HERE / "config1.npz", **out)
+
+    for f in sorted(HERE.glob("*.npz")):
+        print(f.name, f.stat().st_size, "bytes")
+
+
+if __name__ == "__main__":
+    main()
