@@ -34,6 +34,7 @@ sys.path.insert(0, str(ROOT))
 
 import torch
 
+DTYPE_NAME = {torch.float32: "fp32", torch.float16: "fp16", torch.bfloat16: "bf16"}
 METRIC = "swiglu_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this GPU pool, used when MEASURED_PEAKS.json is absent
@@ -194,7 +195,7 @@ def time_cpu_path(w, budget_s: float, min_steps: int = 3, fixed_steps: int | Non
         "cores": torch.get_num_threads(),
         "host_cpus": os.cpu_count(),
         "kind": "port",
-        "sample": f"first {rows} of {w.tokens} token rows of {w.name} ({w.width} wide, {str(w.dtype).split('.')[-1]}), "
+        "sample": f"first {rows} of {w.tokens} token rows of {w.name} ({w.width} wide, {DTYPE_NAME[w.dtype]}), "
                   f"{len(times)} steps of fwd+bwd by the ATen composite + autograd, mean {sec * 1e3:.1f} ms/step",
         "ms_per_step_sample": sec * 1e3,
         "steps": len(times),
@@ -212,7 +213,7 @@ def run_reference_arm(args, w):
         "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": res["ms_per_step_sample"] * (w.tokens / rows),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": str(w.dtype).split(".")[-1], "data": "synthetic",
+        "dtype": DTYPE_NAME[w.dtype], "data": "synthetic",
         "config": config_of(w, args, 1),
         "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -225,7 +226,7 @@ def run_reference_arm(args, w):
 
 def config_of(w, args, world):
     return {
-        "workload": f"{w.name}: {w.note}; gate/up/dh {str(w.dtype).split('.')[-1]} [{w.tokens}, {w.width}] per GPU, "
+        "workload": f"{w.name}: {w.note}; gate/up/dh {DTYPE_NAME[w.dtype]} [{w.tokens}, {w.width}] per GPU, "
                     f"N(0,{w.std:g}^2), seed {w.seed}",
         "tokens_per_gpu": w.tokens, "width": w.width, "global_tokens": w.tokens * world,
         "backward": "out-of-place" if args.preserve_inputs else "in-place",
@@ -336,42 +337,47 @@ def main():
     # ---- end to end from pinned host buffers -------------------------------------------------
     e2e = None
     if not args.no_e2e:
+        from kernel_pocs_b200.host_path import swiglu_fwd_bwd_host, workspace_bytes
+
         es = gate0.element_size()
         hg, hu, hd = (torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in (gate0, up0, dh))
         hg.copy_(gate0), hu.copy_(up0), hd.copy_(dh)
-        oh, odg, odu = (torch.empty(gate0.shape, dtype=gate0.dtype, pin_memory=True) for _ in range(3))
-        dev_dh = torch.empty_like(dh)
+        outs = tuple(torch.empty(gate0.shape, dtype=gate0.dtype, pin_memory=True) for _ in range(3))
+        ws = torch.empty(workspace_bytes(w.tokens, w.width, w.dtype), dtype=torch.uint8, device=device)
 
         def e2e_step():
-            with torch.no_grad():
-                gate.copy_(hg, non_blocking=True)
-                up.copy_(hu, non_blocking=True)
-                dev_dh.copy_(hd, non_blocking=True)
-            h = swiglu(gate, up, 1.0, 1.0, preserve)
-            dgate, dup = torch.autograd.grad(h, (gate, up), dev_dh)
-            oh.copy_(h, non_blocking=True)
-            odg.copy_(dgate, non_blocking=True)
-            odu.copy_(dup, non_blocking=True)
+            # one call of the host-buffer entry point: chunks of rows are copied in, run through
+            # the forward and the in-place backward, and copied out, three chunks in flight
+            swiglu_fwd_bwd_host(hg, hu, hd, 1.0, 1.0, out=outs, workspace=ws)
 
-        e2e_step()
+        for _ in range(2):
+            e2e_step()
         barrier()
+        e2e_launches0 = _lib.launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.e2e_steps):
             e2e_step()
         e1.record()
         barrier()
+        e2e_launches = _lib.launch_count() - e2e_launches0
         te = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
         e2e_ms = te.item() / args.e2e_steps
+        # the bytes that came back are the device path's results
         restore()
-        if not torch.equal(oh[:4], step()[0][:4].cpu()):
-            raise SystemExit("e2e: the bytes copied back to the host differ from the device result")
+        h_dev, dgate_dev, dup_dev = step()
+        for got, want in zip(outs, (h_dev, dgate_dev, dup_dev)):
+            if not torch.equal(got[:64], want[:64].cpu()) or not torch.equal(got[-64:], want[-64:].cpu()):
+                raise SystemExit("e2e: the bytes copied back to the host differ from the device result")
         e2e = {"value": tokens_total / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": 3 * gate0.numel() * es * world, "d2h_bytes_per_step": 3 * gate0.numel() * es * world,
-               "steps": args.e2e_steps,
-               "path": "pinned host gate/up/dh -> device, swiglu() + autograd backward, h/dgate/dup -> pinned host"}
+               "steps": args.e2e_steps, "gpu_launches": e2e_launches,
+               "path": "swiglu_b200_host_fwd_bwd: pinned host gate/up/dh -> device workspace in row chunks, forward + "
+                       "in-place backward per chunk, h/dgate/dup -> pinned host; copies of neighbouring chunks overlap "
+                       "the kernels"}
+        del ws
 
     if sampler:
         sampler.stop()
@@ -383,7 +389,7 @@ def main():
         bwd_gbs = w.bytes_bwd() / bwd_avg_s / 1e9
         fwd_gbs = w.bytes_fwd() / fwd_avg_s / 1e9
         both_gbs = (w.bytes_fwd() + w.bytes_bwd()) / (ms_per_step * 1e-3) / 1e9
-        dt = str(w.dtype).split(".")[-1]
+        dt = DTYPE_NAME[w.dtype]
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",

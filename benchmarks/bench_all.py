@@ -1,0 +1,227 @@
+"""SwiGLU section of the kernel benchmark: GB/s, tokens/s and roofline fraction per configuration.
+
+    python benchmarks/bench_all.py [--configs c1 c2 c3 ...] [--modes forward backward full]
+                                   [--providers b200 b200-safe torch-eager] [--rep 50] [--warmup 20]
+                                   [--save results.json]
+    python -m torch.distributed.run --nproc-per-node G benchmarks/bench_all.py --configs c5 --strong
+
+Takes the place of the reference's per-kernel sweep (kernels/swiglu/benchmarks/benchmark_swiglu.py:
+providers x modes x shapes, CUDA-event timing with the two fastest and two slowest repetitions
+dropped, :97-120) and of the empty benchmarks/bench_all.py the reference ships.  What it adds: every
+row carries the algorithmic byte count (forward 3*N*s, backward 5*N*s, full 8*N*s bytes), the
+achieved GB/s, its fraction of the measured HBM copy bandwidth of this pool and of the nominal
+8 TB/s, and tokens/s.
+
+Providers
+    b200         this library, in-place backward (the operator's default)
+    b200-safe    this library, preserve_inputs=True
+    b200-packed  this library, packed gate|up layout
+    torch-eager  the PyTorch composite (torch_swiglu_reference + autograd) on the same GPU
+
+Configurations are the synthetic workloads of kernel_pocs_b200/workloads.py plus ragged variants
+of the variable-length one: width 11009, and the same with the first token row sliced off so that
+every tensor starts 2 bytes past a 16-byte boundary.
+
+With --strong under torchrun, each rank takes a contiguous block of the token rows (no collective
+on the data path) and rank 0 reports aggregate tokens/s = tokens / max over ranks of the time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+
+import torch
+
+from kernel_pocs_b200 import workloads as W
+
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def hbm_peak():
+    try:
+        return float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def time_cuda(fn, setup, warmup: int, rep: int):
+    """Per-repetition CUDA-event timing; ``setup`` runs untimed before each repetition.
+    Returns (trimmed mean, median, min) in milliseconds."""
+    for _ in range(warmup):
+        setup()
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(rep):
+        setup()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    times.sort()
+    trimmed = times[2:-2] if len(times) > 8 else times
+    return sum(trimmed) / len(trimmed), times[len(times) // 2], times[0]
+
+
+def make_case(name: str, device, rank: int, world: int, strong: bool, max_rows: int = 0):
+    """Returns (workload, gate, up, dh) for this rank."""
+    base = name.split("+")[0]
+    w = W.workloads()[base]
+    variant = name.split("+")[1] if "+" in name else ""
+    if variant in ("w11009", "w11009-off1"):
+        w = W.Workload(name, w.tokens, 11009, w.dtype, w.seed, w.std, w.note + ", odd width 11009")
+    if max_rows and w.tokens > max_rows:
+        w = W.Workload(w.name, max_rows, w.width, w.dtype, w.seed, w.std, w.note + f", first {max_rows} token rows")
+    lo, hi = W.row_shard(w.tokens, world, rank) if strong else (0, w.tokens)
+    gate, up, dh = W.generate_rows(w, lo, hi, device)
+    if variant == "w11009-off1":
+        gate, up, dh = gate[1:], up[1:], dh[1:]  # contiguous, but 11009*s bytes past the allocation start
+    return w, gate, up, dh
+
+
+def run_case(name, args, device, rank, world):
+    from kernels.swiglu import swiglu_backward, swiglu_forward, swiglu_packed_backward, swiglu_packed_forward
+    from kernels.swiglu import torch_swiglu_reference
+
+    w, gate0, up0, dh = make_case(name, device, rank, world, args.strong, args.max_rows)
+    rows, width = gate0.shape
+    es = gate0.element_size()
+    n = rows * width
+    byte_model = {"forward": 3 * n * es, "backward": 5 * n * es, "full": 8 * n * es}
+    out_rows = []
+    for provider in args.providers:
+        packed = provider == "b200-packed"
+        preserve = provider == "b200-safe"
+        gate, up = gate0.clone(), up0.clone()
+        gate_up0 = torch.cat([gate0, up0], dim=-1) if packed else None
+        gate_up = gate_up0.clone() if packed else None
+
+        def restore():
+            if packed:
+                gate_up.copy_(gate_up0)
+            elif provider == "b200":
+                gate.copy_(gate0)
+                up.copy_(up0)
+
+        if provider == "torch-eager":
+            g = gate0.clone().requires_grad_(True)
+            u = up0.clone().requires_grad_(True)
+            state = {}
+
+            def fwd():
+                state["h"] = torch_swiglu_reference(g, u)
+
+            def bwd():
+                torch.autograd.grad(state["h"], (g, u), dh)
+
+            def full():
+                fwd()
+                bwd()
+
+            setups = {"forward": lambda: None, "backward": fwd, "full": lambda: None}
+        elif packed:
+            def fwd():
+                swiglu_packed_forward(gate_up)
+
+            def bwd():
+                swiglu_packed_backward(dh, gate_up, gate_up.shape, preserve_inputs=False)
+
+            def full():
+                fwd()
+                bwd()
+
+            setups = {m: restore for m in ("forward", "backward", "full")}
+        else:
+            def fwd():
+                swiglu_forward(gate, up)
+
+            def bwd():
+                swiglu_backward(dh, gate, up, preserve_inputs=preserve)
+
+            def full():
+                fwd()
+                bwd()
+
+            setups = {m: restore for m in ("forward", "backward", "full")}
+
+        fns = {"forward": fwd, "backward": bwd, "full": full}
+        for mode in args.modes:
+            mean, med, best = time_cuda(fns[mode], setups[mode], args.warmup, args.rep)
+            t = torch.tensor([mean, med, best], dtype=torch.float64, device=device)
+            if world > 1:
+                import torch.distributed as dist
+
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            mean, med, best = t.tolist()
+            out_rows.append({
+                "config": name, "provider": provider, "mode": mode, "dtype": str(w.dtype).split(".")[-1],
+                "tokens_per_gpu": rows, "width": width, "gpus": world,
+                "ms_mean_trimmed": mean, "ms_median": med, "ms_min": best,
+                "algorithmic_bytes_per_gpu": byte_model[mode],
+                "gbs_per_gpu": byte_model[mode] / (mean * 1e-3) / 1e9,
+                "tokens_per_s": (w.tokens if args.strong else rows * world) / (mean * 1e-3),
+            })
+        del gate, up, gate_up, gate_up0
+        torch.cuda.empty_cache()
+    return out_rows
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--configs", nargs="+", default=["c1", "c2", "c3", "c3-fp32", "c3+w11009", "c3+w11009-off1"])
+    ap.add_argument("--providers", nargs="+", default=["b200", "b200-safe", "torch-eager"],
+                    choices=["b200", "b200-safe", "b200-packed", "torch-eager"])
+    ap.add_argument("--modes", nargs="+", default=["forward", "backward", "full"],
+                    choices=["forward", "backward", "full"])
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--rep", type=int, default=50)
+    ap.add_argument("--strong", action="store_true", help="split each configuration's token rows across the ranks")
+    ap.add_argument("--max-rows", type=int, default=0,
+                    help="cap the token rows of every configuration (small cases for profiler captures)")
+    ap.add_argument("--save", default="")
+    args = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("CUDA is required: the SwiGLU path has no CPU fallback")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+
+    peak, kind = hbm_peak()
+    rows = []
+    for name in args.configs:
+        for r in run_case(name, args, device, rank, world):
+            r["frac_of_measured_copy"] = r["gbs_per_gpu"] / peak
+            r["frac_of_nominal_8TBs"] = r["gbs_per_gpu"] / NOMINAL_HBM_GBS
+            rows.append(r)
+            if rank == 0:
+                print(f"{r['config']:>16} {r['provider']:>11} {r['mode']:>8} {r['dtype']:>8} "
+                      f"{r['ms_mean_trimmed']:9.4f} ms  {r['gbs_per_gpu']:8.1f} GB/s/GPU  "
+                      f"{100 * r['frac_of_measured_copy']:6.1f}% of {kind} {peak:.0f}  "
+                      f"{100 * r['frac_of_nominal_8TBs']:5.1f}% of 8000  {r['tokens_per_s'] / 1e6:9.3f} Mtok/s "
+                      f"x{world}", flush=True)
+    if rank == 0 and args.save:
+        Path(args.save).parent.mkdir(parents=True, exist_ok=True)
+        Path(args.save).write_text(json.dumps({"hbm_peak_gbs": peak, "hbm_peak_kind": kind, "rows": rows}, indent=1))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

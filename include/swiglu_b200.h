@@ -55,6 +55,7 @@ extern "C" {
 #define SWIGLU_B200_ERR_DEVICE 6      /* cudaSetDevice / attribute query failed                */
 #define SWIGLU_B200_ERR_LAUNCH 7      /* the kernel launch was rejected by the runtime          */
 #define SWIGLU_B200_ERR_COPY 8        /* a host<->device copy of the host-buffer entry failed  */
+#define SWIGLU_B200_ERR_WORKSPACE 9   /* the device workspace cannot hold even one token row   */
 
 /* ABI version of this header: major*1000 + minor. */
 SWIGLU_B200_API int swiglu_b200_version(void);
@@ -89,6 +90,26 @@ SWIGLU_B200_API int swiglu_b200_fwd(void* out, const void* gate, const void* up,
 SWIGLU_B200_API int swiglu_b200_bwd(void* dgate, void* dup, const void* dout, const void* gate, const void* up, int64_t rows,
                     int64_t cols, int64_t in_row_stride, int64_t grad_row_stride, int64_t dout_row_stride, int dtype,
                     float gm, float dm, int device, void* stream);
+
+/* Forward + backward for tensors held in HOST memory (pinned memory recommended; pageable
+ * memory works but its copies do not overlap).  No counterpart in the reference, whose path
+ * only takes device tensors; it serves callers that keep activations off the device and is
+ * the call the end-to-end benchmark times.
+ *
+ * All six tensors are contiguous rows x cols in host memory: gate, up, dout are read; h,
+ * dgate, dup are written.  The rows are cut into chunks that fit the caller's device
+ * `workspace` (256-byte aligned, any size that holds at least 12 token rows; see
+ * swiglu_b200_host_workspace_bytes for a size that makes the chunks about 32 MiB) and three
+ * chunks are kept in flight: while one is copied in, the kernels run on the previous one and
+ * the one before is copied out, on two internal copy streams and the caller's `stream`.
+ * The call only enqueues work; when `stream` is synchronised every output is on the host.
+ * The workspace must not be used by other work until then. */
+SWIGLU_B200_API int swiglu_b200_host_fwd_bwd(void* h, void* dgate, void* dup, const void* gate, const void* up, const void* dout,
+                             int64_t rows, int64_t cols, int dtype, float gm, float dm, void* workspace,
+                             uint64_t workspace_bytes, int device, void* stream);
+
+/* Recommended workspace size in bytes for swiglu_b200_host_fwd_bwd (0 for an empty problem). */
+SWIGLU_B200_API uint64_t swiglu_b200_host_workspace_bytes(int64_t rows, int64_t cols, int dtype);
 
 #ifdef __cplusplus
 }

@@ -1,7 +1,8 @@
 """ctypes binding of libswiglu_b200.so (the C ABI declared in include/swiglu_b200.h).
 
-There is no fallback: if the shared library is missing or does not export a declared symbol,
-importing this module raises.  Build it with ``python -m kernel_pocs_b200.build``.
+There is no fallback.  If the shared library is missing or was built from other sources than
+the ones in the tree, it is rebuilt with nvcc on import; if that is impossible, or the library
+does not export a declared symbol, importing this module raises.
 """
 from __future__ import annotations
 
@@ -32,15 +33,26 @@ SIGNATURES = {
         [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, ctypes.c_int,
          ctypes.c_float, ctypes.c_float, ctypes.c_int, _c_ptr],
     ),
+    "swiglu_b200_host_fwd_bwd": (
+        ctypes.c_int,
+        [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, ctypes.c_int, ctypes.c_float,
+         ctypes.c_float, _c_ptr, ctypes.c_uint64, ctypes.c_int, _c_ptr],
+    ),
+    "swiglu_b200_host_workspace_bytes": (ctypes.c_uint64, [_c_i64, _c_i64, ctypes.c_int]),
 }
 
 
 def _load() -> ctypes.CDLL:
-    if not LIB_PATH.exists():
-        raise ImportError(
-            f"{LIB_PATH} is missing: the SwiGLU CUDA library has not been built "
-            "(run `python -m kernel_pocs_b200.build`); there is no non-CUDA fallback"
-        )
+    from . import build as _build
+
+    if _build.is_stale():
+        try:
+            _build.build()
+        except Exception as exc:
+            raise ImportError(
+                f"{LIB_PATH} is missing or out of date and could not be built ({exc}); "
+                "there is no non-CUDA fallback"
+            ) from exc
     lib = ctypes.CDLL(str(LIB_PATH))
     for name, (restype, argtypes) in SIGNATURES.items():
         try:

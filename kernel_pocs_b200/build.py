@@ -8,6 +8,7 @@ runtime statically and knows nothing about PyTorch).  nvcc cross-compiles withou
 from __future__ import annotations
 
 import argparse
+import hashlib
 import os
 import shutil
 import subprocess
@@ -19,8 +20,9 @@ ROOT = PKG.parent
 CSRC = PKG / "csrc"
 INCLUDE = ROOT / "include"
 LIB_PATH = PKG / "libswiglu_b200.so"
+STAMP_PATH = PKG / "libswiglu_b200.so.stamp"  # digest of the sources the library was built from
 
-SOURCES = [CSRC / "swiglu_capi.cu"]
+SOURCES = [CSRC / "swiglu_capi.cu", CSRC / "swiglu_host.cu"]
 HEADERS = [CSRC / "swiglu_kernels.cuh", INCLUDE / "swiglu_b200.h"]
 
 NVCC_FLAGS = [
@@ -38,11 +40,21 @@ def _nvcc() -> str:
     return exe
 
 
+def source_digest() -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(NVCC_FLAGS).encode())
+    for p in SOURCES + HEADERS:
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    return h.hexdigest()
+
+
 def is_stale() -> bool:
-    if not LIB_PATH.exists():
+    """True when the library is missing or was built from other sources (compared by content,
+    because file times do not survive a copy of the tree to another machine)."""
+    if not (LIB_PATH.exists() and STAMP_PATH.exists()):
         return True
-    built = LIB_PATH.stat().st_mtime
-    return any(p.stat().st_mtime > built for p in SOURCES + HEADERS + [Path(__file__)])
+    return STAMP_PATH.read_text().strip() != source_digest()
 
 
 def build(force: bool = False, verbose: bool = False, extra_flags: list[str] | None = None) -> Path:
@@ -60,6 +72,9 @@ def build(force: bool = False, verbose: bool = False, extra_flags: list[str] | N
         tmp.unlink(missing_ok=True)
         raise RuntimeError(f"nvcc failed ({proc.returncode}):\n{' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
     os.replace(tmp, LIB_PATH)
+    stamp_tmp = STAMP_PATH.with_suffix(f".stamp.tmp{os.getpid()}")
+    stamp_tmp.write_text(source_digest() + "\n")
+    os.replace(stamp_tmp, STAMP_PATH)
     if verbose:
         sys.stderr.write(proc.stderr)
     return LIB_PATH

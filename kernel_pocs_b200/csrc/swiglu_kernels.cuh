@@ -251,7 +251,11 @@ template <> struct Math<true> {
     float z = g * gm;
     float e, r;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
+#ifdef SWIGLU_RCP_FTZ
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+#else
+    asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));  // no .ftz: for z < -87.3 the reciprocal is subnormal
+#endif
     return (z * r) * u * dm;
   }
   static __device__ __forceinline__ void bwd(float dh, float g, float u, float gm, float dm, float& dgate,
@@ -259,7 +263,11 @@ template <> struct Math<true> {
     float z = g * gm;
     float e, sig;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
+#ifdef SWIGLU_RCP_FTZ
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(sig) : "f"(1.0f + e));
+#else
+    asm("rcp.approx.f32 %0, %1;" : "=f"(sig) : "f"(1.0f + e));
+#endif
     float d = dh * dm;
     float silu = z * sig;
     dup = d * silu;

@@ -72,6 +72,24 @@ def test_argument_errors_need_no_device():
     assert b(dg, du, dg, g, u, 4, 8, 8, 8, 8, _lib.F32, 1.0, 1.0, -1, None) == c["ERR_ALIAS"]  # dgate over dout
 
 
+def test_host_entry_argument_errors_need_no_device():
+    c = _codes()
+    f = _lib.lib.swiglu_b200_host_fwd_bwd
+    p = 0x1000
+    args = (p, p, p, p, p, p)
+    assert f(*args, 4, 8, 5, 1.0, 1.0, 0x100000, 1 << 20, -1, None) == c["ERR_DTYPE"]
+    assert f(*args, -4, 8, _lib.F32, 1.0, 1.0, 0x100000, 1 << 20, -1, None) == c["ERR_SHAPE"]
+    assert f(*args, 0, 8, _lib.F32, 1.0, 1.0, None, 0, -1, None) == 0
+    assert f(None, p, p, p, p, p, 4, 8, _lib.F32, 1.0, 1.0, 0x100000, 1 << 20, -1, None) == c["ERR_NULL"]
+    assert f(*args, 4, 8, _lib.F32, 1.0, 1.0, None, 1 << 20, -1, None) == c["ERR_NULL"]
+    assert f(*args, 4, 8, _lib.F32, 1.0, 1.0, 0x100010, 1 << 20, -1, None) == c["ERR_ALIGN"]
+    assert f(*args, 4, 1 << 20, _lib.F32, 1.0, 1.0, 0x100000, 1 << 20, -1, None) == c["ERR_WORKSPACE"]
+    w = _lib.lib.swiglu_b200_host_workspace_bytes
+    assert w(0, 8, _lib.BF16) == 0
+    assert w(32768, 14336, _lib.BF16) == 12 * ((32 << 20) // (14336 * 2)) * 14336 * 2  # 12 buffers of <= 32 MiB
+    assert w(3, 8, _lib.F32) == 12 * 256  # never more than the problem, rounded to the buffer alignment
+
+
 def test_launch_counter_is_exported_and_idle():
     before = _lib.launch_count()
     _lib.lib.swiglu_b200_fwd(None, None, None, 0, 8, 8, 8, _lib.F32, 1.0, 1.0, -1, None)

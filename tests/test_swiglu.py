@@ -440,3 +440,49 @@ def test_large_shape_properties():
     # dup is linear in dh: doubling dh doubles dup exactly (power-of-two scaling is exact in bf16)
     _, dup2 = swiglu_backward(dout * 2, gate, up, preserve_inputs=True)
     assert torch.equal(dup2, dup * 2)
+
+
+# --------------------------------------------------------------------------------------------
+# host-buffer entry point
+# --------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dname", ["bf16", "fp32"])
+@pytest.mark.parametrize("rows,cols,ws_rows", [(1, 8, 1), (37, 1003, 5), (1000, 512, 64), (4096, 1024, 0)])
+def test_host_buffer_pipeline_matches_device_path(dname, rows, cols, ws_rows):
+    """Host tensors streamed through a small workspace (many chunks, ragged last chunk) give
+    bit-identical results to the device-resident path, and leave the inputs untouched."""
+    from kernel_pocs_b200.host_path import swiglu_fwd_bwd_host, workspace_bytes
+
+    dtype = DTYPES[dname]
+    g = torch.Generator().manual_seed(21)
+    gate, up, dout = (torch.randn(rows, cols, generator=g).to(dtype).pin_memory() for _ in range(3))
+    gate0, up0 = gate.clone(), up.clone()
+    if ws_rows:
+        # room for exactly ws_rows token rows per staged buffer: 3 slots x 4 buffers
+        per = (ws_rows * cols * gate.element_size() + 255) // 256 * 256
+        ws = torch.empty(12 * per, dtype=torch.uint8, device=DEVICE)
+    else:
+        ws = torch.empty(workspace_bytes(rows, cols, dtype), dtype=torch.uint8, device=DEVICE)
+    before = _lib.launch_count()
+    h, dgate, dup = swiglu_fwd_bwd_host(gate, up, dout, 0.9, 1.1, workspace=ws)
+    torch.cuda.synchronize()
+    chunks = -(-rows // ws_rows) if ws_rows else 1
+    assert _lib.launch_count() - before == 2 * chunks
+    assert torch.equal(gate, gate0) and torch.equal(up, up0)
+    dh, dgate_ref, dup_ref = swiglu_forward(gate.to(DEVICE), up.to(DEVICE), 0.9, 1.1)[0], None, None
+    dgate_ref, dup_ref = swiglu_backward(dout.to(DEVICE), gate.to(DEVICE), up.to(DEVICE), 0.9, 1.1, True)
+    assert torch.equal(h, dh.cpu()) and torch.equal(dgate, dgate_ref.cpu()) and torch.equal(dup, dup_ref.cpu())
+    check_against_oracle(h, dgate, dup, gate0, up0, dout, 0.9, 1.1, f"host path {dname} {rows}x{cols}")
+
+
+def test_host_buffer_pipeline_rejects_bad_arguments():
+    from kernel_pocs_b200.host_path import swiglu_fwd_bwd_host
+
+    gate, up, dout = (torch.randn(4, 64).pin_memory() for _ in range(3))
+    with pytest.raises(_lib.SwigluB200Error, match="workspace too small"):
+        swiglu_fwd_bwd_host(gate, up, dout, workspace=torch.empty(256, dtype=torch.uint8, device=DEVICE))
+    with pytest.raises(ValueError, match="host tensors"):
+        swiglu_fwd_bwd_host(gate.to(DEVICE), up.to(DEVICE), dout.to(DEVICE))
+    with pytest.raises(ValueError, match="shape and dtype"):
+        swiglu_fwd_bwd_host(gate, up, dout[:2])
+    torch.cuda.synchronize()
