@@ -111,6 +111,28 @@ SWIGLU_B200_API int swiglu_b200_host_fwd_bwd(void* h, void* dgate, void* dup, co
 /* Recommended workspace size in bytes for swiglu_b200_host_fwd_bwd (0 for an empty problem). */
 SWIGLU_B200_API uint64_t swiglu_b200_host_workspace_bytes(int64_t rows, int64_t cols, int dtype);
 
+/* Fused gate/up projection with SwiGLU epilogue (bf16, fp32 accumulation on the tcgen05 tensor
+ * cores):   h[m][n] = silu((x . w_gate[n]) * gm) * (x . w_up[n]) * dm
+ * Replaces, in one launch, the reference's two projection GEMMs followed by the activation
+ * kernel (forge/forge/patching/kernels/basic.py:97-102: swiglu(gate_proj(x), up_proj(x))); the
+ * reference's own fused attempts are kernels/lora_mlp/experiments/v2/lora_mlp_kernel_v2.py:32-138
+ * (Triton dual GEMM) and kernels/lora_mlp/experiments/v4/cublaslt_silu.cu:9-92 (cuBLASLt SWISH).
+ *   x              m x k bf16, row-major (k contiguous)
+ *   w_gate, w_up   n x k bf16, row-major (the layout of torch.nn.Linear.weight)
+ *   h              m x n bf16, row-major
+ *   gate_out,up_out  both NULL, or both m x n bf16: the pre-activations rounded to bf16, for a
+ *                  backward pass through swiglu_b200_bwd
+ *   status         device int, 4-byte aligned, owned by the caller.  The launch zeroes it; after
+ *                  the stream has been synchronised it is 0, or the code of the first internal
+ *                  wait that gave up (every wait in the kernel is bounded; on such a failure the
+ *                  kernel returns early and h is incomplete).
+ * Requires k % 8 == 0, n % 16 == 0 and 16-byte aligned pointers. */
+SWIGLU_B200_API int swiglu_b200_gemm_fwd(void* h, void* gate_out, void* up_out, const void* x, const void* w_gate, const void* w_up,
+                         int64_t m, int64_t n, int64_t k, float gm, float dm, void* status, int device, void* stream);
+
+/* Number of fused-GEMM kernels launched by this process. */
+SWIGLU_B200_API uint64_t swiglu_b200_gemm_launch_count(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -39,6 +39,12 @@ SIGNATURES = {
          ctypes.c_float, _c_ptr, ctypes.c_uint64, ctypes.c_int, _c_ptr],
     ),
     "swiglu_b200_host_workspace_bytes": (ctypes.c_uint64, [_c_i64, _c_i64, ctypes.c_int]),
+    "swiglu_b200_gemm_fwd": (
+        ctypes.c_int,
+        [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, ctypes.c_float, ctypes.c_float,
+         _c_ptr, ctypes.c_int, _c_ptr],
+    ),
+    "swiglu_b200_gemm_launch_count": (ctypes.c_uint64, []),
 }
 
 

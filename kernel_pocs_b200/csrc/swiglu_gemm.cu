@@ -1,0 +1,358 @@
+// Fused gate/up projection + SwiGLU epilogue for sm_100a:
+//
+//     h[M, N] = silu((X Wg^T) * gm) * (X Wu^T) * dm        X [M, K], Wg, Wu [N, K], all bf16, K contiguous
+//
+// One kernel replaces two projection GEMMs plus the activation kernel, so the 2*M*N
+// pre-activations are never written to or re-read from HBM (unless the caller asks for them for
+// a backward pass).  The nearest code in the reference is its Triton dual-GEMM
+// (kernels/lora_mlp/experiments/v2/lora_mlp_kernel_v2.py:32-138) and its cuBLASLt call with a
+// SWISH epilogue (kernels/lora_mlp/experiments/v4/cublaslt_silu.cu:9-92); this is a dense
+// contraction and therefore runs on the tcgen05 tensor cores.
+//
+// Structure of a CTA (one 128 x 128 tile of h, 192 threads):
+//   warp 0      TMA producer: per 64-wide K block, three tiled bulk loads (X tile, Wg tile, Wu tile,
+//               each 128 rows x 128 bytes, 128-byte swizzle) into a 4-stage shared-memory ring
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=256, K=16, bf16 -> fp32).  The
+//               Wg and Wu tiles sit back to back in shared memory, so ONE instruction produces both
+//               accumulators: TMEM columns [0,128) = gate, [128,256) = up.  Also owns TMEM alloc/free.
+//   warps 2-5   epilogue: each thread owns one row of the tile, reads 16 gate and 16 up columns at a
+//               time from TMEM, applies SwiGLU in fp32 and stores 32 bytes of bf16 h.
+// No load uses cluster multicast.  Every mbarrier wait is bounded in time: when a wait gives up it
+// records where in the caller's status word, every other wait then leaves at once, the CTA lets
+// in-flight copies land, frees its TMEM and returns.
+#include "swiglu_b200.h"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "swiglu_kernels.cuh"
+
+namespace {
+
+using swiglu_b200::Consts;
+using swiglu_b200::Math;
+
+constexpr int BM = 128;           // rows of X / h per tile
+constexpr int BN = 128;           // columns of h per tile (gate and up each)
+constexpr int BK = 64;            // K elements per stage: 128 bytes, one swizzle atom
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int TILE_BYTES = BM * BK * 2;                  // 16 KiB, same for X, Wg and Wu tiles
+constexpr int STAGE_BYTES = 3 * TILE_BYTES;              // 48 KiB
+constexpr int TMEM_COLS = 256;                           // 128 gate + 128 up fp32 columns
+constexpr int THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr long long WAIT_CYCLES = 1000000000LL;          // ~0.5 s of SM clock per wait
+
+// tcgen05 instruction descriptor, kind::f16: D fp32, A and B bf16, both K-major, M=128, N=256.
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* b, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false when the barrier did not flip within WAIT_CYCLES or when another
+// thread has already reported a failure; the first failure stores `code` in *status.
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int* status, int code) {
+  if (mbar_try_wait(b, parity)) return true;
+  const long long t0 = clock64();
+  for (int spin = 0;; ++spin) {
+    if (mbar_try_wait(b, parity)) return true;
+    if ((spin & 63) == 63) {
+      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (clock64() - t0 > WAIT_CYCLES) {
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row groups
+// 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+  asm volatile(
+      "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(IDESC), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
+
+struct GemmParams {
+  __nv_bfloat16* h;
+  __nv_bfloat16* gate_out;  // optional pre-activations for a backward pass
+  __nv_bfloat16* up_out;
+  int* status;
+  long long m, n, k;
+  float gm, dm;
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+swiglu_gemm_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wg,
+                       const __grid_constant__ CUtensorMap map_wu, const GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  // 128-byte-swizzled tiles need 1024-byte aligned bases
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_ready = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // m fastest: the CTAs of one wave share a few Wg/Wu tiles and walk down X
+  const long long tiles_m = (p.m + BM - 1) / BM;
+  const long long tile_m = blockIdx.x % tiles_m;
+  const long long tile_n = blockIdx.x / tiles_m;
+  const int m0 = (int)(tile_m * BM);
+  const int n0 = (int)(tile_n * BN);
+  const int k_blocks = (int)((p.k + BK - 1) / BK);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_ready, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t round = kb / STAGES;
+        if (kb >= STAGES && !mbar_wait(&empty[s], (round - 1) & 1, p.status, 100 + s)) break;
+        unsigned char* stage = smem + s * STAGE_BYTES;
+        mbar_expect_tx(&full[s], STAGE_BYTES);
+        tma_load_2d(stage, &map_x, kb * BK, m0, &full[s]);
+        tma_load_2d(stage + TILE_BYTES, &map_wg, kb * BK, n0, &full[s]);
+        tma_load_2d(stage + 2 * TILE_BYTES, &map_wu, kb * BK, n0, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < k_blocks && ok; ++kb) {
+        const int s = kb % STAGES;
+        ok = mbar_wait(&full[s], (kb / STAGES) & 1, p.status, 200 + s);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+        const uint64_t a_desc = umma_desc(a_addr);
+        const uint64_t b_desc = umma_desc(a_addr + TILE_BYTES);  // Wg rows 0..127, Wu rows 128..255
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+          // 16 K elements = 32 bytes = 2 descriptor address units further along each 128-byte row
+          umma_bf16(tmem_base, a_desc + 2 * kk, b_desc + 2 * kk, (kb | kk) != 0);
+        }
+        umma_commit(&empty[s]);  // arrives once these MMAs have finished reading the stage
+      }
+      if (ok) umma_commit(acc_ready);
+    }
+  } else {
+    // epilogue warps 2..5 read TMEM lane quarters 2, 3, 0, 1
+    const int quarter = warp & 3;
+    const int row = m0 + quarter * 32 + lane;
+    const Consts cst(p.gm, p.dm);
+    const bool ok = mbar_wait(acc_ready, 0, p.status, 300);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        uint32_t g[16], u[16];
+        tmem_ld16(t_row + c, g);
+        tmem_ld16(t_row + BN + c, u);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < p.m && n0 + c < p.n) {
+          uint32_t hv[8], gv[8], uv[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+            const float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+            __nv_bfloat162 hb = __floats2bfloat162_rn(Math<true>::fwd(g0, u0, cst), Math<true>::fwd(g1, u1, cst));
+            __nv_bfloat162 gb = __floats2bfloat162_rn(g0, g1);
+            __nv_bfloat162 ub = __floats2bfloat162_rn(u0, u1);
+            hv[j] = *reinterpret_cast<uint32_t*>(&hb);
+            gv[j] = *reinterpret_cast<uint32_t*>(&gb);
+            uv[j] = *reinterpret_cast<uint32_t*>(&ub);
+          }
+          const long long off = (long long)row * p.n + n0 + c;
+          // n is a multiple of 16 (checked on the host), so a 16-column group is all in or all out
+          uint4* dst = reinterpret_cast<uint4*>(p.h + off);
+          dst[0] = make_uint4(hv[0], hv[1], hv[2], hv[3]);
+          dst[1] = make_uint4(hv[4], hv[5], hv[6], hv[7]);
+          if (p.gate_out) {
+            uint4* dg = reinterpret_cast<uint4*>(p.gate_out + off);
+            dg[0] = make_uint4(gv[0], gv[1], gv[2], gv[3]);
+            dg[1] = make_uint4(gv[4], gv[5], gv[6], gv[7]);
+            uint4* du = reinterpret_cast<uint4*>(p.up_out + off);
+            du[0] = make_uint4(uv[0], uv[1], uv[2], uv[3]);
+            du[1] = make_uint4(uv[4], uv[5], uv[6], uv[7]);
+          }
+        }
+      }
+    }
+  }
+
+  // Teardown.  After a failed wait, give copies that are still in flight time to land in this
+  // CTA's shared memory before it is handed to another CTA.
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (*reinterpret_cast<volatile int*>(p.status) != 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------ host
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+  static std::once_flag once;
+  static EncodeTiled fn = nullptr;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(sym);
+  });
+  return fn;
+}
+
+// [rows, k] bf16 row-major matrix, boxes of 128 rows x 64 K elements, 128-byte swizzle, zero fill
+// outside the matrix.
+bool make_map(CUtensorMap* map, const void* base, long long rows, long long k) {
+  EncodeTiled enc = encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+  cuuint32_t box[2] = {BK, BM};
+  cuuint32_t elem[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+std::atomic<uint64_t> g_gemm_launches{0};
+
+}  // namespace
+
+extern "C" {
+
+uint64_t swiglu_b200_gemm_launch_count(void) { return g_gemm_launches.load(std::memory_order_relaxed); }
+
+int swiglu_b200_gemm_fwd(void* h, void* gate_out, void* up_out, const void* x, const void* w_gate, const void* w_up,
+                         int64_t m, int64_t n, int64_t k, float gm, float dm, void* status, int device, void* stream) {
+  if (m < 0 || n < 0 || k < 0) return SWIGLU_B200_ERR_SHAPE;
+  if (m == 0 || n == 0) return SWIGLU_B200_OK;
+  // 16-byte global strides for the tiled copies and 32-byte output groups
+  if (k == 0 || k % 8 != 0 || n % 16 != 0) return SWIGLU_B200_ERR_SHAPE;
+  if (m > 0x7fffff00LL || n > 0x7fffff00LL || k > 0x7fffff00LL) return SWIGLU_B200_ERR_SHAPE;
+  if (!h || !x || !w_gate || !w_up || !status) return SWIGLU_B200_ERR_NULL;
+  if ((gate_out == nullptr) != (up_out == nullptr)) return SWIGLU_B200_ERR_NULL;
+  if (((uintptr_t)h | (uintptr_t)x | (uintptr_t)w_gate | (uintptr_t)w_up | (uintptr_t)gate_out | (uintptr_t)up_out) % 16)
+    return SWIGLU_B200_ERR_ALIGN;
+  if ((uintptr_t)status % 4) return SWIGLU_B200_ERR_ALIGN;
+
+  int prev = -1;
+  bool switched = false;
+  if (device >= 0) {
+    if (cudaGetDevice(&prev) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
+    if (prev != device) {
+      if (cudaSetDevice(device) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
+      switched = true;
+    }
+  }
+  struct Restore {
+    bool on;
+    int dev;
+    ~Restore() {
+      if (on) cudaSetDevice(dev);
+    }
+  } restore{switched, prev};
+
+  CUtensorMap map_x, map_wg, map_wu;
+  if (!make_map(&map_x, x, m, k) || !make_map(&map_wg, w_gate, n, k) || !make_map(&map_wu, w_up, n, k))
+    return SWIGLU_B200_ERR_DEVICE;
+
+  static std::atomic<bool> attr_set[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
+  if (dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
+    if (cudaFuncSetAttribute(swiglu_gemm_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
+        cudaSuccess)
+      return SWIGLU_B200_ERR_DEVICE;
+    if (dev < 64) attr_set[dev].store(true, std::memory_order_release);
+  }
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
+  GemmParams p{static_cast<__nv_bfloat16*>(h), static_cast<__nv_bfloat16*>(gate_out), static_cast<__nv_bfloat16*>(up_out),
+               static_cast<int*>(status), m, n, k, gm, dm};
+  const long long tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+  if (tiles > 0x7fffffffLL) return SWIGLU_B200_ERR_SHAPE;
+  swiglu_gemm_fwd_kernel<<<(unsigned)tiles, THREADS, SMEM_BYTES, st>>>(map_x, map_wg, map_wu, p);
+  if (cudaGetLastError() != cudaSuccess) return SWIGLU_B200_ERR_LAUNCH;
+  g_gemm_launches.fetch_add(1, std::memory_order_relaxed);
+  return SWIGLU_B200_OK;
+}
+
+}  // extern "C"

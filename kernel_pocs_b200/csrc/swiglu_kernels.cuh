@@ -16,8 +16,9 @@
 // R rounds once, to nearest even, into T.  For fp32 I/O the operation order follows the
 // ATen composite the reference tests compare with (swiglu.py:179-188 and the autograd
 // graph it builds), exp and the division are the accurate ones; for bf16/fp16 I/O the
-// exponential is ex2.approx and the reciprocal rcp.approx, whose error (~1e-6 relative)
-// is far below half an ulp of a 16-bit result.
+// exponential is ex2.approx and the reciprocal rcp.approx, the multipliers are folded into
+// per-launch constants, and the error (~1e-6 relative) is far below half an ulp of a 16-bit
+// result.
 //
 // Memory: every kernel is a pure stream.  Algorithmic traffic per element of size s is
 // 3*s bytes forward (read gate, up; write h) and 5*s backward (read dh, gate, up; write
@@ -246,52 +247,54 @@ template <> struct Codec<__half> {
 
 template <bool FAST> struct Math;
 
+// Per-launch constants derived from the two multipliers, computed once per thread.
+struct Consts {
+  float gm, dm;
+  float neg_gm_log2e;   // -gm * log2(e):       exp(-z) = ex2(gate * neg_gm_log2e)
+  float gm_dm_quarter;  //  gm * dm / 4
+  float gm_dm;          //  gm * dm
+  __device__ __forceinline__ Consts(float gm_, float dm_)
+      : gm(gm_), dm(dm_), neg_gm_log2e(gm_ * -1.4426950408889634f), gm_dm_quarter(gm_ * dm_ * 0.25f),
+        gm_dm(gm_ * dm_) {}
+};
+
 template <> struct Math<true> {
-  static __device__ __forceinline__ float fwd(float g, float u, float gm, float dm) {
-    float z = g * gm;
+  // sigmoid(z)/... via r = 1 / ((1 + exp(-z)) / 4).  Dividing the denominator by four (folded into
+  // one FMA) keeps r a normal number for every finite exp(-z) <= 2^128, so the flush-to-zero
+  // reciprocal loses nothing; the factor 1/4 is multiplied back where it is exact.
+  static __device__ __forceinline__ float quarter_recip(float g, const Consts& c) {
     float e, r;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
-#ifdef SWIGLU_RCP_FTZ
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
-#else
-    asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));  // no .ftz: for z < -87.3 the reciprocal is subnormal
-#endif
-    return (z * r) * u * dm;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * c.neg_gm_log2e));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(fmaf(e, 0.25f, 0.25f)));
+    return r;  // 4 * sigmoid(g * gm)
   }
-  static __device__ __forceinline__ void bwd(float dh, float g, float u, float gm, float dm, float& dgate,
-                                             float& dup) {
-    float z = g * gm;
-    float e, sig;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
-#ifdef SWIGLU_RCP_FTZ
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(sig) : "f"(1.0f + e));
-#else
-    asm("rcp.approx.f32 %0, %1;" : "=f"(sig) : "f"(1.0f + e));
-#endif
-    float d = dh * dm;
-    float silu = z * sig;
-    dup = d * silu;
-    dgate = (d * u) * (sig * (1.0f + z * (1.0f - sig))) * gm;
+  static __device__ __forceinline__ float fwd(float g, float u, const Consts& c) {
+    return ((g * c.gm_dm_quarter) * quarter_recip(g, c)) * u;
+  }
+  static __device__ __forceinline__ void bwd(float dh, float g, float u, const Consts& c, float& dgate, float& dup) {
+    const float sig = quarter_recip(g, c) * 0.25f;
+    const float z = g * c.gm;
+    dup = (dh * c.dm) * (z * sig);
+    dgate = ((dh * c.gm_dm) * u) * (sig * fmaf(z, 1.0f - sig, 1.0f));
   }
 };
 
 template <> struct Math<false> {
   // Same expression tree as ATen's silu / silu_backward, which is what the reference's
   // torch_swiglu_reference (swiglu.py:179-188) evaluates under autograd.
-  static __device__ __forceinline__ float fwd(float g, float u, float gm, float dm) {
-    float z = g * gm;
+  static __device__ __forceinline__ float fwd(float g, float u, const Consts& c) {
+    float z = g * c.gm;
     float silu = z / (1.0f + expf(-z));
-    return (silu * u) * dm;
+    return (silu * u) * c.dm;
   }
-  static __device__ __forceinline__ void bwd(float dh, float g, float u, float gm, float dm, float& dgate,
-                                             float& dup) {
-    float z = g * gm;
+  static __device__ __forceinline__ void bwd(float dh, float g, float u, const Consts& c, float& dgate, float& dup) {
+    float z = g * c.gm;
     float den = 1.0f + expf(-z);
     float sig = 1.0f / den;
     float silu = z / den;
-    float d = dh * dm;
+    float d = dh * c.dm;
     dup = d * silu;
-    dgate = (((d * u) * sig) * (1.0f + z * (1.0f - sig))) * gm;
+    dgate = (((d * u) * sig) * (1.0f + z * (1.0f - sig))) * c.gm;
   }
 };
 
@@ -357,6 +360,7 @@ swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const v
   constexpr int EPV = BYTES / Codec<T>::kSize;
   constexpr long long TILE = (long long)THREADS * UNROLL;
   const long long n_tiles = (s.n_vec + TILE - 1) / TILE;
+  const Consts c(gm, dm);
 
   for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
     const long long v0 = tile * TILE + threadIdx.x;
@@ -381,7 +385,7 @@ swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const v
         Codec<T>::template unpack<BYTES>(g[k], fg);
         Codec<T>::template unpack<BYTES>(u[k], fu);
 #pragma unroll
-        for (int e = 0; e < EPV; ++e) fh[e] = Math<FAST>::fwd(fg[e], fu[e], gm, dm);
+        for (int e = 0; e < EPV; ++e) fh[e] = Math<FAST>::fwd(fg[e], fu[e], c);
         Vec<BYTES> h;
         Codec<T>::template pack<BYTES>(fh, h);
         St<BYTES, STM>::st(byte(out) + oo[k], h);
@@ -403,7 +407,7 @@ swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const v
       float fg[1], fu[1], fh[1];
       Codec<T>::template unpack<ES>(vg, fg);
       Codec<T>::template unpack<ES>(vu, fu);
-      fh[0] = Math<FAST>::fwd(fg[0], fu[0], gm, dm);
+      fh[0] = Math<FAST>::fwd(fg[0], fu[0], c);
       Vec<ES> vh;
       Codec<T>::template pack<ES>(fh, vh);
       St<ES, ST_PLAIN>::st(byte(out) + off, vh);
@@ -423,6 +427,7 @@ swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const v
   constexpr int EPV = BYTES / Codec<T>::kSize;
   constexpr long long TILE = (long long)THREADS * UNROLL;
   const long long n_tiles = (s.n_vec + TILE - 1) / TILE;
+  const Consts c(gm, dm);
 
   for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
     const long long v0 = tile * TILE + threadIdx.x;
@@ -451,7 +456,7 @@ swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const v
         Codec<T>::template unpack<BYTES>(g[k], fg);
         Codec<T>::template unpack<BYTES>(u[k], fu);
 #pragma unroll
-        for (int e = 0; e < EPV; ++e) Math<FAST>::bwd(fd[e], fg[e], fu[e], gm, dm, fdg[e], fdu[e]);
+        for (int e = 0; e < EPV; ++e) Math<FAST>::bwd(fd[e], fg[e], fu[e], c, fdg[e], fdu[e]);
         Vec<BYTES> vdg, vdu;
         Codec<T>::template pack<BYTES>(fdg, vdg);
         Codec<T>::template pack<BYTES>(fdu, vdu);
@@ -474,7 +479,7 @@ swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const v
       Codec<T>::template unpack<ES>(vd, fd);
       Codec<T>::template unpack<ES>(vg, fg);
       Codec<T>::template unpack<ES>(vu, fu);
-      Math<FAST>::bwd(fd[0], fg[0], fu[0], gm, dm, fdg[0], fdu[0]);
+      Math<FAST>::bwd(fd[0], fg[0], fu[0], c, fdg[0], fdu[0]);
       Vec<ES> vdg, vdu;
       Codec<T>::template pack<ES>(fdg, vdg);
       Codec<T>::template pack<ES>(fdu, vdu);

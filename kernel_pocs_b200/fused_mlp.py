@@ -1,0 +1,112 @@
+"""Fused gate/up projection + SwiGLU: ``h = silu((x @ w_gate.T) * gm) * (x @ w_up.T) * dm`` in ONE
+tcgen05 kernel (``swiglu_b200_gemm_fwd`` in the C ABI), bf16 in, fp32 accumulation, bf16 out.
+
+This is the step in front of the activation path in the reference's patched MLP
+(forge/forge/patching/kernels/basic.py:97-102 computes ``swiglu(gate_proj(x), up_proj(x))`` with two
+cuBLAS GEMMs and one activation kernel); fusing it removes the write and re-read of both
+pre-activation matrices.  The backward is composed from this library's SwiGLU backward kernel and
+PyTorch matmuls (cuBLAS): dgate/dup from (dh, gate, up), then dx, dw_gate, dw_up.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .swiglu import _as_float, swiglu_backward
+
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def _status(device: torch.device) -> torch.Tensor:
+    t = _status_words.get(device.index)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[device.index] = t
+    return t
+
+
+def check_status(device: torch.device | int | None = None) -> None:
+    """Synchronises ``device`` and raises if the last fused-GEMM launch on it gave up on an
+    internal wait (the kernel bounds every wait and reports instead of hanging)."""
+    dev = torch.device("cuda", torch.cuda.current_device() if device is None else torch.device(device).index or 0) \
+        if not isinstance(device, torch.device) else device
+    word = _status_words.get(dev.index)
+    if word is None:
+        return
+    code = int(word.item())  # synchronises
+    if code != 0:
+        raise RuntimeError(f"swiglu_b200_gemm_fwd reported a timed-out wait (code {code}); its output is incomplete")
+
+
+def _check_operands(x, w_gate, w_up):
+    if not (x.is_cuda and w_gate.is_cuda and w_up.is_cuda):
+        raise RuntimeError("fused gate/up SwiGLU has a CUDA (sm_100a) kernel only; there is no CPU fallback")
+    if not (x.dtype == w_gate.dtype == w_up.dtype == torch.bfloat16):
+        raise TypeError("fused gate/up SwiGLU supports bf16 operands only")
+    if w_gate.shape != w_up.shape or w_gate.dim() != 2:
+        raise ValueError(f"w_gate and w_up must be [n, k] matrices of one shape, got {w_gate.shape} and {w_up.shape}")
+    if x.shape[-1] != w_gate.shape[1]:
+        raise ValueError(f"x has {x.shape[-1]} features, the weights expect {w_gate.shape[1]}")
+    if w_gate.shape[1] % 8 or w_gate.shape[0] % 16:
+        raise ValueError("the fused kernel needs k % 8 == 0 and n % 16 == 0")
+
+
+def gate_up_swiglu_forward(x, w_gate, w_up, gate_multiplier=1.0, down_multiplier=1.0, save_preactivations=False):
+    """Returns ``h`` or, with ``save_preactivations``, ``(h, gate, up)`` (gate/up rounded to bf16)."""
+    _check_operands(x, w_gate, w_up)
+    gm = _as_float("gate_multiplier", gate_multiplier)
+    dm = _as_float("down_multiplier", down_multiplier)
+    n, k = w_gate.shape
+    x2 = x.contiguous().view(-1, k)
+    wg, wu = w_gate.contiguous(), w_up.contiguous()
+    m = x2.shape[0]
+    h = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    gate = torch.empty_like(h) if save_preactivations else None
+    up = torch.empty_like(h) if save_preactivations else None
+    _lib.check(
+        "gate_up_swiglu_forward",
+        _lib.lib.swiglu_b200_gemm_fwd(
+            h.data_ptr(), gate.data_ptr() if save_preactivations else None,
+            up.data_ptr() if save_preactivations else None, x2.data_ptr(), wg.data_ptr(), wu.data_ptr(),
+            m, n, k, gm, dm, _status(x.device).data_ptr(), x.device.index,
+            torch.cuda.current_stream(x.device).cuda_stream,
+        ),
+    )
+    h = h.view(*x.shape[:-1], n)
+    if save_preactivations:
+        return h, gate, up
+    return h
+
+
+class FusedGateUpSwiGLUFunction(torch.autograd.Function):
+    """``apply(x, w_gate, w_up, gate_multiplier=1.0, down_multiplier=1.0)``."""
+
+    @staticmethod
+    def forward(ctx, x, w_gate, w_up, gate_multiplier=1.0, down_multiplier=1.0):
+        h, gate, up = gate_up_swiglu_forward(x, w_gate, w_up, gate_multiplier, down_multiplier, True)
+        ctx.save_for_backward(x, w_gate, w_up, gate, up)
+        ctx.gate_multiplier = _as_float("gate_multiplier", gate_multiplier)
+        ctx.down_multiplier = _as_float("down_multiplier", down_multiplier)
+        return h
+
+    @staticmethod
+    def backward(ctx, dh):
+        x, w_gate, w_up, gate, up = ctx.saved_tensors
+        n, k = w_gate.shape
+        # gate/up are private to this node, so the in-place backward is safe
+        dgate, dup = swiglu_backward(dh.reshape(-1, n), gate, up, ctx.gate_multiplier, ctx.down_multiplier, False)
+        x2 = x.reshape(-1, k)
+        dx = dw_gate = dw_up = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.addmm(dgate @ w_gate, dup, w_up).view(x.shape)
+        if ctx.needs_input_grad[1]:
+            dw_gate = dgate.t() @ x2
+        if ctx.needs_input_grad[2]:
+            dw_up = dup.t() @ x2
+        return dx, dw_gate, dw_up, None, None
+
+
+def fused_gate_up_swiglu(x, w_gate, w_up, gate_multiplier=1.0, down_multiplier=1.0):
+    """``silu((x @ w_gate.T) * gm) * (x @ w_up.T) * dm`` with autograd support."""
+    _check_operands(x, w_gate, w_up)
+    return FusedGateUpSwiGLUFunction.apply(x, w_gate, w_up, gate_multiplier, down_multiplier)

@@ -182,7 +182,7 @@ def ordinal(x: torch.Tensor) -> torch.Tensor:
 def ulp_distance(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """Elementwise ulp distance; positions where both are NaN count 0, where only one is NaN
     count a large number."""
-    a, b = a.cpu(), b.cpu()
+    a, b = a.detach().cpu().contiguous(), b.detach().cpu().contiguous()
     dist = (ordinal(a) - ordinal(b)).abs()
     an, bn = torch.isnan(a), torch.isnan(b)
     dist = torch.where(an & bn, torch.zeros_like(dist), dist)

@@ -28,8 +28,8 @@ def assert_rounded_once(got: torch.Tensor, truth: torch.Tensor, what: str, slack
     optional absolute allowance ``extra`` per element (dgate: the fp32 evaluation error scales
     with |dh*up|, not with the result, where the derivative factor crosses zero)."""
     dtype = got.dtype
-    g = got.detach().cpu().double().view(-1)
-    t = truth.detach().cpu().double().view(-1)
+    g = got.detach().cpu().double().reshape(-1)
+    t = truth.detach().cpu().double().reshape(-1)
     finite = torch.isfinite(t) & (t.abs() < MAX_FINITE[dtype])
     assert torch.equal(torch.isnan(g), torch.isnan(t)), f"{what}: NaN pattern differs"
     err = (g - t).abs()[finite]
@@ -37,7 +37,7 @@ def assert_rounded_once(got: torch.Tensor, truth: torch.Tensor, what: str, slack
     # truth of magnitude < 1e-36
     bound = slack * ulp_spacing(t[finite], dtype) + 1e-30
     if extra is not None:
-        bound = bound + extra.detach().cpu().double().view(-1)[finite]
+        bound = bound + extra.detach().cpu().double().reshape(-1)[finite]
     bad = err > bound
     assert not bad.any(), (
         f"{what}: {int(bad.sum())} of {bad.numel()} elements are not within {slack} ulp of the exact value; "
@@ -57,15 +57,15 @@ def assert_ulp(got: torch.Tensor, want: torch.Tensor, max_ulp: int, what: str, m
 def assert_rel_scaled(got: torch.Tensor, truth: torch.Tensor, rel: float, what: str, scale: torch.Tensor | None = None,
                       floor: float = 1e-25) -> None:
     """|got - truth| <= rel * max(|truth|, scale, floor), NaN/inf patterns equal."""
-    g = got.detach().cpu().double().view(-1)
-    t = truth.detach().cpu().double().view(-1)
+    g = got.detach().cpu().double().reshape(-1)
+    t = truth.detach().cpu().double().reshape(-1)
     assert torch.equal(torch.isnan(g), torch.isnan(t)), f"{what}: NaN pattern differs"
     inf = torch.isinf(t)
     assert torch.equal(g[inf], t[inf]), f"{what}: infinities differ"
     ok = torch.isfinite(t) & (t.abs() < 3.0e38)
     denom = t.abs()
     if scale is not None:
-        denom = torch.maximum(denom, scale.detach().cpu().double().view(-1))
+        denom = torch.maximum(denom, scale.detach().cpu().double().reshape(-1))
     denom = denom.clamp_min(floor)
     ratio = ((g - t).abs() / denom)[ok]
     worst = float(ratio.max()) if ratio.numel() else 0.0
