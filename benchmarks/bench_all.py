@@ -192,6 +192,75 @@ def run_case(name, args, device, rank, world):
     return out_rows
 
 
+C4 = {"m": 16384, "n": 14336, "k": 4096, "seed": 3}
+FALLBACK_BF16_TFLOPS = 1590.0
+
+
+def tensor_peak():
+    try:
+        d = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+        return float(d["bf16_tflops"]), float(d["bf16_tflops_sustained"]), "measured"
+    except Exception:
+        return FALLBACK_BF16_TFLOPS, 1400.0, "fallback"
+
+
+def run_c4(args, device):
+    """Fused gate/up projection + SwiGLU (BASELINE configuration 4): X [16384, 4096] ~ N(0,1),
+    W_gate, W_up [14336, 4096] ~ N(0, 0.02^2), bf16, seed 3; dh ~ N(0,1) for the backward.
+    FLOPs: forward 4*M*N*K (two GEMMs), backward 8*M*N*K (dX: two GEMMs, dW_gate, dW_up)."""
+    from kernel_pocs_b200.fused_mlp import check_status, fused_gate_up_swiglu, gate_up_swiglu_forward
+    from kernels.swiglu import swiglu, swiglu_forward
+
+    m = min(C4["m"], args.max_rows) if args.max_rows else C4["m"]
+    n, k = C4["n"], C4["k"]
+    g = torch.Generator(device=device).manual_seed(C4["seed"])
+    x = torch.randn(m, k, generator=g, device=device).bfloat16()
+    wg = (0.02 * torch.randn(n, k, generator=g, device=device)).bfloat16()
+    wu = (0.02 * torch.randn(n, k, generator=g, device=device)).bfloat16()
+    dh = torch.randn(m, n, generator=g, device=device).bfloat16()
+    flops = {"forward": 4.0 * m * n * k, "full": 12.0 * m * n * k}
+    xg, wgg, wug = (t.clone().requires_grad_(True) for t in (x, wg, wu))
+
+    def fused_fwd():
+        gate_up_swiglu_forward(x, wg, wu)
+
+    def fused_full():
+        h = fused_gate_up_swiglu(xg, wgg, wug)
+        torch.autograd.grad(h, (xg, wgg, wug), dh)
+
+    def unfused_fwd():
+        swiglu_forward(x @ wg.t(), x @ wu.t())
+
+    def unfused_full():
+        h = swiglu(xg @ wgg.t(), xg @ wug.t())
+        torch.autograd.grad(h, (xg, wgg, wug), dh)
+
+    def cublas_fwd():
+        x @ wg.t()
+        x @ wu.t()
+
+    burst, sustained, kind = tensor_peak()
+    rows = []
+    for provider, fns in (("b200-fused-gemm", {"forward": fused_fwd, "full": fused_full}),
+                          ("cublas+b200-swiglu", {"forward": unfused_fwd, "full": unfused_full}),
+                          ("cublas-2gemm-only", {"forward": cublas_fwd})):
+        for mode, fn in fns.items():
+            if mode not in args.modes:
+                continue
+            mean, med, best = time_cuda(fn, lambda: None, args.warmup, args.rep)
+            check_status(device)
+            r = {"config": "c4", "provider": provider, "mode": mode, "dtype": "bfloat16", "m": m, "n": n, "k": k,
+                 "ms_mean_trimmed": mean, "ms_median": med, "ms_min": best, "flops": flops[mode],
+                 "tflops": flops[mode] / (mean * 1e-3) / 1e12,
+                 "frac_of_measured_bf16_burst": flops[mode] / (mean * 1e-3) / 1e12 / burst,
+                 "tokens_per_s": m / (mean * 1e-3)}
+            rows.append(r)
+            print(f"{'c4':>16} {provider:>18} {mode:>8} bf16 M{m} N{n} K{k} {mean:9.4f} ms  {r['tflops']:8.1f} TFLOP/s  "
+                  f"{100 * r['frac_of_measured_bf16_burst']:5.1f}% of {kind} cuBLAS burst {burst:.0f} "
+                  f"({100 * r['tflops'] / 2250:4.1f}% of nominal 2250)  {r['tokens_per_s'] / 1e6:8.3f} Mtok/s", flush=True)
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--configs", nargs="+", default=["c1", "c2", "c3", "c3-fp32", "c3+w11009", "c3+w11009-off1"])
@@ -222,6 +291,10 @@ def main():
     peak, kind = hbm_peak()
     rows = []
     for name in args.configs:
+        if name == "c4":
+            if world == 1:
+                rows.extend(run_c4(args, device))
+            continue
         for r in run_case(name, args, device, rank, world):
             r["frac_of_measured_copy"] = r["gbs_per_gpu"] / peak
             r["frac_of_nominal_8TBs"] = r["gbs_per_gpu"] / NOMINAL_HBM_GBS
