@@ -27,6 +27,8 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "swiglu_kernels.cuh"
@@ -258,6 +260,271 @@ swiglu_gemm_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Second kernel: CTA pairs (cta_group::2), persistent, double-buffered accumulators.
+//
+// A cluster of two CTAs computes a 256 x 128 tile of h.  Each CTA loads its own 128 rows of X and
+// ONE of the two weight tiles (rank 0: Wg, rank 1: Wu); the leader's tcgen05.mma.cta_group::2
+// (M=256, N=256, K=16) reads X rows from both CTAs' shared memory and treats the two weight tiles
+// as the two halves of its N dimension, so each CTA's TMEM again holds gate in columns [0,128) and
+// up in [128,256) for its 128 rows.  Per K block a CTA now pulls 32 KiB through L2 instead of
+// 48 KiB.  Clusters walk the tiles persistently; TMEM holds two accumulator buffers so the
+// epilogue of one tile overlaps the MMAs of the next.  Tiles are visited in bands of 8 row-tiles
+// so that the X band and the weight tiles in flight stay in L2.
+namespace pair {
+
+constexpr int STAGES = 6;
+constexpr int STAGE_BYTES = 2 * TILE_BYTES;              // X tile + one weight tile
+constexpr int ACC_BUFS = 2;
+constexpr int TMEM_COLS = 512;
+constexpr int BAND = 8;                                  // row-tiles (of 256 rows) per band
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
+
+__device__ __forceinline__ uint32_t cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive (optionally announcing transaction bytes) on a barrier given by its cluster-window address
+__device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// No cluster-scope release here: the producer has written nothing the leader must see, and a
+// cluster-scope release per K block stalled the producer thread.
+__device__ __forceinline__ void remote_expect_tx(uint32_t cluster_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool try_wait_cluster(uint64_t* b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
+  return ok != 0;
+}
+template <bool CLUSTER_SCOPE>
+__device__ __forceinline__ bool wait(uint64_t* b, uint32_t parity, int* status, int code) {
+  auto poll = [&] { return CLUSTER_SCOPE ? try_wait_cluster(b, parity) : mbar_try_wait(b, parity); };
+  if (poll()) return true;
+  const long long t0 = clock64();
+  for (int spin = 0;; ++spin) {
+    if (poll()) return true;
+    if ((spin & 63) == 63) {
+      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (clock64() - t0 > WAIT_CYCLES) {
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+// tiled load whose completion bytes are credited to a barrier of the pair's leader CTA
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(leader_bar) : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+  asm volatile(
+      "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p; }"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(IDESC), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at this shared-memory offset in BOTH CTAs once the MMAs issued so far are done
+__device__ __forceinline__ void commit_both(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+}
+
+struct TileWalk {
+  long long tiles_m, tiles_n, total;
+  __device__ __forceinline__ TileWalk(long long m, long long n)
+      : tiles_m((m + 2 * BM - 1) / (2 * BM)), tiles_n((n + BN - 1) / BN), total(tiles_m * tiles_n) {}
+  __device__ __forceinline__ void at(long long t, int& m0, int& n0) const {
+    const long long per_band = (long long)BAND * tiles_n;
+    const long long band = t / per_band;
+    const long long r = t - band * per_band;
+    const long long rows_in_band = (tiles_m - band * BAND) < BAND ? (tiles_m - band * BAND) : BAND;
+    const long long tn = r / rows_in_band;
+    const long long tm = band * BAND + (r - tn * rows_in_band);
+    m0 = (int)(tm * 2 * BM);
+    n0 = (int)(tn * BN);
+  }
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+swiglu_gemm_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wg,
+                            const __grid_constant__ CUtensorMap map_wu, const GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);  // used in the leader only
+  uint64_t* empty = full + STAGES;                                            // one copy per CTA
+  uint64_t* acc_full = empty + STAGES;                                        // one copy per CTA
+  uint64_t* acc_empty = acc_full + ACC_BUFS;                                  // used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cta_rank();
+  const long long pair_id = blockIdx.x >> 1;
+  const long long n_pairs = gridDim.x >> 1;
+  const TileWalk walk(p.m, p.n);
+  const int k_blocks = (int)((p.k + BK - 1) / BK);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 2);    // one expect_tx arrival from each CTA's producer
+      mbar_init(&empty[s], 1);   // the leader's commit
+    }
+    for (int b = 0; b < ACC_BUFS; ++b) {
+      mbar_init(&acc_full[b], 1);   // the leader's commit
+      mbar_init(&acc_empty[b], 8);  // four epilogue warps in each CTA
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync();  // both CTAs' barriers exist before anyone arrives on them remotely
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const CUtensorMap* map_w = rank == 0 ? &map_wg : &map_wu;
+      long long it = 0;
+      bool ok = true;
+      for (long long t = pair_id; t < walk.total && ok; t += n_pairs) {
+        int m0, n0;
+        walk.at(t, m0, n0);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = (int)(it % STAGES);
+          if (it >= STAGES) {
+            ok = wait<false>(&empty[s], (uint32_t)((it / STAGES - 1) & 1), p.status, 100 + s);
+            if (!ok) break;
+          }
+          const uint32_t leader_full = map_to_rank(smem_u32(&full[s]), 0);
+          remote_expect_tx(leader_full, STAGE_BYTES);
+          unsigned char* stage = smem + s * STAGE_BYTES;
+          tma_load_2d_pair(stage, &map_x, kb * BK, m0 + (int)rank * BM, leader_full);
+          tma_load_2d_pair(stage + TILE_BYTES, map_w, kb * BK, n0, leader_full);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      long long it = 0, i = 0;
+      bool ok = true;
+      for (long long t = pair_id; t < walk.total && ok; t += n_pairs, ++i) {
+        const int b = (int)(i & 1);
+        if (i >= ACC_BUFS) {
+          ok = wait<true>(&acc_empty[b], (uint32_t)(((i >> 1) - 1) & 1), p.status, 400 + b);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        const uint32_t tmem_d = tmem_base + (uint32_t)b * 256u;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = (int)(it % STAGES);
+          ok = wait<false>(&full[s], (uint32_t)((it / STAGES) & 1), p.status, 200 + s);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t a_desc = umma_desc(a_addr);
+          const uint64_t b_desc = umma_desc(a_addr + TILE_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) umma_pair(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, (kb | kk) != 0);
+          commit_both(&empty[s]);
+        }
+        if (ok) commit_both(&acc_full[b]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const Consts cst(p.gm, p.dm);
+    long long i = 0;
+    bool ok = true;
+    for (long long t = pair_id; t < walk.total && ok; t += n_pairs, ++i) {
+      int m0, n0;
+      walk.at(t, m0, n0);
+      const int b = (int)(i & 1);
+      ok = wait<false>(&acc_full[b], (uint32_t)((i >> 1) & 1), p.status, 300 + b);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int row = m0 + (int)rank * BM + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)b * 256u;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        uint32_t g[16], u[16];
+        tmem_ld16(t_row + c, g);
+        tmem_ld16(t_row + BN + c, u);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < p.m && n0 + c < p.n) {
+          uint32_t hv[8], gv[8], uv[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+            const float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+            __nv_bfloat162 hb = __floats2bfloat162_rn(Math<true>::fwd(g0, u0, cst), Math<true>::fwd(g1, u1, cst));
+            __nv_bfloat162 gb = __floats2bfloat162_rn(g0, g1);
+            __nv_bfloat162 ub = __floats2bfloat162_rn(u0, u1);
+            hv[j] = *reinterpret_cast<uint32_t*>(&hb);
+            gv[j] = *reinterpret_cast<uint32_t*>(&gb);
+            uv[j] = *reinterpret_cast<uint32_t*>(&ub);
+          }
+          const long long off = (long long)row * p.n + n0 + c;
+          uint4* dst = reinterpret_cast<uint4*>(p.h + off);
+          dst[0] = make_uint4(hv[0], hv[1], hv[2], hv[3]);
+          dst[1] = make_uint4(hv[4], hv[5], hv[6], hv[7]);
+          if (p.gate_out) {
+            uint4* dg = reinterpret_cast<uint4*>(p.gate_out + off);
+            dg[0] = make_uint4(gv[0], gv[1], gv[2], gv[3]);
+            dg[1] = make_uint4(gv[4], gv[5], gv[6], gv[7]);
+            uint4* du = reinterpret_cast<uint4*>(p.up_out + off);
+            du[0] = make_uint4(uv[0], uv[1], uv[2], uv[3]);
+            du[1] = make_uint4(uv[4], uv[5], uv[6], uv[7]);
+          }
+        }
+      }
+      // this warp has drained its quarter of accumulator buffer b: tell the leader's MMA thread
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) remote_arrive(map_to_rank(smem_u32(&acc_empty[b]), 0));
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (*reinterpret_cast<volatile int*>(p.status) != 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {
+    }
+    __syncthreads();
+  }
+  cluster_sync();  // the peer's shared memory and TMEM stay alive until the leader's MMAs are done
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+}  // namespace pair
+
 // ------------------------------------------------------------------------------------------ host
 
 using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -292,6 +559,54 @@ bool make_map(CUtensorMap* map, const void* base, long long rows, long long k) {
 }
 
 std::atomic<uint64_t> g_gemm_launches{0};
+
+// SWIGLU_B200_GEMM=single selects the one-CTA-per-tile kernel; the CTA-pair kernel is the default.
+bool use_pair_kernel() {
+  static const bool pair_default = [] {
+    const char* v = getenv("SWIGLU_B200_GEMM");
+    return !(v && v[0] == 's');
+  }();
+  return pair_default;
+}
+
+// Number of 2-CTA clusters of the pair kernel that can be resident at once on `dev` (cached).
+int pair_clusters(int dev, int* out) {
+  static std::atomic<int> cache[64];
+  if (dev < 64) {
+    const int c = cache[dev].load(std::memory_order_acquire);
+    if (c > 0) {
+      *out = c;
+      return SWIGLU_B200_OK;
+    }
+  }
+  if (cudaFuncSetAttribute(pair::swiglu_gemm_fwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           pair::SMEM_BYTES) != cudaSuccess)
+    return SWIGLU_B200_ERR_DEVICE;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * 148, 1, 1);
+  cfg.blockDim = dim3(THREADS, 1, 1);
+  cfg.dynamicSmemBytes = pair::SMEM_BYTES;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, pair::swiglu_gemm_fwd_pair_kernel, &cfg) != cudaSuccess || n < 1)
+    return SWIGLU_B200_ERR_DEVICE;
+  if (const char* dbg = getenv("SWIGLU_B200_DEBUG")) {
+    if (dbg[0] == '1') fprintf(stderr, "swiglu_b200: %d resident 2-CTA clusters on device %d\n", n, dev);
+  }
+  if (const char* force = getenv("SWIGLU_B200_GEMM_CLUSTERS")) {  // experiments only
+    const int f = atoi(force);
+    if (f > 0) n = f;
+  }
+  if (dev < 64) cache[dev].store(n, std::memory_order_release);
+  *out = n;
+  return SWIGLU_B200_OK;
+}
 
 }  // namespace
 
@@ -345,6 +660,19 @@ int swiglu_b200_gemm_fwd(void* h, void* gate_out, void* up_out, const void* x, c
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
+  if (use_pair_kernel()) {
+    int clusters = 0;
+    const int rc = pair_clusters(dev, &clusters);
+    if (rc != SWIGLU_B200_OK) return rc;
+    GemmParams pp{static_cast<__nv_bfloat16*>(h), static_cast<__nv_bfloat16*>(gate_out),
+                  static_cast<__nv_bfloat16*>(up_out), static_cast<int*>(status), m, n, k, gm, dm};
+    const long long pair_tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
+    const long long use = pair_tiles < clusters ? pair_tiles : clusters;
+    pair::swiglu_gemm_fwd_pair_kernel<<<(unsigned)(2 * use), THREADS, pair::SMEM_BYTES, st>>>(map_x, map_wg, map_wu, pp);
+    if (cudaGetLastError() != cudaSuccess) return SWIGLU_B200_ERR_LAUNCH;
+    g_gemm_launches.fetch_add(1, std::memory_order_relaxed);
+    return SWIGLU_B200_OK;
+  }
   GemmParams p{static_cast<__nv_bfloat16*>(h), static_cast<__nv_bfloat16*>(gate_out), static_cast<__nv_bfloat16*>(up_out),
                static_cast<int*>(status), m, n, k, gm, dm};
   const long long tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);

@@ -1,0 +1,140 @@
+"""Fused gate/up projection + SwiGLU epilogue (tcgen05 kernel) against a PyTorch fp32 reference.
+
+This is a floating-point contraction, so the comparator is plain PyTorch in fp32 on the same bf16
+operands: g = x @ w_gate.T, u = x @ w_up.T (fp32 accumulation, TF32 off), h = silu(g*gm) * u * dm.
+The kernel accumulates in fp32 in a different order and rounds once to bf16, so the bound is one
+bf16 rounding plus accumulation noise:  |h - ref| <= 2^-7 * |ref| + 2^-9 * rms(ref).
+The optional pre-activation outputs must be the bf16 rounding of g and u to the same bound, and the
+epilogue must agree with the CPU oracle applied to those pre-activations.
+"""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from kernel_pocs_b200 import _lib
+from kernel_pocs_b200 import fused_mlp as F
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+DEVICE = "cuda"
+
+
+def reference(x, wg, wu, gm=1.0, dm=1.0):
+    g = x.float() @ wg.float().t()
+    u = x.float() @ wu.float().t()
+    return torch.nn.functional.silu(g * gm) * u * dm, g, u
+
+
+def assert_close_bf16(got, ref, what):
+    ref = ref.float()
+    tol = 2.0 ** -7 * ref.abs() + 2.0 ** -9 * ref.pow(2).mean().sqrt()
+    err = (got.float() - ref).abs()
+    bad = err > tol
+    assert not bool(bad.any()), f"{what}: {int(bad.sum())} of {bad.numel()} outside tolerance, worst {float((err / tol).max()):.2f}x"
+
+
+def make(m, n, k, seed=3, w_std=0.05):
+    g = torch.Generator(device=DEVICE).manual_seed(seed)
+    x = torch.randn(m, k, generator=g, device=DEVICE).bfloat16()
+    wg = (w_std * torch.randn(n, k, generator=g, device=DEVICE)).bfloat16()
+    wu = (w_std * torch.randn(n, k, generator=g, device=DEVICE)).bfloat16()
+    return x, wg, wu
+
+
+@pytest.mark.parametrize("m,n,k", [
+    (128, 128, 64), (256, 128, 64), (1, 16, 8), (7, 48, 24), (200, 144, 72), (257, 272, 200),
+    (384, 1024, 512), (1000, 2064, 1032), (2048, 1408, 4096), (4500, 384, 256),
+])
+@pytest.mark.parametrize("gm,dm", [(1.0, 1.0), (0.7, 1.3)])
+def test_forward_matches_fp32_reference(m, n, k, gm, dm):
+    x, wg, wu = make(m, n, k)
+    before = _lib.lib.swiglu_b200_gemm_launch_count()
+    h, gate, up = F.gate_up_swiglu_forward(x, wg, wu, gm, dm, save_preactivations=True)
+    F.check_status(x.device)
+    assert _lib.lib.swiglu_b200_gemm_launch_count() == before + 1
+    ref_h, ref_g, ref_u = reference(x, wg, wu, gm, dm)
+    assert h.shape == (m, n) and h.dtype == torch.bfloat16
+    assert_close_bf16(gate, ref_g, "gate pre-activation")
+    assert_close_bf16(up, ref_u, "up pre-activation")
+    assert_close_bf16(h, ref_h, "h")
+    # the epilogue is the SwiGLU forward of the fp32 accumulators; from the bf16-rounded pre-activations the
+    # CPU oracle must land within 2 bf16 ulp of it almost everywhere (the kernel rounds h from unrounded g, u)
+    oh = O.fwd(gate.cpu(), up.cpu(), gm, dm, "once")
+    d = O.ulp_distance(h.cpu(), oh)
+    assert float((d > 4).double().mean()) < 0.02
+    # without the optional outputs the result is bit-identical
+    h2 = F.gate_up_swiglu_forward(x, wg, wu, gm, dm)
+    F.check_status(x.device)
+    assert torch.equal(h, h2)
+
+
+def test_leading_dimensions_and_errors():
+    x, wg, wu = make(6 * 20, 64, 32)
+    h = F.gate_up_swiglu_forward(x.view(6, 20, 32), wg, wu)
+    assert h.shape == (6, 20, 64)
+    with pytest.raises(ValueError, match="features"):
+        F.gate_up_swiglu_forward(x[:, :16].contiguous(), wg, wu)
+    with pytest.raises(ValueError, match="k % 8"):
+        F.gate_up_swiglu_forward(x[:, :20].contiguous(), wg[:, :20].contiguous(), wu[:, :20].contiguous())
+    with pytest.raises(TypeError, match="bf16"):
+        F.gate_up_swiglu_forward(x.float(), wg.float(), wu.float())
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        F.gate_up_swiglu_forward(x.cpu(), wg.cpu(), wu.cpu())
+    c = _lib.lib.swiglu_b200_gemm_fwd
+    p = h.data_ptr()
+    st = torch.zeros(1, dtype=torch.int32, device=DEVICE)
+    assert c(p, None, None, x.data_ptr(), wg.data_ptr(), wu.data_ptr(), 4, 64, 20, 1.0, 1.0, st.data_ptr(), 0, None) == 3
+    assert c(p, p, None, x.data_ptr(), wg.data_ptr(), wu.data_ptr(), 4, 64, 32, 1.0, 1.0, st.data_ptr(), 0, None) == 2
+    assert c(p, None, None, x.data_ptr(), wg.data_ptr(), wu.data_ptr(), 4, 64, 32, 1.0, 1.0, None, 0, None) == 2
+    assert c(p, None, None, x.data_ptr(), wg.data_ptr(), wu.data_ptr(), 0, 64, 32, 1.0, 1.0, st.data_ptr(), 0, None) == 0
+    F.check_status(x.device)
+
+
+def test_autograd_matches_reference():
+    m, n, k = 512, 768, 256
+    x, wg, wu = make(m, n, k, seed=9)
+    dh = torch.randn(m, n, device=DEVICE).bfloat16()
+    xs = [t.clone().requires_grad_(True) for t in (x, wg, wu)]
+    h = F.fused_gate_up_swiglu(*xs, 0.9, 1.1)
+    dx, dwg, dwu = torch.autograd.grad(h, xs, dh)
+    F.check_status(x.device)
+    rs = [t.float().clone().requires_grad_(True) for t in (x, wg, wu)]
+    g = rs[0] @ rs[1].t()
+    u = rs[0] @ rs[2].t()
+    rh = torch.nn.functional.silu(g * 0.9) * u * 1.1
+    rdx, rdwg, rdwu = torch.autograd.grad(rh, rs, dh.float())
+    assert_close_bf16(h, rh.detach(), "h")
+    # gradients go through bf16 dgate/dup and bf16 GEMMs: bound them by the spread of the reference
+    for got, ref, what in ((dx, rdx, "dx"), (dwg, rdwg, "dw_gate"), (dwu, rdwu, "dw_up")):
+        assert got.dtype == torch.bfloat16 and got.shape == ref.shape
+        err = (got.float() - ref).abs()
+        assert float(err.max()) <= 0.03 * float(ref.abs().max()), what
+        assert float(err.pow(2).mean().sqrt()) <= 0.01 * float(ref.pow(2).mean().sqrt()), what
+
+
+def test_single_cta_kernel_variant_agrees():
+    """The one-CTA-per-tile kernel (selected by SWIGLU_B200_GEMM=single at process start) must give the
+    same bits as the CTA-pair kernel: both accumulate each output over K in the same order."""
+    code = (
+        "import sys, torch; sys.path.insert(0, %r)\n"
+        "from kernel_pocs_b200 import fused_mlp as F\n"
+        "g = torch.Generator(device='cuda').manual_seed(3)\n"
+        "x = torch.randn(300, 200, generator=g, device='cuda').bfloat16()\n"
+        "wg = (0.05 * torch.randn(272, 200, generator=g, device='cuda')).bfloat16()\n"
+        "wu = (0.05 * torch.randn(272, 200, generator=g, device='cuda')).bfloat16()\n"
+        "h = F.gate_up_swiglu_forward(x, wg, wu, 0.7, 1.3); F.check_status(x.device)\n"
+        "torch.save(h.cpu(), sys.argv[1])\n" % str(ROOT)
+    )
+    outs = []
+    for variant in ("single", "pair"):
+        path = f"/tmp/swiglu_gemm_{variant}_{os.getpid()}.pt"
+        env = dict(os.environ, SWIGLU_B200_GEMM=variant)
+        subprocess.run([sys.executable, "-c", code, path], check=True, env=env, timeout=300)
+        outs.append(torch.load(path))
+        os.unlink(path)
+    assert torch.equal(outs[0], outs[1])
