@@ -130,6 +130,31 @@ SWIGLU_B200_API uint64_t swiglu_b200_host_workspace_bytes(int64_t rows, int64_t 
 SWIGLU_B200_API int swiglu_b200_gemm_fwd(void* h, void* gate_out, void* up_out, const void* x, const void* w_gate, const void* w_up,
                          int64_t m, int64_t n, int64_t k, float gm, float dm, void* status, int device, void* stream);
 
+/* swiglu_b200_gemm_fwd for callers that cannot allocate device memory.  It has no counterpart in
+ * the reference; it exists for hosts that are not allowed to (or cannot successfully) call
+ * cudaMalloc when they need the kernel: processes in which a memory planner or another
+ * framework's caching allocator already holds all device memory, latency-critical loops where
+ * cudaMalloc/cudaFree are banned because they synchronise the device, plug-ins that receive their
+ * tensors and nothing else.  Same computation and the same requirements on m, n, k and the
+ * pointers as swiglu_b200_gemm_fwd (without the optional pre-activation outputs), but the
+ * kernel's status word lives in a 256-byte array inside the library image, so the caller passes
+ * inputs and outputs only.  The call performs no cudaMalloc/cudaFree and uses no allocating
+ * library routine.
+ *   status_host    NULL, or where to copy the status word after the kernel (asynchronously on
+ *                  `stream`; use pinned memory): 0 once the stream is synchronised means success.
+ * Limit: the scratch array is 256 bytes per device and is held by every GPU that loads the
+ * library until the process exits; a call needs 4 of them for any problem size, and a call whose
+ * need exceeded the array would be refused with SWIGLU_B200_ERR_WORKSPACE.
+ * Set-up: the first call on each device looks up the array's device address (and, like the first
+ * swiglu_b200_gemm_fwd call, configures the kernel); make that first call before any stream
+ * capture is begun.
+ * Sharing: every call on a device uses the same array, which keeps the previous call's contents;
+ * each call zeroes the status word on `stream` before its kernel runs.  Calls whose kernels
+ * overlap on the GPU (different streams, or several host threads) race on that word: serialise
+ * them on one stream, or use swiglu_b200_gemm_fwd with a status word per stream. */
+SWIGLU_B200_API int swiglu_b200_gemm_fwd_noalloc(void* h, const void* x, const void* w_gate, const void* w_up, int64_t m, int64_t n,
+                                 int64_t k, float gm, float dm, int* status_host, int device, void* stream);
+
 /* Number of fused-GEMM kernels launched by this process. */
 SWIGLU_B200_API uint64_t swiglu_b200_gemm_launch_count(void);
 

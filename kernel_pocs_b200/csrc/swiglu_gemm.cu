@@ -683,4 +683,76 @@ int swiglu_b200_gemm_fwd(void* h, void* gate_out, void* up_out, const void* x, c
   return SWIGLU_B200_OK;
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Entry point for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at the moment they need the fused GEMM: a
+// serving process whose memory planner (or another framework's caching allocator) already owns
+// all of the device memory, so that a raw allocation fails; a latency-critical loop in which
+// cudaMalloc/cudaFree are banned because they synchronise the whole device; a plug-in that is
+// handed its tensors and nothing else.  swiglu_b200_gemm_fwd asks such a caller for one device
+// word (the kernel's status word); this variant keeps that word in a small array that lives in
+// the library image itself, so the caller passes inputs and outputs only.
+//
+// The array below is the device-side object; in host code its NAME is only a handle, not a
+// device address, so it is translated once per device with cudaGetSymbolAddress while that
+// device is current, and the translated pointer is what the kernel receives.
+constexpr size_t kNoAllocScratchBytes = 256;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+namespace {
+
+// Device address of g_noalloc_scratch on the CURRENT device (looked up once per device).
+int noalloc_scratch(void** out) {
+  static std::mutex mu;
+  static void* cache[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev < 64 && cache[dev]) {
+    *out = cache[dev];
+    return SWIGLU_B200_OK;
+  }
+  void* ptr = nullptr;
+  if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || ptr == nullptr) return SWIGLU_B200_ERR_DEVICE;
+  if (dev < 64) cache[dev] = ptr;
+  *out = ptr;
+  return SWIGLU_B200_OK;
+}
+
+}  // namespace
+
+int swiglu_b200_gemm_fwd_noalloc(void* h, const void* x, const void* w_gate, const void* w_up, int64_t m, int64_t n,
+                                 int64_t k, float gm, float dm, int* status_host, int device, void* stream) {
+  // Scratch the kernel needs for this problem: one status word, whatever m, n and k are.  The
+  // check is written against the array size so that it keeps guarding if either ever changes.
+  const size_t scratch_needed = sizeof(int);
+  if (scratch_needed > kNoAllocScratchBytes) return SWIGLU_B200_ERR_WORKSPACE;
+
+  int prev = -1;
+  bool switched = false;
+  if (device >= 0) {
+    if (cudaGetDevice(&prev) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
+    if (prev != device) {
+      if (cudaSetDevice(device) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
+      switched = true;
+    }
+  }
+  void* status_dev = nullptr;
+  int rc = noalloc_scratch(&status_dev);  // with the target device current
+  if (rc == SWIGLU_B200_OK) {
+    // The existing entry point zeroes the status word on the stream before the kernel starts
+    // (the array still holds whatever the previous call left) and allocates nothing itself.
+    rc = swiglu_b200_gemm_fwd(h, nullptr, nullptr, x, w_gate, w_up, m, n, k, gm, dm, status_dev, -1, stream);
+    if (rc == SWIGLU_B200_OK && status_host != nullptr && m > 0 && n > 0) {
+      if (cudaMemcpyAsync(status_host, status_dev, sizeof(int), cudaMemcpyDeviceToHost,
+                          static_cast<cudaStream_t>(stream)) != cudaSuccess)
+        rc = SWIGLU_B200_ERR_COPY;
+    }
+  }
+  if (switched) cudaSetDevice(prev);
+  return rc;
+}
+
 }  // extern "C"
