@@ -38,9 +38,12 @@ DTYPE_NAME = {torch.float32: "fp32", torch.float16: "fp16", torch.bfloat16: "bf1
 METRIC = "swiglu_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this GPU pool, used when MEASURED_PEAKS.json is absent
-# dram__bytes_read.sum + dram__bytes_write.sum of one backward launch on the c2 workload, from the
-# ncu capture summarised in profiles/ (None until a capture exists).
-BWD_DRAM_TRAFFIC_BYTES_C2 = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one backward launch on the c2 workload: the ncu
+# capture of the first 8192 of its 32768 token rows (profiles/swiglu_fwd_bwd_c2_8192rows_ncu_full.md:
+# 704.66 MB read + 413.66 MB written) scaled by 4; the traffic of this pure stream grows in proportion
+# to the rows.  Reads equal the algorithmic reads exactly; writes are short by what L2 still holds
+# when the kernel ends.
+BWD_DRAM_TRAFFIC_BYTES_C2 = 4 * (704_655_872 + 413_662_464)
 
 
 def parse_args():
