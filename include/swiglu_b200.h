@@ -18,8 +18,10 @@
  *   separate gate/up  : in_row_stride == out_row_stride == cols
  *   packed gate|up    : gate = base, up = base + cols, in_row_stride = 2*cols,
  *                       out_row_stride = cols (and dup = dgate + cols in the backward)
- * The widest access that the base addresses, strides and `cols` allow is chosen per call
- * (16 bytes when everything is 16-byte compatible, down to one element).
+ * The widest access that the base addresses, strides and `cols` allow is chosen per call:
+ * 16 bytes for contiguous tensors whatever their alignment, as long as the outputs of a call are
+ * aligned alike (inputs that are skewed against them are realigned in registers); for pitched rows
+ * and for outputs skewed against each other, the widest power of two that fits, down to one element.
  *
  * Aliasing.  In the backward, dgate may equal gate and dup may equal up exactly (same address,
  * same stride): the in-place mode of the reference (swiglu.py:247-248, 310).  No other

@@ -28,6 +28,9 @@ using namespace swiglu_b200;
 #ifndef SWIGLU_BWD_UNROLL
 #define SWIGLU_BWD_UNROLL 2
 #endif
+#ifndef SWIGLU_SKEW_UNROLL
+#define SWIGLU_SKEW_UNROLL 2  // skewed-load kernels keep a second granule per vector in registers
+#endif
 #ifndef SWIGLU_LD_RO
 #define SWIGLU_LD_RO LD_NC_NOALLOC  // inputs that this launch never writes
 #endif
@@ -85,15 +88,18 @@ inline int pow2_divisor(unsigned long long v, int limit) {
 
 struct Plan {
   bool rows;   // 2-D addressing
+  bool shift;  // flat, 16-byte body, some input skewed against the outputs (see ld_skewed)
   int bytes;   // access width of the body
   Shape shape;
   long long skip;  // bytes by which every base pointer is advanced (flat head)
+  int skew[3];     // per input, in the order the caller listed them
 };
 
-// Chooses addressing and access width for tensors at addresses `addr[0..n_addr)`, where
+// Chooses addressing and access width.  `out` are the addresses written, `in` the addresses only
+// read (an in-place backward lists gate/up under `out`, since dgate/dup are the same addresses);
 // pitch[k] (elements) are the row strides in play.
-Plan make_plan(const unsigned long long* addr, int n_addr, const long long* pitch, int n_pitch, long long rows,
-               long long cols, int es) {
+Plan make_plan(const unsigned long long* out, int n_out, const unsigned long long* in, int n_in,
+               const long long* pitch, int n_pitch, long long rows, long long cols, int es) {
   constexpr int kWide = 16;
   Plan p{};
   bool flat = true;
@@ -101,11 +107,16 @@ Plan make_plan(const unsigned long long* addr, int n_addr, const long long* pitc
     for (int k = 0; k < n_pitch; ++k) flat = flat && (pitch[k] == cols);
   p.rows = !flat;
   const long long n = rows * cols;
+  int common = kWide;  // widest power of two dividing every address
+  for (int k = 0; k < n_out; ++k) common = pow2_divisor(out[k], common);
+  for (int k = 0; k < n_in; ++k) common = pow2_divisor(in[k], common);
   if (flat) {
-    bool congruent = true;
-    for (int k = 1; k < n_addr; ++k) congruent = congruent && ((addr[k] % kWide) == (addr[0] % kWide));
-    if (congruent) {
-      long long head = (long long)((kWide - addr[0] % kWide) % kWide) / es;
+    bool out_congruent = true;
+    for (int k = 1; k < n_out; ++k) out_congruent = out_congruent && ((out[k] % kWide) == (out[0] % kWide));
+    if (out_congruent) {
+      // Peel a scalar head so that the outputs' body starts on a 16-byte boundary; inputs that do
+      // not land on one as well are read through the skewed-load path.
+      long long head = (long long)((kWide - out[0] % kWide) % kWide) / es;
       if (head > n) head = n;
       const int epv = kWide / es;
       p.bytes = kWide;
@@ -113,19 +124,20 @@ Plan make_plan(const unsigned long long* addr, int n_addr, const long long* pitc
       p.shape.head = (int)head;
       p.shape.edge = (int)(n - p.shape.n_vec * epv);
       p.skip = head * es;
+      for (int k = 0; k < n_in; ++k) {
+        p.skew[k] = (int)((in[k] + (unsigned long long)p.skip) % kWide);
+        p.shift = p.shift || p.skew[k] != 0;
+      }
     } else {
-      int b = kWide;
-      for (int k = 0; k < n_addr; ++k) b = pow2_divisor(addr[k], b);
-      const int epv = b / es;
-      p.bytes = b;
+      const int epv = common / es;
+      p.bytes = common;
       p.shape.n_vec = n / epv;
       p.shape.head = 0;
       p.shape.edge = (int)(n - p.shape.n_vec * epv);
       p.skip = 0;
     }
   } else {
-    int b = kWide;
-    for (int k = 0; k < n_addr; ++k) b = pow2_divisor(addr[k], b);
+    int b = common;
     b = pow2_divisor((unsigned long long)cols * es, b);
     for (int k = 0; k < n_pitch; ++k) b = pow2_divisor((unsigned long long)pitch[k] * es, b);
     p.bytes = b;
@@ -138,11 +150,12 @@ Plan make_plan(const unsigned long long* addr, int n_addr, const long long* pitc
 
 // ------------------------------------------------------------------ forward dispatch
 
-template <class T, int BYTES, bool ROWS>
+template <class T, int BYTES, bool ROWS, bool SHIFT = false>
 int launch_fwd(void* out, const void* gate, const void* up, const Shape& s, float gm, float dm, cudaStream_t st) {
   constexpr bool FAST = (sizeof(T) == 2);
-  auto kernel = swiglu_fwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, SWIGLU_FWD_UNROLL, SWIGLU_LD_RO, SWIGLU_ST>;
-  const unsigned grid = grid_for(s.n_vec, SWIGLU_THREADS, SWIGLU_FWD_UNROLL);
+  constexpr int UNROLL = SHIFT ? SWIGLU_SKEW_UNROLL : SWIGLU_FWD_UNROLL;
+  auto kernel = swiglu_fwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, UNROLL, SWIGLU_LD_RO, SWIGLU_ST, SHIFT>;
+  const unsigned grid = grid_for(s.n_vec, SWIGLU_THREADS, UNROLL);
   kernel<<<grid, SWIGLU_THREADS, 0, st>>>(out, gate, up, s, gm, dm);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail_cuda(SWIGLU_B200_ERR_LAUNCH, err);
@@ -165,20 +178,22 @@ int fwd_by_width(int bytes, void* out, const void* gate, const void* up, const S
 
 template <class T>
 int fwd_typed(const Plan& p, void* out, const void* gate, const void* up, float gm, float dm, cudaStream_t st) {
+  if (p.shift) return launch_fwd<T, 16, false, true>(out, gate, up, p.shape, gm, dm, st);
   return p.rows ? fwd_by_width<T, true>(p.bytes, out, gate, up, p.shape, gm, dm, st)
                 : fwd_by_width<T, false>(p.bytes, out, gate, up, p.shape, gm, dm, st);
 }
 
 // ------------------------------------------------------------------ backward dispatch
 
-template <class T, int BYTES, bool ROWS, bool INPLACE>
+template <class T, int BYTES, bool ROWS, bool INPLACE, bool SHIFT = false>
 int launch_bwd(void* dgate, void* dup, const void* dout, const void* gate, const void* up, const Shape& s, float gm,
                float dm, cudaStream_t st) {
   constexpr bool FAST = (sizeof(T) == 2);
   constexpr int LD_IO = INPLACE ? SWIGLU_LD_ALIASED : SWIGLU_LD_RO;
+  constexpr int UNROLL = SHIFT ? SWIGLU_SKEW_UNROLL : SWIGLU_BWD_UNROLL;
   auto kernel =
-      swiglu_bwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, SWIGLU_BWD_UNROLL, SWIGLU_LD_RO, LD_IO, SWIGLU_ST>;
-  const unsigned grid = grid_for(s.n_vec, SWIGLU_THREADS, SWIGLU_BWD_UNROLL);
+      swiglu_bwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, UNROLL, SWIGLU_LD_RO, LD_IO, SWIGLU_ST, SHIFT>;
+  const unsigned grid = grid_for(s.n_vec, SWIGLU_THREADS, UNROLL);
   kernel<<<grid, SWIGLU_THREADS, 0, st>>>(dgate, dup, dout, gate, up, s, gm, dm);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail_cuda(SWIGLU_B200_ERR_LAUNCH, err);
@@ -202,6 +217,10 @@ int bwd_by_width(int bytes, void* dgate, void* dup, const void* dout, const void
 template <class T>
 int bwd_typed(const Plan& p, bool inplace, void* dgate, void* dup, const void* dout, const void* gate,
               const void* up, float gm, float dm, cudaStream_t st) {
+  if (p.shift) {
+    return inplace ? launch_bwd<T, 16, false, true, true>(dgate, dup, dout, gate, up, p.shape, gm, dm, st)
+                   : launch_bwd<T, 16, false, false, true>(dgate, dup, dout, gate, up, p.shape, gm, dm, st);
+  }
   if (p.rows) {
     return inplace ? bwd_by_width<T, true, true>(p.bytes, dgate, dup, dout, gate, up, p.shape, gm, dm, st)
                    : bwd_by_width<T, true, false>(p.bytes, dgate, dup, dout, gate, up, p.shape, gm, dm, st);
@@ -269,9 +288,13 @@ int swiglu_b200_fwd(void* out, const void* gate, const void* up, int64_t rows, i
   DeviceScope scope(device);
   if (scope.err != cudaSuccess) return fail_cuda(SWIGLU_B200_ERR_DEVICE, scope.err);
 
-  const unsigned long long addr[3] = {addr_of(out), addr_of(gate), addr_of(up)};
+  const unsigned long long outs[1] = {addr_of(out)};
+  const unsigned long long ins[2] = {addr_of(gate), addr_of(up)};
   const long long pitch[2] = {in_row_stride, out_row_stride};
-  Plan p = make_plan(addr, 3, pitch, 2, rows, cols, es);
+  Plan p = make_plan(outs, 1, ins, 2, pitch, 2, rows, cols, es);
+  p.shape.skew_gate = p.skew[0];
+  p.shape.skew_up = p.skew[1];
+  p.shape.skew_dout = 0;
   p.shape.pitch_in = in_row_stride * es;
   p.shape.pitch_out = out_row_stride * es;
   p.shape.pitch_grad = 0;
@@ -323,9 +346,13 @@ int swiglu_b200_bwd(void* dgate, void* dup, const void* dout, const void* gate, 
   DeviceScope scope(device);
   if (scope.err != cudaSuccess) return fail_cuda(SWIGLU_B200_ERR_DEVICE, scope.err);
 
-  const unsigned long long addr[5] = {addr_of(dgate), addr_of(dup), addr_of(dout), addr_of(gate), addr_of(up)};
+  const unsigned long long outs[2] = {addr_of(dgate), addr_of(dup)};
+  const unsigned long long ins[3] = {addr_of(dout), addr_of(gate), addr_of(up)};  // in place: gate/up == outs
   const long long pitch[3] = {in_row_stride, grad_row_stride, dout_row_stride};
-  Plan p = make_plan(addr, 5, pitch, 3, rows, cols, es);
+  Plan p = make_plan(outs, 2, ins, 3, pitch, 3, rows, cols, es);
+  p.shape.skew_dout = p.skew[0];
+  p.shape.skew_gate = p.skew[1];
+  p.shape.skew_up = p.skew[2];
   p.shape.pitch_in = in_row_stride * es;
   p.shape.pitch_out = dout_row_stride * es;
   p.shape.pitch_grad = grad_row_stride * es;

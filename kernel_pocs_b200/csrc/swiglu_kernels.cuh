@@ -319,7 +319,75 @@ struct Shape {
   long long pitch_grad;    // bytes between rows of dgate / dup              (ROWS, bwd only)
   int head;                // scalar elements before the body                (FLAT only)
   int edge;                // head + tail scalar elements                    (FLAT only)
+  // SHIFT kernels only: how many bytes past a 16-byte boundary the body of each INPUT starts, when
+  // the outputs' bodies start on one (0..15, a multiple of the element size).
+  int skew_gate, skew_up, skew_dout;
 };
+
+// ---------------------------------------------------------------------------------------
+// Loads for inputs that are misaligned relative to the outputs (flat layout, 16-byte vectors).
+// Vector i of such an input straddles two aligned 16-byte granules.  Every thread loads the first
+// granule of its vector with one aligned access; the second granule is the first granule of vector
+// i+1, which the next lane of the warp loads anyway, so it arrives by shuffle.  Only the last
+// lane of a warp (and the owner of the launch's last vector) fetches its second granule itself.
+// The two granules are then funnel-shifted into place.  Bytes outside the tensor that share a
+// granule with its first or last element are read and discarded.
+// ---------------------------------------------------------------------------------------
+
+static __device__ __forceinline__ const char* cbyte(const void* p) { return static_cast<const char*>(p); }
+static __device__ __forceinline__ char* byte(void* p) { return static_cast<char*>(p); }
+
+__device__ __forceinline__ Vec<16> funnel16(const Vec<16>& lo, const Vec<16>& hi, int skew) {
+  const uint32_t w[8] = {lo.w[0], lo.w[1], lo.w[2], lo.w[3], hi.w[0], hi.w[1], hi.w[2], hi.w[3]};
+  const int sh = (skew & 3) * 8;
+  Vec<16> o;
+  switch (skew >> 2) {  // uniform over the launch
+    case 0:
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o.w[i] = __funnelshift_r(w[i], w[i + 1], sh);
+      break;
+    case 1:
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o.w[i] = __funnelshift_r(w[i + 1], w[i + 2], sh);
+      break;
+    case 2:
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o.w[i] = __funnelshift_r(w[i + 2], w[i + 3], sh);
+      break;
+    default:
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o.w[i] = __funnelshift_r(w[i + 3], w[i + 4], sh);
+      break;
+  }
+  return o;
+}
+
+// Phase 1, with the other loads of the tile: `base` is the input's body pointer (misaligned by `skew`
+// bytes), `off` the byte offset of vector i in the outputs.  Loads the first granule of the vector
+// into `lo` and, for the lanes that cannot get it from a neighbour, the second into `own_hi`.
+template <int LDM>
+__device__ __forceinline__ void ld_skewed_issue(const void* base, long long off, int skew, bool active,
+                                                bool self_fetch, Vec<16>& lo, Vec<16>& own_hi) {
+  lo = Vec<16>{};
+  own_hi = Vec<16>{};
+  const char* granule = cbyte(base) - skew + off;
+  if (active) {
+    lo = Ld<16, LDM>::ld(granule);
+    if (skew != 0 && self_fetch) own_hi = Ld<16, LDM>::ld(granule + 16);
+  }
+}
+
+// Phase 2, after every load of the tile has been issued (a shuffle waits for its operand, so doing
+// this between the loads would serialise them).  All 32 lanes must call this together.
+__device__ __forceinline__ Vec<16> ld_skewed_finish(const Vec<16>& lo, const Vec<16>& own_hi, int skew,
+                                                    bool self_fetch) {
+  if (skew == 0) return lo;  // uniform over the launch
+  Vec<16> hi;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) hi.w[i] = __shfl_down_sync(0xffffffffu, lo.w[i], 1);
+  if (self_fetch) hi = own_hi;
+  return funnel16(lo, hi, skew);
+}
 
 template <bool ROWS, int BYTES>
 struct Locator {
@@ -345,15 +413,12 @@ struct Locator {
   }
 };
 
-static __device__ __forceinline__ const char* cbyte(const void* p) { return static_cast<const char*>(p); }
-static __device__ __forceinline__ char* byte(void* p) { return static_cast<char*>(p); }
-
 // ---------------------------------------------------------------------------------------
 // Forward.  One tile = THREADS*UNROLL vectors; thread t owns vectors t, t+THREADS, ... of
 // the tile, so each warp-wide access is one contiguous 512- or 1024-byte segment.
 // ---------------------------------------------------------------------------------------
 
-template <class T, int BYTES, bool FAST, bool ROWS, int THREADS, int UNROLL, int LDM, int STM>
+template <class T, int BYTES, bool FAST, bool ROWS, int THREADS, int UNROLL, int LDM, int STM, bool SHIFT = false>
 __global__ void __launch_bounds__(THREADS)
 swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const void* __restrict__ up, Shape s,
                   float gm, float dm) {
@@ -366,11 +431,19 @@ swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const v
     const long long v0 = tile * TILE + threadIdx.x;
     const bool full = (tile + 1) * TILE <= s.n_vec;
     Vec<BYTES> g[UNROLL], u[UNROLL];
+    Vec<SHIFT ? 16 : 2> g2[SHIFT ? UNROLL : 1], u2[SHIFT ? UNROLL : 1];  // self-fetched second granules
     long long oo[UNROLL];
 #pragma unroll
     for (int k = 0; k < UNROLL; ++k) {
       const long long i = v0 + (long long)k * THREADS;
-      if (full || i < s.n_vec) {
+      if constexpr (SHIFT) {
+        static_assert(!SHIFT || (BYTES == 16 && !ROWS), "skewed loads exist for flat 16-byte streams only");
+        const bool active = full || i < s.n_vec;
+        const bool self_fetch = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec;
+        oo[k] = i * BYTES;
+        ld_skewed_issue<LDM>(gate, oo[k], s.skew_gate, active, self_fetch, g[k], g2[k]);
+        ld_skewed_issue<LDM>(up, oo[k], s.skew_up, active, self_fetch, u[k], u2[k]);
+      } else if (full || i < s.n_vec) {
         long long oi, og;
         Locator<ROWS, BYTES>::at(s, i, oi, oo[k], og);
         g[k] = Ld<BYTES, LDM>::ld(cbyte(gate) + oi);
@@ -380,6 +453,11 @@ swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const v
 #pragma unroll
     for (int k = 0; k < UNROLL; ++k) {
       const long long i = v0 + (long long)k * THREADS;
+      if constexpr (SHIFT) {
+        const bool self_fetch = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec;
+        g[k] = ld_skewed_finish(g[k], g2[k], s.skew_gate, self_fetch);
+        u[k] = ld_skewed_finish(u[k], u2[k], s.skew_up, self_fetch);
+      }
       if (full || i < s.n_vec) {
         float fg[EPV], fu[EPV], fh[EPV];
         Codec<T>::template unpack<BYTES>(g[k], fg);
@@ -420,7 +498,8 @@ swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const v
 // dgate/dup alias them.  dh is always read-only.
 // ---------------------------------------------------------------------------------------
 
-template <class T, int BYTES, bool FAST, bool ROWS, int THREADS, int UNROLL, int LDM_DH, int LDM_IO, int STM>
+template <class T, int BYTES, bool FAST, bool ROWS, int THREADS, int UNROLL, int LDM_DH, int LDM_IO, int STM,
+          bool SHIFT = false>
 __global__ void __launch_bounds__(THREADS)
 swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const void* gate, const void* up, Shape s,
                   float gm, float dm) {
@@ -433,11 +512,20 @@ swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const v
     const long long v0 = tile * TILE + threadIdx.x;
     const bool full = (tile + 1) * TILE <= s.n_vec;
     Vec<BYTES> d[UNROLL], g[UNROLL], u[UNROLL];
+    Vec<SHIFT ? 16 : 2> d2[SHIFT ? UNROLL : 1], g2[SHIFT ? UNROLL : 1], u2[SHIFT ? UNROLL : 1];
     long long og[UNROLL];
 #pragma unroll
     for (int k = 0; k < UNROLL; ++k) {
       const long long i = v0 + (long long)k * THREADS;
-      if (full || i < s.n_vec) {
+      if constexpr (SHIFT) {
+        static_assert(!SHIFT || (BYTES == 16 && !ROWS), "skewed loads exist for flat 16-byte streams only");
+        const bool active = full || i < s.n_vec;
+        const bool self_fetch = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec;
+        og[k] = i * BYTES;
+        ld_skewed_issue<LDM_DH>(dout, og[k], s.skew_dout, active, self_fetch, d[k], d2[k]);
+        ld_skewed_issue<LDM_IO>(gate, og[k], s.skew_gate, active, self_fetch, g[k], g2[k]);
+        ld_skewed_issue<LDM_IO>(up, og[k], s.skew_up, active, self_fetch, u[k], u2[k]);
+      } else if (full || i < s.n_vec) {
         long long oi, oo;
         Locator<ROWS, BYTES>::at(s, i, oi, oo, og[k]);
         d[k] = Ld<BYTES, LDM_DH>::ld(cbyte(dout) + oo);
@@ -450,6 +538,12 @@ swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const v
 #pragma unroll
     for (int k = 0; k < UNROLL; ++k) {
       const long long i = v0 + (long long)k * THREADS;
+      if constexpr (SHIFT) {
+        const bool self_fetch = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec;
+        d[k] = ld_skewed_finish(d[k], d2[k], s.skew_dout, self_fetch);
+        g[k] = ld_skewed_finish(g[k], g2[k], s.skew_gate, self_fetch);
+        u[k] = ld_skewed_finish(u[k], u2[k], s.skew_up, self_fetch);
+      }
       if (full || i < s.n_vec) {
         float fd[EPV], fg[EPV], fu[EPV], fdg[EPV], fdu[EPV];
         Codec<T>::template unpack<BYTES>(d[k], fd);

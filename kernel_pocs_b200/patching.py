@@ -1,0 +1,135 @@
+"""Model-level adapter for the SwiGLU path: ``patch(model)`` / ``unpatch(model)``.
+
+Covers the part of the reference's ``forge.patch`` that calls this path
+(forge/forge/patching/core.py:152-267 for the orchestration, qwen3.py:49-50 for the class mapping,
+kernels/basic.py:88-104 for the closure): every ``Qwen2MLP`` / ``Qwen3MLP`` instance of a Hugging Face
+model gets the forward ``down_proj(swiglu(gate_proj(x), up_proj(x)))`` bound to the CUDA kernels of this
+package, with the original bound method kept for a bit-exact ``unpatch``.  Book-keeping attributes
+(``_forge_patched``, ``_forge_originals``, ``_forge_patched_counts``, ``_forge_arch``) and error types follow the
+reference.  The other kernels of the reference's registry (rmsnorm, rope, embedding, cross entropy, LoRA)
+are not part of this package; asking for them raises ``KeyError``.
+
+One kernel is added that the reference does not have: ``"fused_gate_up"`` replaces the two projection GEMMs
+and the activation by the single tcgen05 kernel of ``fused_mlp`` when the module's projections are plain
+bias-free bf16 ``nn.Linear`` layers (otherwise the module is left to ``"swiglu"``).  It is opt-in:
+``patch(model, kernels=["fused_gate_up", "swiglu"])``.
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, List, Optional
+
+import torch
+
+from .fused_mlp import fused_gate_up_swiglu
+from .swiglu import swiglu
+
+SUPPORTED_MODEL_TYPES = ("qwen2", "qwen3")
+MLP_CLASSES = ("Qwen2MLP", "Qwen3MLP")
+DEFAULT_KERNELS = ("swiglu",)
+
+
+class SkipPatch(Exception):
+    """Raised by a forward factory that does not apply to a module; the next kernel is tried."""
+
+
+def _model_config(model):
+    config = getattr(model, "config", None)
+    if config is None:
+        inner = getattr(getattr(model, "base_model", None), "model", None)
+        config = getattr(inner, "config", None)
+    if config is None:
+        raise ValueError("patch: model does not expose a Hugging Face config.")
+    return config
+
+
+def _activation_name(module) -> str:
+    cfg = getattr(module, "config", None)
+    name = getattr(cfg, "hidden_act", None) if cfg is not None else None
+    return name or "silu"
+
+
+def make_swiglu_forward(module) -> Callable:
+    if _activation_name(module) != "silu":
+        raise NotImplementedError(
+            f"patch: the swiglu kernel only supports activation='silu', got {_activation_name(module)!r}"
+        )
+
+    def forward(x):
+        return module.down_proj(swiglu(module.gate_proj(x), module.up_proj(x)))
+
+    return forward
+
+
+def make_fused_gate_up_forward(module) -> Callable:
+    if _activation_name(module) != "silu":
+        raise SkipPatch
+    for proj in (module.gate_proj, module.up_proj):
+        if type(proj) is not torch.nn.Linear or proj.bias is not None or proj.weight.dtype != torch.bfloat16:
+            raise SkipPatch
+    n, k = module.gate_proj.weight.shape
+    if k % 8 or n % 16:
+        raise SkipPatch
+
+    def forward(x):
+        # weights are read at call time, so optimiser updates and .to() moves are seen
+        return module.down_proj(fused_gate_up_swiglu(x, module.gate_proj.weight, module.up_proj.weight))
+
+    return forward
+
+
+FORWARD_MAKERS: Dict[str, Callable] = {
+    "swiglu": make_swiglu_forward,
+    "fused_gate_up": make_fused_gate_up_forward,
+}
+
+
+def patch(model, kernels: Optional[List[str]] = None):
+    """Rebinds the MLP forwards of ``model`` in place and returns it.
+
+    ``kernels``: ordered list of kernel names to try per MLP; the first whose factory accepts the module
+    wins.  ``None`` means ``["swiglu"]``.
+    """
+    if getattr(model, "_forge_patched", False):
+        raise RuntimeError("Model already patched. Call unpatch(model) first.")
+    model_type = getattr(_model_config(model), "model_type", None)
+    if model_type not in SUPPORTED_MODEL_TYPES:
+        raise ValueError(
+            f"patch: no mapping for model_type={model_type!r}. Supported: {sorted(SUPPORTED_MODEL_TYPES)}."
+        )
+    wanted = list(DEFAULT_KERNELS if kernels is None else kernels)
+    for name in wanted:  # validate before touching any module
+        if name not in FORWARD_MAKERS:
+            raise KeyError(f"patch: unknown kernel {name!r}. Known: {sorted(FORWARD_MAKERS)}.")
+
+    originals: dict = {}
+    counts: Dict[str, int] = {}
+    for _name, module in model.named_modules():
+        if type(module).__name__ not in MLP_CLASSES:
+            continue
+        for name in wanted:
+            try:
+                new_forward = FORWARD_MAKERS[name](module)
+            except SkipPatch:
+                continue
+            originals[id(module)] = (module, module.forward)
+            module.forward = new_forward
+            counts[name] = counts.get(name, 0) + 1
+            break
+
+    model._forge_originals = originals
+    model._forge_patched = True
+    model._forge_patched_counts = counts
+    model._forge_arch = model_type
+    return model
+
+
+def unpatch(model):
+    """Restores the original forwards; a no-op on a model that is not patched."""
+    if not getattr(model, "_forge_patched", False):
+        return model
+    for module, original in model._forge_originals.values():
+        module.forward = original
+    for attr in ("_forge_originals", "_forge_patched", "_forge_patched_counts", "_forge_arch"):
+        if hasattr(model, attr):
+            delattr(model, attr)
+    return model

@@ -1,0 +1,88 @@
+"""Model-level drop-in: patch()/unpatch() on a randomly initialised tiny Qwen3 (no checkpoint needed).
+
+CPU tests cover the orchestration (what gets rebound, book-keeping, error types, bit-exact unpatch);
+the GPU tests apply the acceptance criteria of the reference's verify_patch_qwen3.py:186-201 to the
+logits of the patched model -- NaN-free, same shape, max-abs difference < 1.0, cosine > 0.999 -- and its
+requirement that unpatch restores the original outputs bit for bit (:219-225), plus gradient agreement in
+the spirit of verify_qwen_patch_backward.py:187-204 (loss difference and gradient cosine).
+"""
+import pytest
+import torch
+
+from kernel_pocs_b200 import _lib, patching
+
+transformers = pytest.importorskip("transformers")
+
+
+def tiny_qwen3(dtype=torch.float32, device="cpu", layers=2):
+    cfg = transformers.Qwen3Config(
+        vocab_size=512, hidden_size=128, intermediate_size=384, num_hidden_layers=layers, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=32, max_position_embeddings=128, tie_word_embeddings=False,
+    )
+    torch.manual_seed(0)
+    return transformers.Qwen3ForCausalLM(cfg).to(device=device, dtype=dtype)
+
+
+def test_patch_rebinds_every_mlp_and_unpatch_restores_them():
+    model = tiny_qwen3()
+    mlps = [m for m in model.modules() if type(m).__name__ == "Qwen3MLP"]
+    originals = [m.forward for m in mlps]
+    assert patching.patch(model) is model
+    assert model._forge_patched and model._forge_arch == "qwen3"
+    assert model._forge_patched_counts == {"swiglu": len(mlps)} and len(mlps) == 2
+    assert all(m.forward is not o for m, o in zip(mlps, originals))
+    with pytest.raises(RuntimeError, match="already patched"):
+        patching.patch(model)
+    # the patched forward reaches the CUDA-only operator: on CPU tensors it must refuse, not compute
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        model(torch.randint(0, 512, (1, 8)))
+    patching.unpatch(model)
+    assert not hasattr(model, "_forge_patched") and not hasattr(model, "_forge_originals")
+    assert all(m.forward == o for m, o in zip(mlps, originals))
+    ids = torch.randint(0, 512, (1, 8))
+    assert torch.equal(model(ids).logits, tiny_qwen3()(ids).logits)
+    assert patching.unpatch(model) is model  # idempotent
+
+
+def test_patch_validates_before_mutating():
+    model = tiny_qwen3()
+    with pytest.raises(KeyError, match="unknown kernel"):
+        patching.patch(model, kernels=["swiglu", "rmsnorm"])
+    assert not getattr(model, "_forge_patched", False)
+    model.config.model_type = "gpt2"
+    with pytest.raises(ValueError, match="no mapping for model_type"):
+        patching.patch(model)
+    # fp32 projections are not eligible for the fused GEMM: the module falls through to swiglu
+    model = tiny_qwen3()
+    patching.patch(model, kernels=["fused_gate_up", "swiglu"])
+    assert model._forge_patched_counts == {"swiglu": 2}
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kernels,expected", [(None, "swiglu"), (["fused_gate_up", "swiglu"], "fused_gate_up")])
+def test_patched_logits_and_gradients_match(kernels, expected):
+    model = tiny_qwen3(torch.bfloat16, "cuda", layers=3)
+    ids = torch.randint(0, 512, (4, 64), device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+
+    def run():
+        model.zero_grad(set_to_none=True)
+        out = model(ids, labels=ids)
+        out.loss.backward()
+        grads = torch.cat([p.grad.float().flatten() for p in model.parameters()])
+        return out.logits.detach().clone(), out.loss.detach().clone(), grads
+
+    base_logits, base_loss, base_grads = run()
+    launches = _lib.launch_count() + _lib.lib.swiglu_b200_gemm_launch_count()
+    patching.patch(model, kernels=kernels)
+    assert model._forge_patched_counts == {expected: 3}
+    logits, loss, grads = run()
+    assert _lib.launch_count() + _lib.lib.swiglu_b200_gemm_launch_count() > launches, "no kernel of this library ran"
+    assert logits.shape == base_logits.shape and bool(torch.isfinite(logits).all())
+    assert float((logits.float() - base_logits.float()).abs().max()) < 1.0
+    cos = torch.nn.functional.cosine_similarity(logits.float().flatten(), base_logits.float().flatten(), dim=0)
+    assert float(cos) > 0.999
+    assert abs(float(loss) - float(base_loss)) <= 2e-2
+    assert float(torch.nn.functional.cosine_similarity(grads, base_grads, dim=0)) >= 0.999
+    patching.unpatch(model)
+    again_logits, _, _ = run()
+    assert torch.equal(again_logits, base_logits)
