@@ -17,6 +17,7 @@ Providers
     b200-safe    this library, preserve_inputs=True
     b200-packed  this library, packed gate|up layout
     torch-eager  the PyTorch composite (torch_swiglu_reference + autograd) on the same GPU
+    geglu-tanh, geglu-erf   the sibling GeGLU operator of this library (in-place backward), same byte model
 
 Configurations are the synthetic workloads of kernel_pocs_b200/workloads.py plus ragged variants
 of the variable-length one: width 11009, and the same with the first token row sliced off so that
@@ -122,7 +123,7 @@ def run_case(name, args, device, rank, world):
             # before the timed kernels start
             if packed:
                 gate_up.copy_(gate_up0)
-            elif provider == "b200":
+            elif provider == "b200" or provider.startswith("geglu-"):
                 gate.copy_(gate0)
                 up.copy_(up0)
             else:
@@ -145,6 +146,22 @@ def run_case(name, args, device, rank, world):
                 bwd()
 
             setups = {"forward": lambda: None, "backward": fwd, "full": lambda: None}
+        elif provider.startswith("geglu-"):
+            from kernels.geglu import geglu_backward, geglu_forward
+
+            approximate = "tanh" if provider == "geglu-tanh" else "none"
+
+            def fwd():
+                geglu_forward(gate, up, approximate)
+
+            def bwd():
+                geglu_backward(dh, gate, up, approximate)
+
+            def full():
+                fwd()
+                bwd()
+
+            setups = {m: restore for m in ("forward", "backward", "full")}
         elif packed:
             def fwd():
                 swiglu_packed_forward(gate_up)
@@ -265,7 +282,7 @@ def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--configs", nargs="+", default=["c1", "c2", "c3", "c3-fp32", "c3+w11009", "c3+w11009-off1"])
     ap.add_argument("--providers", nargs="+", default=["b200", "b200-safe", "torch-eager"],
-                    choices=["b200", "b200-safe", "b200-packed", "torch-eager"])
+                    choices=["b200", "b200-safe", "b200-packed", "torch-eager", "geglu-tanh", "geglu-erf"])
     ap.add_argument("--modes", nargs="+", default=["forward", "backward", "full"],
                     choices=["forward", "backward", "full"])
     ap.add_argument("--warmup", type=int, default=20)

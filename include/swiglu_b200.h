@@ -93,6 +93,18 @@ SWIGLU_B200_API int swiglu_b200_bwd(void* dgate, void* dup, const void* dout, co
                     int64_t cols, int64_t in_row_stride, int64_t grad_row_stride, int64_t dout_row_stride, int dtype,
                     float gm, float dm, int device, void* stream);
 
+/* GeGLU, the sibling operator: h = gelu(gate) * up and its backward, with the tanh approximation
+ * (approximate_tanh != 0) or the exact erf form.  Same layouts, strides, aliasing rule and
+ * return codes as swiglu_b200_fwd / swiglu_b200_bwd; there are no multipliers.  They replace the
+ * Triton launches of the reference's kernels/geglu/geglu.py (forward :396, packed forward :456,
+ * backward :425, packed backward :486). */
+SWIGLU_B200_API int swiglu_b200_geglu_fwd(void* out, const void* gate, const void* up, int64_t rows, int64_t cols,
+                          int64_t in_row_stride, int64_t out_row_stride, int dtype, int approximate_tanh, int device,
+                          void* stream);
+SWIGLU_B200_API int swiglu_b200_geglu_bwd(void* dgate, void* dup, const void* dout, const void* gate, const void* up, int64_t rows,
+                          int64_t cols, int64_t in_row_stride, int64_t grad_row_stride, int64_t dout_row_stride,
+                          int dtype, int approximate_tanh, int device, void* stream);
+
 /* Forward + backward for tensors held in HOST memory (pinned memory recommended; pageable
  * memory works but its copies do not overlap).  No counterpart in the reference, whose path
  * only takes device tensors; it serves callers that keep activations off the device and is

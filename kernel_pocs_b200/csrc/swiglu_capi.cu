@@ -150,11 +150,12 @@ Plan make_plan(const unsigned long long* out, int n_out, const unsigned long lon
 
 // ------------------------------------------------------------------ forward dispatch
 
-template <class T, int BYTES, bool ROWS, bool SHIFT = false>
+template <class T, int ACT, int BYTES, bool ROWS, bool SHIFT = false>
 int launch_fwd(void* out, const void* gate, const void* up, const Shape& s, float gm, float dm, cudaStream_t st) {
   constexpr bool FAST = (sizeof(T) == 2);
   constexpr int UNROLL = SHIFT ? SWIGLU_SKEW_UNROLL : SWIGLU_FWD_UNROLL;
-  auto kernel = swiglu_fwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, UNROLL, SWIGLU_LD_RO, SWIGLU_ST, SHIFT>;
+  auto kernel =
+      swiglu_fwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, UNROLL, SWIGLU_LD_RO, SWIGLU_ST, SHIFT, ACT>;
   const unsigned grid = grid_for(s.n_vec, SWIGLU_THREADS, UNROLL);
   kernel<<<grid, SWIGLU_THREADS, 0, st>>>(out, gate, up, s, gm, dm);
   cudaError_t err = cudaGetLastError();
@@ -163,36 +164,36 @@ int launch_fwd(void* out, const void* gate, const void* up, const Shape& s, floa
   return SWIGLU_B200_OK;
 }
 
-template <class T, bool ROWS>
+template <class T, int ACT, bool ROWS>
 int fwd_by_width(int bytes, void* out, const void* gate, const void* up, const Shape& s, float gm, float dm,
                  cudaStream_t st) {
   switch (bytes) {
-    case 16: return launch_fwd<T, 16, ROWS>(out, gate, up, s, gm, dm, st);
-    case 8: return launch_fwd<T, 8, ROWS>(out, gate, up, s, gm, dm, st);
-    case 4: return launch_fwd<T, 4, ROWS>(out, gate, up, s, gm, dm, st);
+    case 16: return launch_fwd<T, ACT, 16, ROWS>(out, gate, up, s, gm, dm, st);
+    case 8: return launch_fwd<T, ACT, 8, ROWS>(out, gate, up, s, gm, dm, st);
+    case 4: return launch_fwd<T, ACT, 4, ROWS>(out, gate, up, s, gm, dm, st);
     case 2:
-      if constexpr (sizeof(T) == 2) return launch_fwd<T, 2, ROWS>(out, gate, up, s, gm, dm, st);
+      if constexpr (sizeof(T) == 2) return launch_fwd<T, ACT, 2, ROWS>(out, gate, up, s, gm, dm, st);
   }
   return SWIGLU_B200_ERR_ALIGN;
 }
 
-template <class T>
+template <class T, int ACT>
 int fwd_typed(const Plan& p, void* out, const void* gate, const void* up, float gm, float dm, cudaStream_t st) {
-  if (p.shift) return launch_fwd<T, 16, false, true>(out, gate, up, p.shape, gm, dm, st);
-  return p.rows ? fwd_by_width<T, true>(p.bytes, out, gate, up, p.shape, gm, dm, st)
-                : fwd_by_width<T, false>(p.bytes, out, gate, up, p.shape, gm, dm, st);
+  if (p.shift) return launch_fwd<T, ACT, 16, false, true>(out, gate, up, p.shape, gm, dm, st);
+  return p.rows ? fwd_by_width<T, ACT, true>(p.bytes, out, gate, up, p.shape, gm, dm, st)
+                : fwd_by_width<T, ACT, false>(p.bytes, out, gate, up, p.shape, gm, dm, st);
 }
 
 // ------------------------------------------------------------------ backward dispatch
 
-template <class T, int BYTES, bool ROWS, bool INPLACE, bool SHIFT = false>
+template <class T, int ACT, int BYTES, bool ROWS, bool INPLACE, bool SHIFT = false>
 int launch_bwd(void* dgate, void* dup, const void* dout, const void* gate, const void* up, const Shape& s, float gm,
                float dm, cudaStream_t st) {
   constexpr bool FAST = (sizeof(T) == 2);
   constexpr int LD_IO = INPLACE ? SWIGLU_LD_ALIASED : SWIGLU_LD_RO;
   constexpr int UNROLL = SHIFT ? SWIGLU_SKEW_UNROLL : SWIGLU_BWD_UNROLL;
   auto kernel =
-      swiglu_bwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, UNROLL, SWIGLU_LD_RO, LD_IO, SWIGLU_ST, SHIFT>;
+      swiglu_bwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, UNROLL, SWIGLU_LD_RO, LD_IO, SWIGLU_ST, SHIFT, ACT>;
   const unsigned grid = grid_for(s.n_vec, SWIGLU_THREADS, UNROLL);
   kernel<<<grid, SWIGLU_THREADS, 0, st>>>(dgate, dup, dout, gate, up, s, gm, dm);
   cudaError_t err = cudaGetLastError();
@@ -201,32 +202,32 @@ int launch_bwd(void* dgate, void* dup, const void* dout, const void* gate, const
   return SWIGLU_B200_OK;
 }
 
-template <class T, bool ROWS, bool INPLACE>
+template <class T, int ACT, bool ROWS, bool INPLACE>
 int bwd_by_width(int bytes, void* dgate, void* dup, const void* dout, const void* gate, const void* up,
                  const Shape& s, float gm, float dm, cudaStream_t st) {
   switch (bytes) {
-    case 16: return launch_bwd<T, 16, ROWS, INPLACE>(dgate, dup, dout, gate, up, s, gm, dm, st);
-    case 8: return launch_bwd<T, 8, ROWS, INPLACE>(dgate, dup, dout, gate, up, s, gm, dm, st);
-    case 4: return launch_bwd<T, 4, ROWS, INPLACE>(dgate, dup, dout, gate, up, s, gm, dm, st);
+    case 16: return launch_bwd<T, ACT, 16, ROWS, INPLACE>(dgate, dup, dout, gate, up, s, gm, dm, st);
+    case 8: return launch_bwd<T, ACT, 8, ROWS, INPLACE>(dgate, dup, dout, gate, up, s, gm, dm, st);
+    case 4: return launch_bwd<T, ACT, 4, ROWS, INPLACE>(dgate, dup, dout, gate, up, s, gm, dm, st);
     case 2:
-      if constexpr (sizeof(T) == 2) return launch_bwd<T, 2, ROWS, INPLACE>(dgate, dup, dout, gate, up, s, gm, dm, st);
+      if constexpr (sizeof(T) == 2) return launch_bwd<T, ACT, 2, ROWS, INPLACE>(dgate, dup, dout, gate, up, s, gm, dm, st);
   }
   return SWIGLU_B200_ERR_ALIGN;
 }
 
-template <class T>
+template <class T, int ACT>
 int bwd_typed(const Plan& p, bool inplace, void* dgate, void* dup, const void* dout, const void* gate,
               const void* up, float gm, float dm, cudaStream_t st) {
   if (p.shift) {
-    return inplace ? launch_bwd<T, 16, false, true, true>(dgate, dup, dout, gate, up, p.shape, gm, dm, st)
-                   : launch_bwd<T, 16, false, false, true>(dgate, dup, dout, gate, up, p.shape, gm, dm, st);
+    return inplace ? launch_bwd<T, ACT, 16, false, true, true>(dgate, dup, dout, gate, up, p.shape, gm, dm, st)
+                   : launch_bwd<T, ACT, 16, false, false, true>(dgate, dup, dout, gate, up, p.shape, gm, dm, st);
   }
   if (p.rows) {
-    return inplace ? bwd_by_width<T, true, true>(p.bytes, dgate, dup, dout, gate, up, p.shape, gm, dm, st)
-                   : bwd_by_width<T, true, false>(p.bytes, dgate, dup, dout, gate, up, p.shape, gm, dm, st);
+    return inplace ? bwd_by_width<T, ACT, true, true>(p.bytes, dgate, dup, dout, gate, up, p.shape, gm, dm, st)
+                   : bwd_by_width<T, ACT, true, false>(p.bytes, dgate, dup, dout, gate, up, p.shape, gm, dm, st);
   }
-  return inplace ? bwd_by_width<T, false, true>(p.bytes, dgate, dup, dout, gate, up, p.shape, gm, dm, st)
-                 : bwd_by_width<T, false, false>(p.bytes, dgate, dup, dout, gate, up, p.shape, gm, dm, st);
+  return inplace ? bwd_by_width<T, ACT, false, true>(p.bytes, dgate, dup, dout, gate, up, p.shape, gm, dm, st)
+                 : bwd_by_width<T, ACT, false, false>(p.bytes, dgate, dup, dout, gate, up, p.shape, gm, dm, st);
 }
 
 inline unsigned long long addr_of(const void* p) { return (unsigned long long)(uintptr_t)p; }
@@ -269,8 +270,13 @@ int swiglu_b200_last_cuda_error(void) { return t_last_cuda_error; }
 
 uint64_t swiglu_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
-int swiglu_b200_fwd(void* out, const void* gate, const void* up, int64_t rows, int64_t cols, int64_t in_row_stride,
-                    int64_t out_row_stride, int dtype, float gm, float dm, int device, void* stream) {
+}  // extern "C"
+
+namespace {
+
+template <int ACT>
+int fwd_entry(void* out, const void* gate, const void* up, int64_t rows, int64_t cols, int64_t in_row_stride,
+              int64_t out_row_stride, int dtype, float gm, float dm, int device, void* stream) {
   if (dtype != SWIGLU_B200_F32 && dtype != SWIGLU_B200_F16 && dtype != SWIGLU_B200_BF16) return SWIGLU_B200_ERR_DTYPE;
   if (rows < 0 || cols < 0) return SWIGLU_B200_ERR_SHAPE;
   if (rows == 0 || cols == 0) return SWIGLU_B200_OK;
@@ -303,15 +309,16 @@ int swiglu_b200_fwd(void* out, const void* gate, const void* up, int64_t rows, i
   up = advance(up, p.skip);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
-    case SWIGLU_B200_F32: return fwd_typed<float>(p, out, gate, up, gm, dm, st);
-    case SWIGLU_B200_F16: return fwd_typed<__half>(p, out, gate, up, gm, dm, st);
-    default: return fwd_typed<__nv_bfloat16>(p, out, gate, up, gm, dm, st);
+    case SWIGLU_B200_F32: return fwd_typed<float, ACT>(p, out, gate, up, gm, dm, st);
+    case SWIGLU_B200_F16: return fwd_typed<__half, ACT>(p, out, gate, up, gm, dm, st);
+    default: return fwd_typed<__nv_bfloat16, ACT>(p, out, gate, up, gm, dm, st);
   }
 }
 
-int swiglu_b200_bwd(void* dgate, void* dup, const void* dout, const void* gate, const void* up, int64_t rows,
-                    int64_t cols, int64_t in_row_stride, int64_t grad_row_stride, int64_t dout_row_stride, int dtype,
-                    float gm, float dm, int device, void* stream) {
+template <int ACT>
+int bwd_entry(void* dgate, void* dup, const void* dout, const void* gate, const void* up, int64_t rows, int64_t cols,
+              int64_t in_row_stride, int64_t grad_row_stride, int64_t dout_row_stride, int dtype, float gm, float dm,
+              int device, void* stream) {
   if (dtype != SWIGLU_B200_F32 && dtype != SWIGLU_B200_F16 && dtype != SWIGLU_B200_BF16) return SWIGLU_B200_ERR_DTYPE;
   if (rows < 0 || cols < 0) return SWIGLU_B200_ERR_SHAPE;
   if (rows == 0 || cols == 0) return SWIGLU_B200_OK;
@@ -363,10 +370,46 @@ int swiglu_b200_bwd(void* dgate, void* dup, const void* dout, const void* gate, 
   up = advance(up, p.skip);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
-    case SWIGLU_B200_F32: return bwd_typed<float>(p, inplace, dgate, dup, dout, gate, up, gm, dm, st);
-    case SWIGLU_B200_F16: return bwd_typed<__half>(p, inplace, dgate, dup, dout, gate, up, gm, dm, st);
-    default: return bwd_typed<__nv_bfloat16>(p, inplace, dgate, dup, dout, gate, up, gm, dm, st);
+    case SWIGLU_B200_F32: return bwd_typed<float, ACT>(p, inplace, dgate, dup, dout, gate, up, gm, dm, st);
+    case SWIGLU_B200_F16: return bwd_typed<__half, ACT>(p, inplace, dgate, dup, dout, gate, up, gm, dm, st);
+    default: return bwd_typed<__nv_bfloat16, ACT>(p, inplace, dgate, dup, dout, gate, up, gm, dm, st);
   }
+}
+
+}  // namespace
+
+extern "C" {
+
+int swiglu_b200_fwd(void* out, const void* gate, const void* up, int64_t rows, int64_t cols, int64_t in_row_stride,
+                    int64_t out_row_stride, int dtype, float gm, float dm, int device, void* stream) {
+  return fwd_entry<ACT_SILU>(out, gate, up, rows, cols, in_row_stride, out_row_stride, dtype, gm, dm, device, stream);
+}
+
+int swiglu_b200_bwd(void* dgate, void* dup, const void* dout, const void* gate, const void* up, int64_t rows,
+                    int64_t cols, int64_t in_row_stride, int64_t grad_row_stride, int64_t dout_row_stride, int dtype,
+                    float gm, float dm, int device, void* stream) {
+  return bwd_entry<ACT_SILU>(dgate, dup, dout, gate, up, rows, cols, in_row_stride, grad_row_stride, dout_row_stride,
+                             dtype, gm, dm, device, stream);
+}
+
+int swiglu_b200_geglu_fwd(void* out, const void* gate, const void* up, int64_t rows, int64_t cols,
+                          int64_t in_row_stride, int64_t out_row_stride, int dtype, int approximate_tanh, int device,
+                          void* stream) {
+  return approximate_tanh
+             ? fwd_entry<ACT_GELU_TANH>(out, gate, up, rows, cols, in_row_stride, out_row_stride, dtype, 1.0f, 1.0f,
+                                        device, stream)
+             : fwd_entry<ACT_GELU_ERF>(out, gate, up, rows, cols, in_row_stride, out_row_stride, dtype, 1.0f, 1.0f,
+                                       device, stream);
+}
+
+int swiglu_b200_geglu_bwd(void* dgate, void* dup, const void* dout, const void* gate, const void* up, int64_t rows,
+                          int64_t cols, int64_t in_row_stride, int64_t grad_row_stride, int64_t dout_row_stride,
+                          int dtype, int approximate_tanh, int device, void* stream) {
+  return approximate_tanh
+             ? bwd_entry<ACT_GELU_TANH>(dgate, dup, dout, gate, up, rows, cols, in_row_stride, grad_row_stride,
+                                        dout_row_stride, dtype, 1.0f, 1.0f, device, stream)
+             : bwd_entry<ACT_GELU_ERF>(dgate, dup, dout, gate, up, rows, cols, in_row_stride, grad_row_stride,
+                                       dout_row_stride, dtype, 1.0f, 1.0f, device, stream);
 }
 
 }  // extern "C"

@@ -273,7 +273,10 @@ swiglu_gemm_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 // so that the X band and the weight tiles in flight stay in L2.
 namespace pair {
 
-constexpr int STAGES = 6;
+#ifndef SWIGLU_GEMM_PAIR_STAGES
+#define SWIGLU_GEMM_PAIR_STAGES 6
+#endif
+constexpr int STAGES = SWIGLU_GEMM_PAIR_STAGES;
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;              // X tile + one weight tile
 constexpr int ACC_BUFS = 2;
 constexpr int TMEM_COLS = 512;

@@ -245,7 +245,9 @@ template <> struct Codec<__half> {
 // The arithmetic.  FAST selects the approximate transcendental pair used for 16-bit I/O.
 // ---------------------------------------------------------------------------------------
 
-template <bool FAST> struct Math;
+enum Activation : int { ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_GELU_ERF = 2 };
+
+template <bool FAST, int ACT = ACT_SILU> struct Math;
 
 // Per-launch constants derived from the two multipliers, computed once per thread.
 struct Consts {
@@ -258,7 +260,7 @@ struct Consts {
         gm_dm(gm_ * dm_) {}
 };
 
-template <> struct Math<true> {
+template <> struct Math<true, ACT_SILU> {
   // sigmoid(z)/... via r = 1 / ((1 + exp(-z)) / 4).  Dividing the denominator by four (folded into
   // one FMA) keeps r a normal number for every finite exp(-z) <= 2^128, so the flush-to-zero
   // reciprocal loses nothing; the factor 1/4 is multiplied back where it is exact.
@@ -279,7 +281,7 @@ template <> struct Math<true> {
   }
 };
 
-template <> struct Math<false> {
+template <> struct Math<false, ACT_SILU> {
   // Same expression tree as ATen's silu / silu_backward, which is what the reference's
   // torch_swiglu_reference (swiglu.py:179-188) evaluates under autograd.
   static __device__ __forceinline__ float fwd(float g, float u, const Consts& c) {
@@ -295,6 +297,82 @@ template <> struct Math<false> {
     float d = dh * c.dm;
     dup = d * silu;
     dgate = (((d * u) * sig) * (1.0f + z * (1.0f - sig))) * c.gm;
+  }
+};
+
+// ---------------------------------------------------------------------------------------
+// GeGLU (the sibling operator, reference kernels/geglu/geglu.py:90-123): h = gelu(gate) * up with
+// the tanh approximation or the exact erf form; no multipliers.
+//
+// tanh form: 0.5*(1 + tanh(a)) is sigmoid(2a), so gelu_tanh(x) = x * sigmoid(q(x)) with
+// q(x) = 2*sqrt(2/pi)*(x + 0.044715 x^3).  Evaluated that way the negative tail keeps its relative
+// accuracy (1 + tanh cancels there) and the silu machinery is reused:
+//   d/dx = s * (1 + x * (1 - s) * q'(x)),   q'(x) = 2*sqrt(2/pi)*(1 + 3*0.044715 x^2).
+// erf form: Phi(x) = 0.5*erfc(-x/sqrt 2) (erfc, not 1+erf, again for the negative tail),
+//   gelu = x*Phi,  d/dx = Phi + x*exp(-x^2/2)/sqrt(2 pi).
+// ---------------------------------------------------------------------------------------
+
+struct GeluConst {
+  static constexpr float kQ1 = 1.5957691216057308f;    // 2*sqrt(2/pi)
+  static constexpr float kQ3 = 0.07135481627f;         // 2*sqrt(2/pi)*0.044715
+  static constexpr float kLog2e = 1.4426950408889634f;
+  static constexpr float kInvSqrt2 = 0.7071067811865476f;
+  static constexpr float kInvSqrt2Pi = 0.3989422804014327f;
+};
+
+template <> struct Math<true, ACT_GELU_TANH> {
+  // 4*sigmoid(q(x)) by one ex2 and one rcp; see Math<true, ACT_SILU>::quarter_recip.
+  static __device__ __forceinline__ float quarter_recip(float x, float x2) {
+    float e, r;
+    const float t = x * fmaf(x2, -GeluConst::kQ3 * GeluConst::kLog2e, -GeluConst::kQ1 * GeluConst::kLog2e);
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(fmaf(e, 0.25f, 0.25f)));
+    return r;
+  }
+  static __device__ __forceinline__ float fwd(float g, float u, const Consts&) {
+    return ((g * 0.25f) * quarter_recip(g, g * g)) * u;
+  }
+  static __device__ __forceinline__ void bwd(float dh, float g, float u, const Consts&, float& dgate, float& dup) {
+    const float x2 = g * g;
+    const float sig = quarter_recip(g, x2) * 0.25f;
+    dup = dh * (g * sig);
+    const float dq = fmaf(x2, 3.0f * GeluConst::kQ3, GeluConst::kQ1);
+    dgate = (dh * u) * (sig * fmaf(g * (1.0f - sig), dq, 1.0f));
+  }
+};
+
+template <> struct Math<false, ACT_GELU_TANH> {
+  // 1 - s is formed as exp(-q) * s, which keeps its relative accuracy for large positive x (1 - s
+  // itself would carry an absolute error that the derivative multiplies by x * q'(x), over a hundred
+  // for |x| ~ 8); where exp(-q) overflows, s is 0 and 1 - s is 1.
+  static __device__ __forceinline__ float fwd(float g, float u, const Consts&) {
+    const float q = g * fmaf(g * g, GeluConst::kQ3, GeluConst::kQ1);
+    return (g / (1.0f + expf(-q))) * u;
+  }
+  static __device__ __forceinline__ void bwd(float dh, float g, float u, const Consts&, float& dgate, float& dup) {
+    const float x2 = g * g;
+    const float q = g * fmaf(x2, GeluConst::kQ3, GeluConst::kQ1);
+    const float e = expf(-q);
+    const float den = 1.0f + e;
+    const float sig = 1.0f / den;
+    const float one_minus_sig = e < 1e30f ? e * sig : 1.0f;
+    dup = dh * (g / den);
+    const float dq = fmaf(x2, 3.0f * GeluConst::kQ3, GeluConst::kQ1);
+    dgate = (dh * u) * (sig * fmaf(g * one_minus_sig, dq, 1.0f));
+  }
+};
+
+// The exact form uses the accurate erfcf/expf for every I/O type: there is no cheap approximation
+// whose relative error survives in the tail.
+template <bool FAST> struct Math<FAST, ACT_GELU_ERF> {
+  static __device__ __forceinline__ float fwd(float g, float u, const Consts&) {
+    return (g * (0.5f * erfcf(-g * GeluConst::kInvSqrt2))) * u;
+  }
+  static __device__ __forceinline__ void bwd(float dh, float g, float u, const Consts&, float& dgate, float& dup) {
+    const float cdf = 0.5f * erfcf(-g * GeluConst::kInvSqrt2);
+    dup = dh * (g * cdf);
+    const float pdf = GeluConst::kInvSqrt2Pi * expf(-0.5f * g * g);
+    dgate = (dh * u) * fmaf(g, pdf, cdf);
   }
 };
 
@@ -418,7 +496,8 @@ struct Locator {
 // the tile, so each warp-wide access is one contiguous 512- or 1024-byte segment.
 // ---------------------------------------------------------------------------------------
 
-template <class T, int BYTES, bool FAST, bool ROWS, int THREADS, int UNROLL, int LDM, int STM, bool SHIFT = false>
+template <class T, int BYTES, bool FAST, bool ROWS, int THREADS, int UNROLL, int LDM, int STM, bool SHIFT = false,
+          int ACT = ACT_SILU>
 __global__ void __launch_bounds__(THREADS)
 swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const void* __restrict__ up, Shape s,
                   float gm, float dm) {
@@ -463,7 +542,7 @@ swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const v
         Codec<T>::template unpack<BYTES>(g[k], fg);
         Codec<T>::template unpack<BYTES>(u[k], fu);
 #pragma unroll
-        for (int e = 0; e < EPV; ++e) fh[e] = Math<FAST>::fwd(fg[e], fu[e], c);
+        for (int e = 0; e < EPV; ++e) fh[e] = Math<FAST, ACT>::fwd(fg[e], fu[e], c);
         Vec<BYTES> h;
         Codec<T>::template pack<BYTES>(fh, h);
         St<BYTES, STM>::st(byte(out) + oo[k], h);
@@ -485,7 +564,7 @@ swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const v
       float fg[1], fu[1], fh[1];
       Codec<T>::template unpack<ES>(vg, fg);
       Codec<T>::template unpack<ES>(vu, fu);
-      fh[0] = Math<FAST>::fwd(fg[0], fu[0], c);
+      fh[0] = Math<FAST, ACT>::fwd(fg[0], fu[0], c);
       Vec<ES> vh;
       Codec<T>::template pack<ES>(fh, vh);
       St<ES, ST_PLAIN>::st(byte(out) + off, vh);
@@ -499,7 +578,7 @@ swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const v
 // ---------------------------------------------------------------------------------------
 
 template <class T, int BYTES, bool FAST, bool ROWS, int THREADS, int UNROLL, int LDM_DH, int LDM_IO, int STM,
-          bool SHIFT = false>
+          bool SHIFT = false, int ACT = ACT_SILU>
 __global__ void __launch_bounds__(THREADS)
 swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const void* gate, const void* up, Shape s,
                   float gm, float dm) {
@@ -550,7 +629,7 @@ swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const v
         Codec<T>::template unpack<BYTES>(g[k], fg);
         Codec<T>::template unpack<BYTES>(u[k], fu);
 #pragma unroll
-        for (int e = 0; e < EPV; ++e) Math<FAST>::bwd(fd[e], fg[e], fu[e], c, fdg[e], fdu[e]);
+        for (int e = 0; e < EPV; ++e) Math<FAST, ACT>::bwd(fd[e], fg[e], fu[e], c, fdg[e], fdu[e]);
         Vec<BYTES> vdg, vdu;
         Codec<T>::template pack<BYTES>(fdg, vdg);
         Codec<T>::template pack<BYTES>(fdu, vdu);
@@ -573,7 +652,7 @@ swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const v
       Codec<T>::template unpack<ES>(vd, fd);
       Codec<T>::template unpack<ES>(vg, fg);
       Codec<T>::template unpack<ES>(vu, fu);
-      Math<FAST>::bwd(fd[0], fg[0], fu[0], c, fdg[0], fdu[0]);
+      Math<FAST, ACT>::bwd(fd[0], fg[0], fu[0], c, fdg[0], fdu[0]);
       Vec<ES> vdg, vdu;
       Codec<T>::template pack<ES>(fdg, vdg);
       Codec<T>::template pack<ES>(fdu, vdu);

@@ -62,6 +62,12 @@ def lib() -> ctypes.CDLL:
         L.swiglu_oracle_fwd_f64.argtypes = [i, i64, p, p, d, d, p]
         L.swiglu_oracle_bwd_f64.restype = i
         L.swiglu_oracle_bwd_f64.argtypes = [i, i64, p, p, p, d, d, p, p, p]
+        L.geglu_oracle_fwd.restype = i
+        L.geglu_oracle_fwd.argtypes = [i, i, i, i64, p, p, p]
+        L.geglu_oracle_bwd.restype = i
+        L.geglu_oracle_bwd.argtypes = [i, i, i, i64, p, p, p, p, p]
+        L.geglu_oracle_f64.restype = i
+        L.geglu_oracle_f64.argtypes = [i, i, i64, p, p, p, p, p, p, p]
         L.swiglu_oracle_to_f32.restype = None
         L.swiglu_oracle_to_f32.argtypes = [i, i64, p, p]
         L.swiglu_oracle_from_f32.restype = None
@@ -131,6 +137,43 @@ def bwd_f64(dout: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, gm: float 
         "oracle bwd f64",
     )
     return dgate.view(gate.shape), dup.view(gate.shape), scale.view(gate.shape)
+
+
+# GeGLU, the sibling operator (reference kernels/geglu/geglu.py)
+
+def _tanh_flag(approximate: str) -> int:
+    if approximate not in ("tanh", "none"):
+        raise ValueError(approximate)
+    return 1 if approximate == "tanh" else 0
+
+
+def geglu_fwd(gate: torch.Tensor, up: torch.Tensor, approximate: str = "tanh", variant: str = "chain") -> torch.Tensor:
+    g, u = _flat(gate), _flat(up)
+    out = torch.empty_like(g)
+    _check(lib().geglu_oracle_fwd(int(variant == "once"), DTYPE_CODE[gate.dtype], _tanh_flag(approximate), g.numel(),
+                                  g.data_ptr(), u.data_ptr(), out.data_ptr()), "oracle geglu fwd")
+    return out.view(gate.shape)
+
+
+def geglu_bwd(dout: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, approximate: str = "tanh",
+              variant: str = "chain"):
+    d, g, u = _flat(dout), _flat(gate), _flat(up)
+    dgate, dup = torch.empty_like(g), torch.empty_like(u)
+    _check(lib().geglu_oracle_bwd(int(variant == "once"), DTYPE_CODE[gate.dtype], _tanh_flag(approximate), g.numel(),
+                                  d.data_ptr(), g.data_ptr(), u.data_ptr(), dgate.data_ptr(), dup.data_ptr()),
+           "oracle geglu bwd")
+    return dgate.view(gate.shape), dup.view(gate.shape)
+
+
+def geglu_f64(dout: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, approximate: str = "tanh"):
+    """(h, dgate, dup, dgate_scale) as float64."""
+    d, g, u = _flat(dout), _flat(gate), _flat(up)
+    n = g.numel()
+    h, dgate, dup, scale = (torch.empty(n, dtype=torch.float64) for _ in range(4))
+    _check(lib().geglu_oracle_f64(DTYPE_CODE[gate.dtype], _tanh_flag(approximate), n, d.data_ptr(), g.data_ptr(),
+                                  u.data_ptr(), h.data_ptr(), dgate.data_ptr(), dup.data_ptr(), scale.data_ptr()),
+           "oracle geglu f64")
+    return tuple(t.view(gate.shape) for t in (h, dgate, dup, scale))
 
 
 def packed_split(gate_up: torch.Tensor):

@@ -233,6 +233,125 @@ EXPORT int swiglu_oracle_bwd_f64(int dtype, int64_t n, const void* dout, const v
   return 0;
 }
 
+
+/* ------------------------------------------------------------------ GeGLU (sibling operator)
+ * h = gelu(gate) * up, reference kernels/geglu/geglu.py: torch_geglu_reference (:255-263) is
+ * gelu(gate.float(), approximate).to(dtype) * up with the backward by autograd; the Triton kernels
+ * (:90-123, :126-182) use the same formulas.  approximate_tanh != 0 selects the tanh form.
+ * ATen's expressions (activation and derivative):
+ *   tanh:  inner = sqrt(2/pi) * (x + 0.044715 x^3);  gelu = 0.5 x (1 + tanh(inner))
+ *          d/dx  = 0.5 (1 + tanh) + 0.5 x (1 - tanh^2) * sqrt(2/pi) (1 + 3*0.044715 x^2)
+ *   erf:   cdf = 0.5 (1 + erf(x / sqrt 2));  gelu = x cdf;  d/dx = cdf + x exp(-x^2/2)/sqrt(2 pi)
+ * chain = these in fp32 with the reference's rounding points; once = the cancellation-free closed
+ * form (sigmoid / erfc) in fp32 rounded once, the kernels' target; f64 = the truth. */
+
+static inline float gelu_chain_f32(float x, int tanh_form) {
+  if (tanh_form) {
+    const float inner = 0.7978845608028654f * (x + 0.044715f * (x * x * x));
+    return 0.5f * x * (1.0f + tanhf(inner));
+  }
+  return x * (0.5f * (1.0f + erff(x * 0.7071067811865476f)));
+}
+static inline float gelu_grad_chain_f32(float x, int tanh_form) {
+  if (tanh_form) {
+    const float x2 = x * x;
+    const float inner = 0.7978845608028654f * (x + 0.044715f * (x2 * x));
+    const float t = tanhf(inner);
+    const float left_derivative = 0.5f * (1.0f + t);
+    const float right_derivative = (0.5f * x) * (1.0f - t * t) * (0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x2));
+    return left_derivative + right_derivative;
+  }
+  const float cdf = 0.5f * (1.0f + erff(x * 0.7071067811865476f));
+  const float pdf = expf(-0.5f * x * x) * 0.3989422804014327f;
+  return cdf + x * pdf;
+}
+static inline void gelu_once_f32(float x, int tanh_form, float* act, float* grad) {
+  if (tanh_form) {
+    const float x2 = x * x;
+    const float q = x * (1.5957691216057308f + 0.07135481627f * x2);
+    const float e = expf(-q);
+    const float den = 1.0f + e;
+    const float sig = 1.0f / den;
+    const float one_minus_sig = e < 1e30f ? e * sig : 1.0f; /* accurate for large x; no inf * 0 */
+    *act = x / den;
+    *grad = sig * (1.0f + (x * one_minus_sig) * (1.5957691216057308f + 3.0f * 0.07135481627f * x2));
+  } else {
+    const float cdf = 0.5f * erfcf(-x * 0.7071067811865476f);
+    *act = x * cdf;
+    *grad = cdf + x * (0.3989422804014327f * expf(-0.5f * x * x));
+  }
+}
+static inline void gelu_f64(double x, int tanh_form, double* act, double* grad) {
+  if (tanh_form) {
+    const double q = 2.0 * 0.7978845608028654 * (x + 0.044715 * x * x * x);
+    const double sig = 1.0 / (1.0 + exp(-q));
+    *act = x * sig;
+    *grad = sig * (1.0 + x * (1.0 - sig) * 2.0 * 0.7978845608028654 * (1.0 + 3.0 * 0.044715 * x * x));
+  } else {
+    const double cdf = 0.5 * erfc(-x * 0.7071067811865476);
+    *act = x * cdf;
+    *grad = cdf + x * 0.3989422804014327 * exp(-0.5 * x * x);
+  }
+}
+
+EXPORT int geglu_oracle_fwd(int variant_once, int dtype, int tanh_form, int64_t n, const void* gate, const void* up,
+                            void* out) {
+  if (bad_dtype(dtype) || n < 0) return 1;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    const float g = load_elem(dtype, gate, i), u = load_elem(dtype, up, i);
+    if (variant_once) {
+      float a, d;
+      gelu_once_f32(g, tanh_form, &a, &d);
+      store_elem(dtype, out, i, a * u);
+    } else {
+      const float a = round_io(dtype, gelu_chain_f32(g, tanh_form));   /* gelu(...).to(dtype)  geglu.py:262 */
+      store_elem(dtype, out, i, a * u);                                /* activated * up       geglu.py:263 */
+    }
+  }
+  return 0;
+}
+
+EXPORT int geglu_oracle_bwd(int variant_once, int dtype, int tanh_form, int64_t n, const void* dout, const void* gate,
+                            const void* up, void* dgate, void* dup) {
+  if (bad_dtype(dtype) || n < 0) return 1;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    const float g = load_elem(dtype, gate, i), u = load_elem(dtype, up, i), d = load_elem(dtype, dout, i);
+    float dg, du;
+    if (variant_once) {
+      float a, gr;
+      gelu_once_f32(g, tanh_form, &a, &gr);
+      du = d * a;
+      dg = (d * u) * gr;
+    } else {
+      const float a = round_io(dtype, gelu_chain_f32(g, tanh_form));
+      du = d * a;                                  /* grad of up: dout * activated (in the I/O dtype) */
+      const float da = round_io(dtype, d * u);     /* grad of activated, rounded by autograd          */
+      dg = da * gelu_grad_chain_f32(g, tanh_form); /* gelu_backward in fp32, then cast                */
+    }
+    store_elem(dtype, dgate, i, dg);
+    store_elem(dtype, dup, i, du);
+  }
+  return 0;
+}
+
+EXPORT int geglu_oracle_f64(int dtype, int tanh_form, int64_t n, const void* dout, const void* gate, const void* up,
+                            double* h, double* dgate, double* dup, double* dgate_scale) {
+  if (bad_dtype(dtype) || n < 0) return 1;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    const double g = load_elem(dtype, gate, i), u = load_elem(dtype, up, i), d = load_elem(dtype, dout, i);
+    double a, gr;
+    gelu_f64(g, tanh_form, &a, &gr);
+    h[i] = a * u;
+    dup[i] = d * a;
+    dgate[i] = d * u * gr;
+    dgate_scale[i] = fabs(d * u);
+  }
+  return 0;
+}
+
 /* ------------------------------------------------------------------ codec access for tests */
 
 EXPORT void swiglu_oracle_to_f32(int dtype, int64_t n, const void* in, float* out) {

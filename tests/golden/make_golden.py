@@ -130,6 +130,36 @@ def main() -> None:
         out[f"{name}_meanabs"] = np.array(flat.double().abs().mean().item())
     np.savez_compressed(HERE / "config1.npz", **out)
 
+    # --- GeGLU sibling: reference tests/test_geglu.py:32-103 (shapes reduced), both GELU forms -----------
+    import kernels.geglu as ref_geglu
+
+    assert Path(ref_geglu.__file__).resolve().is_relative_to(Path(args.reference).resolve())
+    out = {}
+    for dname, dtype in DTYPES.items():
+        for approximate in ("tanh", "none"):
+            for shape in [(2, 8, 128), (1, 3, 257)]:
+                torch.manual_seed(0)
+                gate = (1.5 * torch.randn(*shape)).to(dtype)
+                up = torch.randn(*shape, dtype=dtype)
+                dout = torch.randn(*shape, dtype=dtype)
+                g = gate.detach().clone().requires_grad_(True)
+                u = up.detach().clone().requires_grad_(True)
+                h = ref_geglu.geglu(g, u, approximate)
+                h.backward(dout)
+                key = f"{dname}|{'x'.join(map(str, shape))}|{approximate}"
+                for name, t in dict(gate=gate, up=up, dout=dout, h=h.detach(), dgate=g.grad, dup=u.grad).items():
+                    out[f"{key}|{name}"] = bits(t)
+            torch.manual_seed(1)
+            gate_up = torch.randn(1, 3, 514, dtype=dtype)
+            dout = torch.randn(1, 3, 257, dtype=dtype)
+            gu = gate_up.detach().clone().requires_grad_(True)
+            h = ref_geglu.geglu_packed(gu, approximate)
+            h.backward(dout)
+            key = f"{dname}|packed|{approximate}"
+            for name, t in dict(gate_up=gate_up, dout=dout, h=h.detach(), dgate_up=gu.grad).items():
+                out[f"{key}|{name}"] = bits(t)
+    np.savez_compressed(HERE / "geglu.npz", **out)
+
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size, "bytes")
 
