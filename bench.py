@@ -55,7 +55,7 @@ def parse_args():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--preserve-inputs", action="store_true", help="out-of-place backward instead of the default in-place")
     ap.add_argument("--e2e-steps", type=int, default=5)
-    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the cpu_baseline leg")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="time limit of the cpu_baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -171,7 +171,7 @@ def cpu_sample_rows(w) -> int:
     return min(w.tokens, rows)
 
 
-def time_cpu_path(w, budget_s: float, min_steps: int = 3, fixed_steps: int | None = None, warmup: int = 1):
+def time_cpu_path(w, limit_s: float, min_steps: int = 3, fixed_steps: int | None = None, warmup: int = 1):
     """tokens/s of fwd+bwd on the host for a row sample of workload ``w``."""
     from kernel_pocs_b200 import workloads as W
     from oracle import oracle as O
@@ -189,7 +189,7 @@ def time_cpu_path(w, budget_s: float, min_steps: int = 3, fixed_steps: int | Non
         if fixed_steps is not None:
             if len(times) >= fixed_steps:
                 break
-        elif len(times) >= min_steps and time.perf_counter() - t_begin > budget_s:
+        elif len(times) >= min_steps and time.perf_counter() - t_begin > limit_s:
             break
     sec = sum(times) / len(times)
     return {

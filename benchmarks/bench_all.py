@@ -222,7 +222,7 @@ def tensor_peak():
 
 
 def run_c4(args, device):
-    """Fused gate/up projection + SwiGLU (BASELINE configuration 4): X [16384, 4096] ~ N(0,1),
+    """Fused gate/up projection + SwiGLU (benchmark configuration c4): X [16384, 4096] ~ N(0,1),
     W_gate, W_up [14336, 4096] ~ N(0, 0.02^2), bf16, seed 3; dh ~ N(0,1) for the backward.
     FLOPs: forward 4*M*N*K (two GEMMs), backward 8*M*N*K (dX: two GEMMs, dW_gate, dW_up)."""
     from kernel_pocs_b200.fused_mlp import check_status, fused_gate_up_swiglu, gate_up_swiglu_forward

@@ -1,6 +1,6 @@
 """Writes tests/golden/*.npz by running the REFERENCE ITSELF on the host.
 
-    python tests/golden/make_golden.py [--reference /path/to/kernel-POCs]
+    python tests/golden/make_golden.py --reference /path/to/kernel-POCs
 
 Imports ``kernels.swiglu`` from a checkout of Forge-researchlab/kernel-POCs and calls its own
 ``swiglu`` / ``swiglu_packed`` on CPU tensors (for which it evaluates torch_swiglu_reference,
@@ -50,7 +50,7 @@ def run_packed(ref, gate_up, dout, gm, dm):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of Forge-researchlab/kernel-POCs")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     import kernels.swiglu as ref  # the reference package, not this repository's drop-in
