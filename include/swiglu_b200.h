@@ -169,6 +169,22 @@ SWIGLU_B200_API int swiglu_b200_gemm_fwd(void* h, void* gate_out, void* up_out, 
 SWIGLU_B200_API int swiglu_b200_gemm_fwd_noalloc(void* h, const void* x, const void* w_gate, const void* w_up, int64_t m, int64_t n,
                                  int64_t k, float gm, float dm, int* status_host, int device, void* stream);
 
+/* Backward GEMMs of the fused projection, from dgate/dup (the outputs of swiglu_b200_bwd on the
+ * saved pre-activations):
+ *     dx      [m, k] = dgate . w_gate + dup . w_up        (skipped when dx is NULL)
+ *     dw_gate [n, k] = dgate^T . x,  dw_up [n, k] = dup^T . x   (both NULL to skip, or both given)
+ * bf16 in and out, fp32 accumulation on the tcgen05 tensor cores, no transposed copies.  In the
+ * reference these are the cuBLAS GEMMs autograd derives for down_proj(swiglu(gate_proj(x), up_proj(x)))
+ * (forge/forge/patching/kernels/basic.py:97-102).  dgate, dup: m x n; x: m x k; w_gate, w_up: n x k;
+ * all row-major and 16-byte aligned; requires k % 16 == 0 and n % 8 == 0.  `status` as in
+ * swiglu_b200_gemm_fwd (one word serves both launches). */
+SWIGLU_B200_API int swiglu_b200_gemm_bwd(void* dx, void* dw_gate, void* dw_up, const void* dgate, const void* dup, const void* x,
+                         const void* w_gate, const void* w_up, int64_t m, int64_t n, int64_t k, void* status,
+                         int device, void* stream);
+
+/* Number of backward-GEMM kernels launched by this process. */
+SWIGLU_B200_API uint64_t swiglu_b200_gemm_bwd_launch_count(void);
+
 /* Number of fused-GEMM kernels launched by this process. */
 SWIGLU_B200_API uint64_t swiglu_b200_gemm_launch_count(void);
 

@@ -59,6 +59,12 @@ SIGNATURES = {
          ctypes.c_int, _c_ptr],
     ),
     "swiglu_b200_gemm_launch_count": (ctypes.c_uint64, []),
+    "swiglu_b200_gemm_bwd": (
+        ctypes.c_int,
+        [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr,
+         ctypes.c_int, _c_ptr],
+    ),
+    "swiglu_b200_gemm_bwd_launch_count": (ctypes.c_uint64, []),
 }
 
 

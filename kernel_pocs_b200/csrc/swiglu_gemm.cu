@@ -32,8 +32,11 @@
 #include <mutex>
 
 #include "swiglu_kernels.cuh"
+#include "tcgen05_common.cuh"
 
 namespace {
+
+using namespace swiglu_b200::tc;
 
 using swiglu_b200::Consts;
 using swiglu_b200::Math;
@@ -48,73 +51,9 @@ constexpr int STAGE_BYTES = 3 * TILE_BYTES;              // 48 KiB
 constexpr int TMEM_COLS = 256;                           // 128 gate + 128 up fp32 columns
 constexpr int THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr long long WAIT_CYCLES = 1000000000LL;          // ~0.5 s of SM clock per wait
 
 // tcgen05 instruction descriptor, kind::f16: D fp32, A and B bf16, both K-major, M=128, N=256.
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* b, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-      : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
-  return ok != 0;
-}
-
-// Bounded wait.  Returns false when the barrier did not flip within WAIT_CYCLES or when another
-// thread has already reported a failure; the first failure stores `code` in *status.
-__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int* status, int code) {
-  if (mbar_try_wait(b, parity)) return true;
-  const long long t0 = clock64();
-  for (int spin = 0;; ++spin) {
-    if (mbar_try_wait(b, parity)) return true;
-    if ((spin & 63) == 63) {
-      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
-      if (clock64() - t0 > WAIT_CYCLES) {
-        atomicCAS(status, 0, code);
-        return false;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row groups
-// 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-  return (uint64_t)((smem_addr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
-         (2ull << 61);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
-  asm volatile(
-      "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
-      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(IDESC), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr) : "memory");
-}
 
 struct GemmParams {
   __nv_bfloat16* h;
@@ -192,7 +131,7 @@ swiglu_gemm_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 #pragma unroll
         for (int kk = 0; kk < BK / UMMA_K; ++kk) {
           // 16 K elements = 32 bytes = 2 descriptor address units further along each 128-byte row
-          umma_bf16(tmem_base, a_desc + 2 * kk, b_desc + 2 * kk, (kb | kk) != 0);
+          umma_bf16(tmem_base, a_desc + 2 * kk, b_desc + 2 * kk, IDESC, (kb | kk) != 0);
         }
         umma_commit(&empty[s]);  // arrives once these MMAs have finished reading the stage
       }
@@ -283,72 +222,6 @@ constexpr int TMEM_COLS = 512;
 constexpr int BAND = 8;                                  // row-tiles (of 256 rows) per band
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
-
-__device__ __forceinline__ uint32_t cta_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// arrive (optionally announcing transaction bytes) on a barrier given by its cluster-window address
-__device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// No cluster-scope release here: the producer has written nothing the leader must see, and a
-// cluster-scope release per K block stalled the producer thread.
-__device__ __forceinline__ void remote_expect_tx(uint32_t cluster_addr, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool try_wait_cluster(uint64_t* b, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{ .reg .pred p; mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-      : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
-  return ok != 0;
-}
-template <bool CLUSTER_SCOPE>
-__device__ __forceinline__ bool wait(uint64_t* b, uint32_t parity, int* status, int code) {
-  auto poll = [&] { return CLUSTER_SCOPE ? try_wait_cluster(b, parity) : mbar_try_wait(b, parity); };
-  if (poll()) return true;
-  const long long t0 = clock64();
-  for (int spin = 0;; ++spin) {
-    if (poll()) return true;
-    if ((spin & 63) == 63) {
-      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
-      if (clock64() - t0 > WAIT_CYCLES) {
-        atomicCAS(status, 0, code);
-        return false;
-      }
-    }
-  }
-}
-// tiled load whose completion bytes are credited to a barrier of the pair's leader CTA
-__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y,
-                                                 uint32_t leader_bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(leader_bar) : "memory");
-}
-__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
-  asm volatile(
-      "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p; }"
-      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(IDESC), "r"(accumulate) : "memory");
-}
-// arrives on the barrier at this shared-memory offset in BOTH CTAs once the MMAs issued so far are done
-__device__ __forceinline__ void commit_both(uint64_t* bar) {
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-      ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
-}
 
 struct TileWalk {
   long long tiles_m, tiles_n, total;
@@ -451,7 +324,7 @@ swiglu_gemm_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __g
           const uint64_t a_desc = umma_desc(a_addr);
           const uint64_t b_desc = umma_desc(a_addr + TILE_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk) umma_pair(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, (kb | kk) != 0);
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) umma_pair(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, IDESC, (kb | kk) != 0);
           commit_both(&empty[s]);
         }
         if (ok) commit_both(&acc_full[b]);
@@ -529,37 +402,6 @@ swiglu_gemm_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __g
 }  // namespace pair
 
 // ------------------------------------------------------------------------------------------ host
-
-using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-  static std::once_flag once;
-  static EncodeTiled fn = nullptr;
-  std::call_once(once, [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiled>(sym);
-  });
-  return fn;
-}
-
-// [rows, k] bf16 row-major matrix, boxes of 128 rows x 64 K elements, 128-byte swizzle, zero fill
-// outside the matrix.
-bool make_map(CUtensorMap* map, const void* base, long long rows, long long k) {
-  EncodeTiled enc = encode_fn();
-  if (!enc) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-  cuuint32_t box[2] = {BK, BM};
-  cuuint32_t elem[2] = {1, 1};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
 
 std::atomic<uint64_t> g_gemm_launches{0};
 

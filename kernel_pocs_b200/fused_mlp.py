@@ -4,8 +4,9 @@ tcgen05 kernel (``swiglu_b200_gemm_fwd`` in the C ABI), bf16 in, fp32 accumulati
 This is the step in front of the activation path in the reference's patched MLP
 (forge/forge/patching/kernels/basic.py:97-102 computes ``swiglu(gate_proj(x), up_proj(x))`` with two
 cuBLAS GEMMs and one activation kernel); fusing it removes the write and re-read of both
-pre-activation matrices.  The backward is composed from this library's SwiGLU backward kernel and
-PyTorch matmuls (cuBLAS): dgate/dup from (dh, gate, up), then dx, dw_gate, dw_up.
+pre-activation matrices.  The backward is this library's SwiGLU backward kernel on the saved
+pre-activations (dgate/dup from dh, gate, up) followed by its tcgen05 backward GEMMs for dx, dw_gate and
+dw_up (``SWIGLU_B200_GEMM_BWD=cublas`` selects PyTorch matmuls instead, for comparison).
 """
 from __future__ import annotations
 
@@ -78,6 +79,37 @@ def gate_up_swiglu_forward(x, w_gate, w_up, gate_multiplier=1.0, down_multiplier
     return h
 
 
+def gate_up_swiglu_backward_gemms(dgate, dup, x, w_gate, w_up, need_dx=True, need_dw=True):
+    """``(dx, dw_gate, dw_up)`` from the activation gradients, by this library's tcgen05 kernels
+    (``swiglu_b200_gemm_bwd``); entries that are not needed are ``None``."""
+    n, k = w_gate.shape
+    x2 = x.contiguous().view(-1, k)
+    m = x2.shape[0]
+    dgate, dup = dgate.contiguous().view(m, n), dup.contiguous().view(m, n)
+    wg, wu = w_gate.contiguous(), w_up.contiguous()
+    dx = torch.empty_like(x2) if need_dx else None
+    dwg = torch.empty_like(wg) if need_dw else None
+    dwu = torch.empty_like(wu) if need_dw else None
+    if not (need_dx or need_dw):
+        return None, None, None
+    _lib.check(
+        "gate_up_swiglu_backward_gemms",
+        _lib.lib.swiglu_b200_gemm_bwd(
+            dx.data_ptr() if need_dx else None, dwg.data_ptr() if need_dw else None,
+            dwu.data_ptr() if need_dw else None, dgate.data_ptr(), dup.data_ptr(), x2.data_ptr(), wg.data_ptr(),
+            wu.data_ptr(), m, n, k, _status(x.device).data_ptr(), x.device.index,
+            torch.cuda.current_stream(x.device).cuda_stream,
+        ),
+    )
+    return (dx.view(x.shape) if need_dx else None), dwg, dwu
+
+
+def _own_backward_gemms(n: int, k: int) -> bool:
+    import os
+
+    return os.environ.get("SWIGLU_B200_GEMM_BWD", "own") != "cublas" and k % 16 == 0 and n % 8 == 0
+
+
 class FusedGateUpSwiGLUFunction(torch.autograd.Function):
     """``apply(x, w_gate, w_up, gate_multiplier=1.0, down_multiplier=1.0)``."""
 
@@ -95,6 +127,11 @@ class FusedGateUpSwiGLUFunction(torch.autograd.Function):
         n, k = w_gate.shape
         # gate/up are private to this node, so the in-place backward is safe
         dgate, dup = swiglu_backward(dh.reshape(-1, n), gate, up, ctx.gate_multiplier, ctx.down_multiplier, False)
+        if _own_backward_gemms(n, k):
+            need_dw = ctx.needs_input_grad[1] or ctx.needs_input_grad[2]
+            dx, dw_gate, dw_up = gate_up_swiglu_backward_gemms(dgate, dup, x, w_gate, w_up,
+                                                               ctx.needs_input_grad[0], need_dw)
+            return dx, dw_gate, dw_up, None, None
         x2 = x.reshape(-1, k)
         dx = dw_gate = dw_up = None
         if ctx.needs_input_grad[0]:

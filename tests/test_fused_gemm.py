@@ -138,3 +138,30 @@ def test_single_cta_kernel_variant_agrees():
         outs.append(torch.load(path))
         os.unlink(path)
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 128, 256), (512, 256, 512), (300, 136, 80), (1000, 2064, 1040),
+                                   (4096, 1408, 1024)])
+def test_backward_gemms_match_fp32_reference(m, n, k):
+    """dx, dw_gate, dw_up from the tcgen05 backward kernels (operands whose contiguous dimension is not the
+    contraction dimension, i.e. MN-major shared-memory descriptors) against fp32 matmuls of the same bf16
+    operands; one bf16 rounding plus accumulation noise relative to the spread of the result."""
+    g = torch.Generator(device=DEVICE).manual_seed(5)
+    x = torch.randn(m, k, generator=g, device=DEVICE).bfloat16()
+    wg = (0.05 * torch.randn(n, k, generator=g, device=DEVICE)).bfloat16()
+    wu = (0.05 * torch.randn(n, k, generator=g, device=DEVICE)).bfloat16()
+    dgate = torch.randn(m, n, generator=g, device=DEVICE).bfloat16()
+    dup = torch.randn(m, n, generator=g, device=DEVICE).bfloat16()
+    before = _lib.lib.swiglu_b200_gemm_bwd_launch_count()
+    dx, dwg, dwu = F.gate_up_swiglu_backward_gemms(dgate, dup, x, wg, wu)
+    F.check_status(x.device)
+    assert _lib.lib.swiglu_b200_gemm_bwd_launch_count() == before + 2
+    assert_close_bf16(dx, dgate.float() @ wg.float() + dup.float() @ wu.float(), "dx")
+    assert_close_bf16(dwg, dgate.float().t() @ x.float(), "dw_gate")
+    assert_close_bf16(dwu, dup.float().t() @ x.float(), "dw_up")
+    # either half on its own
+    dx2, none_g, none_u = F.gate_up_swiglu_backward_gemms(dgate, dup, x, wg, wu, need_dw=False)
+    assert none_g is None and none_u is None and torch.equal(dx2, dx)
+    none_x, dwg2, dwu2 = F.gate_up_swiglu_backward_gemms(dgate, dup, x, wg, wu, need_dx=False)
+    F.check_status(x.device)
+    assert none_x is None and torch.equal(dwg2, dwg) and torch.equal(dwu2, dwu)
