@@ -516,3 +516,43 @@ def test_inputs_skewed_against_each_other(dname, offsets, n):
         dg2, du2 = swiglu_backward(dout, g2, u2, 0.8, 1.25)
         assert dg2.data_ptr() == g2.data_ptr()
         assert torch.equal(dg2, dgate) and torch.equal(du2, dup)
+
+
+@pytest.mark.parametrize("name", ["c2", "c5"])
+def test_full_size_workloads(name):
+    """The benchmark configurations at their FULL sizes (c2: bf16 [32768, 14336]; c5: bf16 [65536, 28672],
+    3.76 GB per tensor, so byte offsets pass 2^32): sampled token rows from the start, the middle and the very
+    end against the oracle, and size-independent properties -- in place == out of place, a row range computed
+    on its own == the same rows of the whole (the multi-GPU partition), dup linear in dh."""
+    from kernel_pocs_b200 import workloads as W
+
+    w = W.workloads()[name]
+    need = 7 * w.tokens * w.width * 2
+    free, _total = torch.cuda.mem_get_info()
+    if free < need + (4 << 30):
+        pytest.skip(f"needs {need / 2**30:.0f} GiB of device memory")
+    gate, up, dh = W.generate_rows(w, 0, w.tokens, DEVICE)
+    h = swiglu_forward(gate, up)[0]
+    dgate, dup = swiglu_backward(dh, gate, up, preserve_inputs=True)
+    rows = torch.tensor([0, 1, w.tokens // 2 - 1, w.tokens // 2, w.tokens - 2, w.tokens - 1], device=DEVICE)
+    check_against_oracle(h[rows], dgate[rows], dup[rows], gate[rows].cpu(), up[rows].cpu(), dh[rows].cpu(), 1.0, 1.0,
+                         f"{name} sampled rows")
+    # a shard of rows that starts beyond the 4 GiB mark (for c5) computed on its own
+    lo, hi = W.row_shard(w.tokens, 8, 7)
+    hs = swiglu_forward(gate[lo:hi], up[lo:hi])[0]
+    dgs, dus = swiglu_backward(dh[lo:hi], gate[lo:hi], up[lo:hi], preserve_inputs=True)
+    assert torch.equal(hs, h[lo:hi]) and torch.equal(dgs, dgate[lo:hi]) and torch.equal(dus, dup[lo:hi])
+    del hs, dgs, dus
+    # the generator reproduces the shard bit for bit on its own (what each GPU of a multi-GPU run holds)
+    g2, u2, d2 = W.generate_rows(w, lo, hi, DEVICE)
+    assert torch.equal(g2, gate[lo:hi]) and torch.equal(u2, up[lo:hi]) and torch.equal(d2, dh[lo:hi])
+    del g2, u2, d2
+    # linearity of dup in dh (exact for a power-of-two factor), then in place == out of place
+    dh.mul_(2)
+    _, dup2 = swiglu_backward(dh, gate, up, preserve_inputs=True)
+    dh.mul_(0.5)
+    assert torch.equal(dup2, dup * 2)
+    del dup2
+    dg_inplace, du_inplace = swiglu_backward(dh, gate, up)  # overwrites gate/up
+    assert dg_inplace.data_ptr() == gate.data_ptr()
+    assert torch.equal(dg_inplace, dgate) and torch.equal(du_inplace, dup)
