@@ -93,6 +93,21 @@ SWIGLU_B200_API int swiglu_b200_bwd(void* dgate, void* dup, const void* dout, co
                     int64_t cols, int64_t in_row_stride, int64_t grad_row_stride, int64_t dout_row_stride, int dtype,
                     float gm, float dm, int device, void* stream);
 
+/* Dry run of the access planning of swiglu_b200_fwd / swiglu_b200_bwd (and their GeGLU twins): which
+ * access width and addressing a call with these pointers and strides would use.  No CUDA call is made and
+ * no memory is touched, so the host-side planning can be tested without a device.  No counterpart in the
+ * reference (Triton picks its own vector widths).  Returns, when >= 0:
+ *   bits 0-7   access width of the body in bytes (16, 8, 4 or 2)
+ *   bit  8     pitched-row addressing (a row stride differs from cols)
+ *   bit  9     inputs skewed against the outputs: aligned loads + shuffle + funnel shift
+ *   bits 16-23 scalar elements peeled in front of the body, bits 24-31 scalar elements in front and behind
+ * and when < 0 the negated SWIGLU_B200_ERR_* code the real call would return for these arguments. */
+SWIGLU_B200_API int swiglu_b200_plan_fwd(const void* out, const void* gate, const void* up, int64_t rows, int64_t cols,
+                         int64_t in_row_stride, int64_t out_row_stride, int dtype);
+SWIGLU_B200_API int swiglu_b200_plan_bwd(const void* dgate, const void* dup, const void* dout, const void* gate, const void* up,
+                         int64_t rows, int64_t cols, int64_t in_row_stride, int64_t grad_row_stride,
+                         int64_t dout_row_stride, int dtype);
+
 /* GeGLU, the sibling operator: h = gelu(gate) * up and its backward, with the tanh approximation
  * (approximate_tanh != 0) or the exact erf form.  Same layouts, strides, aliasing rule and
  * return codes as swiglu_b200_fwd / swiglu_b200_bwd; there are no multipliers.  They replace the

@@ -33,6 +33,11 @@ SIGNATURES = {
         [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, ctypes.c_int,
          ctypes.c_float, ctypes.c_float, ctypes.c_int, _c_ptr],
     ),
+    "swiglu_b200_plan_fwd": (ctypes.c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_i64, ctypes.c_int]),
+    "swiglu_b200_plan_bwd": (
+        ctypes.c_int,
+        [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, ctypes.c_int],
+    ),
     "swiglu_b200_geglu_fwd": (
         ctypes.c_int,
         [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_i64, ctypes.c_int, ctypes.c_int, ctypes.c_int, _c_ptr],

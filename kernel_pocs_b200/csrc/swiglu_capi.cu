@@ -412,4 +412,37 @@ int swiglu_b200_geglu_bwd(void* dgate, void* dup, const void* dout, const void* 
                                        dout_row_stride, dtype, 1.0f, 1.0f, device, stream);
 }
 
+// Reports, without launching anything, how a forward / backward call with these addresses and strides
+// would be executed: bits 0-7 the access width in bytes, bit 8 pitched-row addressing, bit 9 the
+// skewed-load kernel, bits 16-23 the scalar head elements, bits 24-31 head + tail scalar elements.
+// Negative: the argument error the real call would return, negated.
+int swiglu_b200_plan_fwd(const void* out, const void* gate, const void* up, int64_t rows, int64_t cols,
+                         int64_t in_row_stride, int64_t out_row_stride, int dtype) {
+  if (dtype != SWIGLU_B200_F32 && dtype != SWIGLU_B200_F16 && dtype != SWIGLU_B200_BF16) return -SWIGLU_B200_ERR_DTYPE;
+  if (rows <= 0 || cols <= 0 || in_row_stride < cols || out_row_stride < cols) return -SWIGLU_B200_ERR_SHAPE;
+  const int es = elem_size(dtype);
+  if (addr_of(out) % es || addr_of(gate) % es || addr_of(up) % es) return -SWIGLU_B200_ERR_ALIGN;
+  const unsigned long long outs[1] = {addr_of(out)};
+  const unsigned long long ins[2] = {addr_of(gate), addr_of(up)};
+  const long long pitch[2] = {in_row_stride, out_row_stride};
+  const Plan p = make_plan(outs, 1, ins, 2, pitch, 2, rows, cols, es);
+  return p.bytes | (p.rows ? 1 << 8 : 0) | (p.shift ? 1 << 9 : 0) | (p.shape.head << 16) | (p.shape.edge << 24);
+}
+
+int swiglu_b200_plan_bwd(const void* dgate, const void* dup, const void* dout, const void* gate, const void* up,
+                         int64_t rows, int64_t cols, int64_t in_row_stride, int64_t grad_row_stride,
+                         int64_t dout_row_stride, int dtype) {
+  if (dtype != SWIGLU_B200_F32 && dtype != SWIGLU_B200_F16 && dtype != SWIGLU_B200_BF16) return -SWIGLU_B200_ERR_DTYPE;
+  if (rows <= 0 || cols <= 0 || in_row_stride < cols || grad_row_stride < cols || dout_row_stride < cols)
+    return -SWIGLU_B200_ERR_SHAPE;
+  const int es = elem_size(dtype);
+  if (addr_of(dgate) % es || addr_of(dup) % es || addr_of(dout) % es || addr_of(gate) % es || addr_of(up) % es)
+    return -SWIGLU_B200_ERR_ALIGN;
+  const unsigned long long outs[2] = {addr_of(dgate), addr_of(dup)};
+  const unsigned long long ins[3] = {addr_of(dout), addr_of(gate), addr_of(up)};
+  const long long pitch[3] = {in_row_stride, grad_row_stride, dout_row_stride};
+  const Plan p = make_plan(outs, 2, ins, 3, pitch, 3, rows, cols, es);
+  return p.bytes | (p.rows ? 1 << 8 : 0) | (p.shift ? 1 << 9 : 0) | (p.shape.head << 16) | (p.shape.edge << 24);
+}
+
 }  // extern "C"

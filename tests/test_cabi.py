@@ -100,3 +100,44 @@ def test_check_raises_with_code():
     with pytest.raises(_lib.SwigluB200Error, match="unsupported dtype") as info:
         _lib.check("here", 1)
     assert info.value.code == 1
+
+
+def _plan(v):
+    return {"bytes": v & 0xff, "rows": bool(v & 0x100), "shift": bool(v & 0x200), "head": (v >> 16) & 0xff,
+            "edge": (v >> 24) & 0xff}
+
+
+def test_access_planning_without_a_device():
+    """Which access width, addressing and edge handling a call would get, from its addresses alone."""
+    f, b = _lib.lib.swiglu_b200_plan_fwd, _lib.lib.swiglu_b200_plan_bwd
+    A = 0x7f0000000000  # a 16-byte aligned "allocation"; nothing is dereferenced
+    G, U, O, D = A, A + (1 << 32), A + (2 << 32), A + (3 << 32)
+    BF, F32 = _lib.BF16, _lib.F32
+    # the benchmark shape: flat, 16-byte vectors, no edges
+    assert _plan(f(O, G, U, 32768, 14336, 14336, 14336, BF)) == dict(bytes=16, rows=False, shift=False, head=0, edge=0)
+    # odd width, aligned bases: still flat 16-byte vectors; 3 * 11009 = 33027 = 8 * 4128 + 3 tail elements
+    assert _plan(f(O, G, U, 3, 11009, 11009, 11009, BF)) == dict(bytes=16, rows=False, shift=False, head=0, edge=3)
+    # every tensor 2 bytes past a boundary: 7 head elements, then vectors
+    p = _plan(f(O + 2, G + 2, U + 2, 1, 1000, 1000, 1000, BF))
+    assert (p["bytes"], p["shift"], p["head"]) == (16, False, 7) and p["edge"] == 7 + (1000 - 7) % 8
+    # inputs skewed against an aligned output: skewed-load kernel, no head
+    assert _plan(f(O, G + 2, U + 6, 4, 4096, 4096, 4096, BF)) == dict(bytes=16, rows=False, shift=True, head=0, edge=0)
+    assert _plan(f(O, G + 4, U, 4, 4096, 4096, 4096, F32)) == dict(bytes=16, rows=False, shift=True, head=0, edge=0)
+    # packed gate|up: pitched rows; even half-width keeps 16 bytes, an odd one drops to the element size
+    assert _plan(f(O, G, G + 2 * 5504, 8, 5504, 11008, 5504, BF)) == dict(bytes=16, rows=True, shift=False, head=0, edge=0)
+    assert _plan(f(O, G, G + 2 * 257, 3, 257, 514, 257, BF))["bytes"] == 2
+    assert _plan(f(O, G, G + 4 * 257, 3, 257, 514, 257, F32))["bytes"] == 4
+    assert _plan(f(O, G, G + 2 * 260, 3, 260, 520, 260, BF))["bytes"] == 8
+    # a single row is flat whatever its stride says
+    assert not _plan(f(O, G, U, 1, 100, 4000, 100, BF))["rows"]
+    # backward in place: outputs are gate/up; dh skewed against them -> skewed loads for dh only
+    assert _plan(b(G, U, D + 10, G, U, 16, 512, 512, 512, 512, BF)) == dict(bytes=16, rows=False, shift=True, head=0, edge=0)
+    # backward out of place with everything congruent
+    assert _plan(b(O, O + (1 << 30), D, G, U, 16, 512, 512, 512, 512, BF)) == dict(bytes=16, rows=False, shift=False, head=0, edge=0)
+    # outputs skewed against each other: no common vector start -> narrower accesses
+    assert _plan(b(O, O + (1 << 30) + 4, D, G, U, 16, 512, 512, 512, 512, BF))["bytes"] == 4
+    # argument errors come back negated
+    c = _codes()
+    assert f(O, G, U, 4, 8, 4, 8, BF) == -c["ERR_SHAPE"]
+    assert f(O + 1, G, U, 4, 8, 8, 8, BF) == -c["ERR_ALIGN"]
+    assert b(G, U, D, G, U, 4, 8, 8, 8, 8, 11) == -c["ERR_DTYPE"]
