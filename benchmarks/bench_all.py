@@ -278,6 +278,50 @@ def run_c4(args, device):
     return rows
 
 
+def run_lora(args, device):
+    """LoRA + SwiGLU epilogue on the c4 activation shape: E, G bf16 [16384, 14336], rank 16 adapters.
+    Algorithmic bytes: read E and G, write h (3*M*N*2), plus e and g written back when saved for the backward
+    (5*M*N*2); the rank-r operands are negligible.  Comparator: the unfused sequence the reference's fusion
+    replaces, two in-place addmm_ (cuBLAS) followed by this library's SwiGLU kernel."""
+    from kernel_pocs_b200.fused_mlp import check_status
+    from kernel_pocs_b200.lora_mlp import fused_lora_swiglu
+    from kernels.swiglu import swiglu_forward
+
+    m = min(C4["m"], args.max_rows) if args.max_rows else C4["m"]
+    n, r = C4["n"], 16
+    g = torch.Generator(device=device).manual_seed(7)
+    mk = lambda *shape, std=1.0: (std * torch.randn(*shape, generator=g, device=device)).bfloat16()
+    e, gg, xag, xau, bg, bu = mk(m, n), mk(m, n), mk(m, r), mk(m, r), mk(n, r, std=0.3), mk(n, r, std=0.3)
+    e2, g2 = e.clone(), gg.clone()
+    peak, kind = hbm_peak()
+    rows = []
+
+    def fused():
+        fused_lora_swiglu(e, gg, xag, xau, bg, bu, 2.0, 2.0)
+
+    def fused_save():
+        fused_lora_swiglu(e, gg, xag, xau, bg, bu, 2.0, 2.0, save_eg=True)
+
+    def unfused():
+        e2.addmm_(xag, bg.t(), alpha=2.0)
+        g2.addmm_(xau, bu.t(), alpha=2.0)
+        swiglu_forward(e2, g2)
+
+    for provider, fn, nbytes in (("b200-lora-epilogue", fused, 3 * m * n * 2),
+                                 ("b200-lora-epilogue+save", fused_save, 5 * m * n * 2),
+                                 ("addmm_x2+b200-swiglu", unfused, 3 * m * n * 2)):
+        mean, med, best = time_cuda(fn, lambda: None, args.warmup, args.rep)
+        check_status(device)
+        r_ = {"config": "lora", "provider": provider, "mode": "forward", "dtype": "bfloat16", "m": m, "n": n, "r": r,
+              "ms_mean_trimmed": mean, "ms_median": med, "ms_min": best, "algorithmic_bytes_per_gpu": nbytes,
+              "gbs_per_gpu": nbytes / (mean * 1e-3) / 1e9, "tokens_per_s": m / (mean * 1e-3)}
+        r_["frac_of_measured_copy"] = r_["gbs_per_gpu"] / peak
+        rows.append(r_)
+        print(f"{'lora':>16} {provider:>24} forward bf16 M{m} N{n} r{r} {mean:9.4f} ms  {r_['gbs_per_gpu']:8.1f} GB/s  "
+              f"{100 * r_['frac_of_measured_copy']:6.1f}% of {kind} {peak:.0f}  {r_['tokens_per_s'] / 1e6:8.3f} Mtok/s", flush=True)
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--configs", nargs="+", default=["c1", "c2", "c3", "c3-fp32", "c3+w11009", "c3+w11009-off1"])
@@ -311,6 +355,10 @@ def main():
         if name == "c4":
             if world == 1:
                 rows.extend(run_c4(args, device))
+            continue
+        if name == "lora":
+            if world == 1:
+                rows.extend(run_lora(args, device))
             continue
         for r in run_case(name, args, device, rank, world):
             r["frac_of_measured_copy"] = r["gbs_per_gpu"] / peak

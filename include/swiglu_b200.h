@@ -200,6 +200,24 @@ SWIGLU_B200_API int swiglu_b200_gemm_bwd(void* dx, void* dw_gate, void* dw_up, c
 /* Number of backward-GEMM kernels launched by this process. */
 SWIGLU_B200_API uint64_t swiglu_b200_gemm_bwd_launch_count(void);
 
+/* LoRA + SwiGLU epilogue (bf16):
+ *     e = e_base + s_gate * (xa_gate . b_gate^T),  g = g_base + s_up * (xa_up . b_up^T),  h = silu(e) * g
+ * Replaces the launch of _fused_lora_swiglu_kernel in the reference's fused_lora_swiglu
+ * (kernels/lora_mlp/experiments/v3/lora_mlp_kernel_v3.py:141-200).
+ *   e_base, g_base   m x n   outputs of the frozen gate / up projections
+ *   xa_gate, xa_up   m x r   x . A^T of the two adapters        b_gate, b_up   n x r
+ *   h                m x n   result;   e_out, g_out: both NULL, or m x n to receive e and g (the
+ *                            reference's save_eg=True, for the backward)
+ * All row-major, contiguous, 16-byte aligned; requires r % 8 == 0, 8 <= r <= 64, n % 8 == 0.
+ * `status` as in swiglu_b200_gemm_fwd. */
+SWIGLU_B200_API int swiglu_b200_lora_swiglu_fwd(void* h, void* e_out, void* g_out, const void* e_base, const void* g_base,
+                                const void* xa_gate, const void* xa_up, const void* b_gate, const void* b_up,
+                                int64_t m, int64_t n, int64_t r, float s_gate, float s_up, void* status, int device,
+                                void* stream);
+
+/* Number of LoRA + SwiGLU epilogue kernels launched by this process. */
+SWIGLU_B200_API uint64_t swiglu_b200_lora_launch_count(void);
+
 /* Number of fused-GEMM kernels launched by this process. */
 SWIGLU_B200_API uint64_t swiglu_b200_gemm_launch_count(void);
 

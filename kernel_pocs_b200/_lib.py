@@ -64,6 +64,12 @@ SIGNATURES = {
          ctypes.c_int, _c_ptr],
     ),
     "swiglu_b200_gemm_launch_count": (ctypes.c_uint64, []),
+    "swiglu_b200_lora_swiglu_fwd": (
+        ctypes.c_int,
+        [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64,
+         ctypes.c_float, ctypes.c_float, _c_ptr, ctypes.c_int, _c_ptr],
+    ),
+    "swiglu_b200_lora_launch_count": (ctypes.c_uint64, []),
     "swiglu_b200_gemm_bwd": (
         ctypes.c_int,
         [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr,

@@ -1,0 +1,372 @@
+// LoRA + SwiGLU epilogue for sm_100a:
+//
+//     e = E + s_gate * (XAg . Bg^T)      g = G + s_up * (XAu . Bu^T)      h = silu(e) * g
+//
+// E, G [M, N]: outputs of the frozen gate / up projections; XAg, XAu [M, r]: x . A^T of the two adapters;
+// Bg, Bu [N, r]: the adapters' second factors; all bf16, r a multiple of 8 up to 64.  Optionally e and g
+// (with the adapter terms added) are written out for a backward pass.  This is the step the reference
+// performs with _fused_lora_swiglu_kernel (kernels/lora_mlp/experiments/v3/lora_mlp_kernel_v3.py:45-138),
+// launched from fused_lora_swiglu (:141-200): a Triton tile kernel with two small tl.dot per tile.
+//
+// The operator streams 3 (or 5) M x N matrices, so it is bound by HBM bandwidth, but the rank-r products
+// cost 4*r flops per output, too many for the fp32 pipes at that rate (64 flop per 6 bytes at r = 16); they
+// go to the tcgen05 tensor cores, and all the traffic goes through the TMA engine:
+//
+//   * A CTA owns 128 token rows and walks a range of 64-column tiles.  XAg / XAu tiles (128 x 64, zero
+//     filled beyond r) are loaded once per range.
+//   * Per tile the producer warp loads E, G (128 x 64) and Bg, Bu (64 x 64) into a 3-stage ring.  One
+//     thread issues two M=128, N=64 MMAs per 16 ranks into TMEM (double buffered), which yield the adapter
+//     terms in the row-per-thread layout the epilogue reads.
+//   * Four epilogue warps add the terms to E and G taken from the swizzled shared-memory tiles, apply
+//     SwiGLU in fp32, write h (and e, g in place over the staged tiles) back to shared memory, and one
+//     thread stores the tiles with bulk tensor stores, which also clip at the matrix edge.
+// No load uses cluster multicast.  Every mbarrier wait is bounded; a wait that gives up records its code
+// in the status word, the other waits then leave, and the CTA drains its copies, frees TMEM and returns.
+#include "swiglu_b200.h"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+
+#include "swiglu_kernels.cuh"
+#include "tcgen05_common.cuh"
+
+namespace {
+
+using namespace swiglu_b200::tc;
+using swiglu_b200::Consts;
+using swiglu_b200::Math;
+
+constexpr int TM = 128;                         // token rows per CTA tile
+constexpr int TN = 64;                          // output columns per tile (one 128-byte swizzle span)
+constexpr int RK = 64;                          // rank, padded by the loads' zero fill
+constexpr int STAGES = 3;
+constexpr int TILES_PER_RANGE = 16;             // 1024 columns per work item
+constexpr int XA_BYTES = TM * RK * 2;           // 16 KiB
+constexpr int EG_BYTES = TM * TN * 2;           // 16 KiB
+constexpr int B_BYTES = TN * RK * 2;            // 8 KiB
+constexpr int STAGE_BYTES = 2 * EG_BYTES + 2 * B_BYTES;  // 48 KiB
+constexpr int OUT_BUFS = 2;
+constexpr int TMEM_COLS = 256;                  // 2 buffers x (64 gate + 64 up) fp32 columns
+constexpr int THREADS = 192;
+constexpr int SMEM_BYTES = 2 * XA_BYTES + STAGES * STAGE_BYTES + OUT_BUFS * EG_BYTES + 1024 + 256;
+// kind::f16, D fp32, A and B bf16 K-major, M = 128, N = 64
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+
+struct LoraParams {
+  int* status;
+  long long m, n;
+  int r;
+  int save;  // also store e and g
+  float s_gate, s_up;
+};
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, const void* smem_src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y),
+               "r"(smem_u32(smem_src)) : "memory");
+}
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// barrier over the 128 epilogue threads that also ANDs a predicate across them
+__device__ __forceinline__ bool epilogue_all(bool ok) {
+  uint32_t all;
+  asm volatile("{ .reg .pred p, q; setp.ne.u32 q, %1, 0; bar.red.and.pred p, 1, 128, q; selp.u32 %0, 1, 0, p; }"
+               : "=r"(all) : "r"((uint32_t)ok) : "memory");
+  return all != 0;
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr) : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_constant__ CUtensorMap map_g,
+                   const __grid_constant__ CUtensorMap map_xag, const __grid_constant__ CUtensorMap map_xau,
+                   const __grid_constant__ CUtensorMap map_bg, const __grid_constant__ CUtensorMap map_bu,
+                   const __grid_constant__ CUtensorMap map_h, const __grid_constant__ CUtensorMap map_eo,
+                   const __grid_constant__ CUtensorMap map_go, const LoraParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* xa_g = smem;
+  unsigned char* xa_u = smem + XA_BYTES;
+  unsigned char* ring = smem + 2 * XA_BYTES;
+  unsigned char* outs = ring + STAGES * STAGE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(outs + OUT_BUFS * EG_BYTES);
+  uint64_t* empty = full + STAGES;        // MMA commit + one epilogue thread
+  uint64_t* acc_full = empty + STAGES;    // [2]
+  uint64_t* acc_empty = acc_full + 2;     // [2], four epilogue warps
+  uint64_t* xa_full = acc_empty + 2;
+  uint64_t* xa_empty = xa_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xa_empty + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long tiles_n = (p.n + TN - 1) / TN;
+  const long long ranges_n = (tiles_n + TILES_PER_RANGE - 1) / TILES_PER_RANGE;
+  const long long items = ((p.m + TM - 1) / TM) * ranges_n;
+  const int k_steps = (p.r + 15) / 16;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 2);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);
+    }
+    mbar_init(xa_full, 1);
+    mbar_init(xa_empty, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Every role walks the same sequence: items (row tile, column range), tiles within the range.
+  if (warp == 0) {
+    if (lane == 0) {
+      long long it = 0, item_no = 0;
+      bool ok = true;
+      for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++item_no) {
+        const int m0 = (int)(item / ranges_n) * TM;
+        const long long t_lo = (item % ranges_n) * TILES_PER_RANGE;
+        const long long t_hi = (t_lo + TILES_PER_RANGE) < tiles_n ? (t_lo + TILES_PER_RANGE) : tiles_n;
+        if (item_no > 0) {
+          ok = mbar_wait(xa_empty, (uint32_t)((item_no - 1) & 1), p.status, 500);
+          if (!ok) break;
+        }
+        mbar_expect_tx(xa_full, 2 * XA_BYTES);
+        tma_load_2d(xa_g, &map_xag, 0, m0, xa_full);
+        tma_load_2d(xa_u, &map_xau, 0, m0, xa_full);
+        for (long long t = t_lo; t < t_hi; ++t, ++it) {
+          const int s = (int)(it % STAGES);
+          if (it >= STAGES) {
+            ok = mbar_wait(&empty[s], (uint32_t)((it / STAGES - 1) & 1), p.status, 100 + s);
+            if (!ok) break;
+          }
+          unsigned char* stage = ring + s * STAGE_BYTES;
+          const int n0 = (int)(t * TN);
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          tma_load_2d(stage, &map_e, n0, m0, &full[s]);
+          tma_load_2d(stage + EG_BYTES, &map_g, n0, m0, &full[s]);
+          tma_load_2d(stage + 2 * EG_BYTES, &map_bg, 0, n0, &full[s]);
+          tma_load_2d(stage + 2 * EG_BYTES + B_BYTES, &map_bu, 0, n0, &full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      long long it = 0, item_no = 0;
+      bool ok = true;
+      const uint64_t ag_desc = umma_desc(smem_u32(xa_g));
+      const uint64_t au_desc = umma_desc(smem_u32(xa_u));
+      for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++item_no) {
+        const long long t_lo = (item % ranges_n) * TILES_PER_RANGE;
+        const long long t_hi = (t_lo + TILES_PER_RANGE) < tiles_n ? (t_lo + TILES_PER_RANGE) : tiles_n;
+        ok = mbar_wait(xa_full, (uint32_t)(item_no & 1), p.status, 510);
+        if (!ok) break;
+        for (long long t = t_lo; t < t_hi; ++t, ++it) {
+          const int s = (int)(it % STAGES);
+          const int b = (int)(it & 1);
+          if (it >= 2) {
+            ok = mbar_wait(&acc_empty[b], (uint32_t)(((it >> 1) - 1) & 1), p.status, 400 + b);
+            if (!ok) break;
+          }
+          ok = mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1), p.status, 200 + s);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t b_addr = smem_u32(ring + s * STAGE_BYTES + 2 * EG_BYTES);
+          const uint64_t bg_desc = umma_desc(b_addr);
+          const uint64_t bu_desc = umma_desc(b_addr + B_BYTES);
+          const uint32_t d_gate = tmem_base + (uint32_t)b * 128u;
+          for (int kk = 0; kk < k_steps; ++kk) {
+            umma_bf16(d_gate, ag_desc + 2 * kk, bg_desc + 2 * kk, IDESC, kk != 0);
+            umma_bf16(d_gate + 64, au_desc + 2 * kk, bu_desc + 2 * kk, IDESC, kk != 0);
+          }
+          umma_commit(&acc_full[b]);  // adapter terms of this tile are in TMEM
+          umma_commit(&empty[s]);     // ... and the Bg / Bu tiles of the stage have been read
+        }
+        if (ok) umma_commit(xa_empty);  // the XA tiles may be replaced once these MMAs are done
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;           // row of the tile owned by this thread
+    const bool elected = (warp == 2 && lane == 0);
+    const Consts one(1.0f, 1.0f);
+    long long it = 0;
+    bool ok = true;
+    for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
+      const int m0 = (int)(item / ranges_n) * TM;
+      const long long t_lo = (item % ranges_n) * TILES_PER_RANGE;
+      const long long t_hi = (t_lo + TILES_PER_RANGE) < tiles_n ? (t_lo + TILES_PER_RANGE) : tiles_n;
+      for (long long t = t_lo; t < t_hi; ++t, ++it) {
+        const int s = (int)(it % STAGES);
+        const int b = (int)(it & 1);
+        unsigned char* e_tile = ring + s * STAGE_BYTES;
+        unsigned char* g_tile = e_tile + EG_BYTES;
+        unsigned char* h_tile = outs + (it & 1) * EG_BYTES;
+        // the bulk store that last read h_tile (two tiles ago) must be done with it
+        if (elected) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        ok = mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1), p.status, 600 + s) &&
+             mbar_wait(&acc_full[b], (uint32_t)((it >> 1) & 1), p.status, 300 + b);
+        // The 128 epilogue threads meet here and agree on the outcome, so that none is left waiting
+        // at a later barrier for a thread whose wait gave up.
+        ok = epilogue_all(ok);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)b * 128u;
+#pragma unroll 1
+        for (int c = 0; c < TN; c += 8) {
+          uint32_t lg[8], lu[8];
+          tmem_ld8(t_row + c, lg);
+          tmem_ld8(t_row + 64 + c, lu);
+          // 16-byte chunk c/8 of this row inside the 128-byte-swizzled tile
+          const int off = row * 128 + (((c >> 3) ^ (row & 7)) << 4);
+          const uint4 e4 = *reinterpret_cast<const uint4*>(e_tile + off);
+          const uint4 g4 = *reinterpret_cast<const uint4*>(g_tile + off);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          const uint32_t ew[4] = {e4.x, e4.y, e4.z, e4.w}, gw[4] = {g4.x, g4.y, g4.z, g4.w};
+          uint32_t hw[4], eo[4], go[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float e0 = fmaf(p.s_gate, __uint_as_float(lg[2 * j]), __uint_as_float(ew[j] << 16));
+            const float e1 = fmaf(p.s_gate, __uint_as_float(lg[2 * j + 1]), __uint_as_float(ew[j] & 0xffff0000u));
+            const float g0 = fmaf(p.s_up, __uint_as_float(lu[2 * j]), __uint_as_float(gw[j] << 16));
+            const float g1 = fmaf(p.s_up, __uint_as_float(lu[2 * j + 1]), __uint_as_float(gw[j] & 0xffff0000u));
+            __nv_bfloat162 hb = __floats2bfloat162_rn(Math<true>::fwd(e0, g0, one), Math<true>::fwd(e1, g1, one));
+            __nv_bfloat162 eb = __floats2bfloat162_rn(e0, e1);
+            __nv_bfloat162 gb = __floats2bfloat162_rn(g0, g1);
+            hw[j] = *reinterpret_cast<uint32_t*>(&hb);
+            eo[j] = *reinterpret_cast<uint32_t*>(&eb);
+            go[j] = *reinterpret_cast<uint32_t*>(&gb);
+          }
+          *reinterpret_cast<uint4*>(h_tile + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+          if (p.save) {
+            *reinterpret_cast<uint4*>(e_tile + off) = make_uint4(eo[0], eo[1], eo[2], eo[3]);
+            *reinterpret_cast<uint4*>(g_tile + off) = make_uint4(go[0], go[1], go[2], go[3]);
+          }
+        }
+        // TMEM buffer b is drained; shared-memory tiles are complete
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[b]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        epilogue_barrier();
+        if (elected) {
+          const int n0 = (int)(t * TN);
+          tma_store_2d(&map_h, n0, m0, h_tile);
+          if (p.save) {
+            tma_store_2d(&map_eo, n0, m0, e_tile);
+            tma_store_2d(&map_go, n0, m0, g_tile);
+          }
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          // the stage may be refilled once nothing reads it any more
+          if (p.save) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          mbar_arrive(&empty[s]);
+        }
+      }
+    }
+    if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (*reinterpret_cast<volatile int*>(p.status) != 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+std::atomic<uint64_t> g_lora_launches{0};
+
+}  // namespace
+
+extern "C" {
+
+uint64_t swiglu_b200_lora_launch_count(void) { return g_lora_launches.load(std::memory_order_relaxed); }
+
+int swiglu_b200_lora_swiglu_fwd(void* h, void* e_out, void* g_out, const void* e_base, const void* g_base,
+                                const void* xa_gate, const void* xa_up, const void* b_gate, const void* b_up,
+                                int64_t m, int64_t n, int64_t r, float s_gate, float s_up, void* status, int device,
+                                void* stream) {
+  if (m < 0 || n < 0 || r < 0) return SWIGLU_B200_ERR_SHAPE;
+  if (m == 0 || n == 0) return SWIGLU_B200_OK;
+  if (r == 0 || r > RK || r % 8 != 0 || n % 8 != 0) return SWIGLU_B200_ERR_SHAPE;
+  if (m > 0x7fffff00LL || n > 0x7fffff00LL) return SWIGLU_B200_ERR_SHAPE;
+  if (!h || !e_base || !g_base || !xa_gate || !xa_up || !b_gate || !b_up || !status) return SWIGLU_B200_ERR_NULL;
+  if ((e_out == nullptr) != (g_out == nullptr)) return SWIGLU_B200_ERR_NULL;
+  if (((uintptr_t)h | (uintptr_t)e_out | (uintptr_t)g_out | (uintptr_t)e_base | (uintptr_t)g_base | (uintptr_t)xa_gate |
+       (uintptr_t)xa_up | (uintptr_t)b_gate | (uintptr_t)b_up) % 16)
+    return SWIGLU_B200_ERR_ALIGN;
+  if ((uintptr_t)status % 4) return SWIGLU_B200_ERR_ALIGN;
+
+  int prev = -1;
+  bool switched = false;
+  if (device >= 0) {
+    if (cudaGetDevice(&prev) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
+    if (prev != device) {
+      if (cudaSetDevice(device) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
+      switched = true;
+    }
+  }
+  struct Restore {
+    bool on;
+    int dev;
+    ~Restore() {
+      if (on) cudaSetDevice(dev);
+    }
+  } restore{switched, prev};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
+
+  const bool save = e_out != nullptr;
+  CUtensorMap me, mg, mxg, mxu, mbg, mbu, mh, meo, mgo;
+  if (!make_map(&me, e_base, m, n, TM) || !make_map(&mg, g_base, m, n, TM) || !make_map(&mh, h, m, n, TM) ||
+      !make_map(&meo, save ? e_out : h, m, n, TM) || !make_map(&mgo, save ? g_out : h, m, n, TM) ||
+      !make_map(&mxg, xa_gate, m, r, TM) || !make_map(&mxu, xa_up, m, r, TM) || !make_map(&mbg, b_gate, n, r, TN) ||
+      !make_map(&mbu, b_up, n, r, TN))
+    return SWIGLU_B200_ERR_DEVICE;
+
+  static std::atomic<int> sms[64];
+  int n_sm = dev < 64 ? sms[dev].load(std::memory_order_acquire) : 0;
+  if (n_sm == 0) {
+    if (cudaFuncSetAttribute(lora_swiglu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+      return SWIGLU_B200_ERR_DEVICE;
+    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm < 1)
+      return SWIGLU_B200_ERR_DEVICE;
+    if (dev < 64) sms[dev].store(n_sm, std::memory_order_release);
+  }
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
+  const long long tiles_n = (n + TN - 1) / TN;
+  const long long items = ((m + TM - 1) / TM) * ((tiles_n + TILES_PER_RANGE - 1) / TILES_PER_RANGE);
+  const long long grid = items < n_sm ? items : n_sm;
+  LoraParams p{static_cast<int*>(status), m, n, (int)r, save ? 1 : 0, s_gate, s_up};
+  lora_swiglu_kernel<<<(unsigned)grid, THREADS, SMEM_BYTES, st>>>(me, mg, mxg, mxu, mbg, mbu, mh, meo, mgo, p);
+  if (cudaGetLastError() != cudaSuccess) return SWIGLU_B200_ERR_LAUNCH;
+  g_lora_launches.fetch_add(1, std::memory_order_relaxed);
+  return SWIGLU_B200_OK;
+}
+
+}  // extern "C"
