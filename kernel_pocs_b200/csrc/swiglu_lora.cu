@@ -12,12 +12,12 @@
 // cost 4*r flops per output, too many for the fp32 pipes at that rate (64 flop per 6 bytes at r = 16); they
 // go to the tcgen05 tensor cores, and all the traffic goes through the TMA engine:
 //
-//   * A CTA owns 128 token rows and walks a range of 64-column tiles.  XAg / XAu tiles (128 x 64, zero
-//     filled beyond r) are loaded once per range.
-//   * Per tile the producer warp loads E, G (128 x 64) and Bg, Bu (64 x 64) into a 3-stage ring.  One
+//   * A CTA owns 128 token rows and walks a range of 64-column tiles.  XAg / XAu tiles (128 rows, rank
+//     padded to 16, 32 or 64 by the loads' zero fill) are loaded once per range.
+//   * Per tile the producer warp loads E, G (128 x 64) and Bg, Bu (64 rows) into a 3- or 4-stage ring.  One
 //     thread issues two M=128, N=64 MMAs per 16 ranks into TMEM (double buffered), which yield the adapter
 //     terms in the row-per-thread layout the epilogue reads.
-//   * Four epilogue warps add the terms to E and G taken from the swizzled shared-memory tiles, apply
+//   * Sixteen epilogue warps (four per TMEM lane quarter, 16 columns each) add the terms to E and G taken from the swizzled shared-memory tiles, apply
 //     SwiGLU in fp32, write h (and e, g in place over the staged tiles) back to shared memory, and one
 //     thread stores the tiles with bulk tensor stores, which also clip at the matrix edge.
 // No load uses cluster multicast.  Every mbarrier wait is bounded; a wait that gives up records its code
@@ -41,19 +41,33 @@ using swiglu_b200::Math;
 
 constexpr int TM = 128;                         // token rows per CTA tile
 constexpr int TN = 64;                          // output columns per tile (one 128-byte swizzle span)
-constexpr int RK = 64;                          // rank, padded by the loads' zero fill
-constexpr int STAGES = 3;
-constexpr int TILES_PER_RANGE = 16;             // 1024 columns per work item
-constexpr int XA_BYTES = TM * RK * 2;           // 16 KiB
+#ifndef SWIGLU_LORA_TILES_PER_RANGE
+#define SWIGLU_LORA_TILES_PER_RANGE 4  // finer items balance the SMs better (16 -> 4: +3..6 %)
+#endif
+constexpr int TILES_PER_RANGE = SWIGLU_LORA_TILES_PER_RANGE;  // 64-column tiles per work item
 constexpr int EG_BYTES = TM * TN * 2;           // 16 KiB
-constexpr int B_BYTES = TN * RK * 2;            // 8 KiB
-constexpr int STAGE_BYTES = 2 * EG_BYTES + 2 * B_BYTES;  // 48 KiB
-constexpr int OUT_BUFS = 2;
+constexpr int OUT_BUFS = 3;                     // h tiles waiting for their bulk store
 constexpr int TMEM_COLS = 256;                  // 2 buffers x (64 gate + 64 up) fp32 columns
-constexpr int THREADS = 192;
-constexpr int SMEM_BYTES = 2 * XA_BYTES + STAGES * STAGE_BYTES + OUT_BUFS * EG_BYTES + 1024 + 256;
+#ifndef SWIGLU_LORA_EPI_WARPS
+#define SWIGLU_LORA_EPI_WARPS 16
+#endif
+constexpr int EPI_WARPS = SWIGLU_LORA_EPI_WARPS;  // EPI_WARPS / 4 warps share a TMEM lane quarter
+constexpr int CW = 64 / (EPI_WARPS / 4);         // columns of a tile handled by one warp
+constexpr int THREADS = 64 + 32 * EPI_WARPS;
 // kind::f16, D fp32, A and B bf16 K-major, M = 128, N = 64
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+
+// Shared-memory budget for a rank padded to RK (16, 32 or 64): the narrower the adapter tiles, the more
+// stages of E / G tiles fit, and bytes in flight are what this kernel's bandwidth comes from.
+template <int RK>
+struct Cfg {
+  static constexpr int XA_BYTES = TM * RK * 2;
+  static constexpr int B_BYTES = TN * RK * 2;
+  static constexpr int STAGE_BYTES = 2 * EG_BYTES + 2 * B_BYTES;
+  static constexpr int STAGES = RK == 64 ? 3 : 4;
+  static constexpr int SMEM_BYTES = 2 * XA_BYTES + STAGES * STAGE_BYTES + OUT_BUFS * EG_BYTES + 1024 + 256;
+  static_assert(SMEM_BYTES <= 227 * 1024, "exceeds the shared memory of an SM");
+};
 
 struct LoraParams {
   int* status;
@@ -67,23 +81,28 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int 
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y),
                "r"(smem_u32(smem_src)) : "memory");
 }
-__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-// barrier over the 128 epilogue threads that also ANDs a predicate across them
+// barrier over the epilogue threads that also ANDs a predicate across them
 __device__ __forceinline__ bool epilogue_all(bool ok) {
   uint32_t all;
-  asm volatile("{ .reg .pred p, q; setp.ne.u32 q, %1, 0; bar.red.and.pred p, 1, 128, q; selp.u32 %0, 1, 0, p; }"
-               : "=r"(all) : "r"((uint32_t)ok) : "memory");
+  asm volatile("{ .reg .pred p, q; setp.ne.u32 q, %1, 0; bar.red.and.pred p, 1, %2, q; selp.u32 %0, 1, 0, p; }"
+               : "=r"(all) : "r"((uint32_t)ok), "n"(32 * EPI_WARPS) : "memory");
   return all != 0;
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* b) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
 }
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* r) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr) : "memory");
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
 }
 
+template <int RK>
 __global__ void __launch_bounds__(THREADS, 1)
 lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_constant__ CUtensorMap map_g,
                    const __grid_constant__ CUtensorMap map_xag, const __grid_constant__ CUtensorMap map_xau,
@@ -92,6 +111,8 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
                    const __grid_constant__ CUtensorMap map_go, const LoraParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int XA_BYTES = Cfg<RK>::XA_BYTES, B_BYTES = Cfg<RK>::B_BYTES, STAGE_BYTES = Cfg<RK>::STAGE_BYTES,
+                STAGES = Cfg<RK>::STAGES;
   unsigned char* xa_g = smem;
   unsigned char* xa_u = smem + XA_BYTES;
   unsigned char* ring = smem + 2 * XA_BYTES;
@@ -99,7 +120,7 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
   uint64_t* full = reinterpret_cast<uint64_t*>(outs + OUT_BUFS * EG_BYTES);
   uint64_t* empty = full + STAGES;        // MMA commit + one epilogue thread
   uint64_t* acc_full = empty + STAGES;    // [2]
-  uint64_t* acc_empty = acc_full + 2;     // [2], four epilogue warps
+  uint64_t* acc_empty = acc_full + 2;     // [2], every epilogue warp
   uint64_t* xa_full = acc_empty + 2;
   uint64_t* xa_empty = xa_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xa_empty + 1);
@@ -118,7 +139,7 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);
+      mbar_init(&acc_empty[b], EPI_WARPS);
     }
     mbar_init(xa_full, 1);
     mbar_init(xa_empty, 1);
@@ -171,8 +192,8 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
     if (lane == 0) {
       long long it = 0, item_no = 0;
       bool ok = true;
-      const uint64_t ag_desc = umma_desc(smem_u32(xa_g));
-      const uint64_t au_desc = umma_desc(smem_u32(xa_u));
+      const uint64_t ag_desc = umma_desc_rows<RK * 2>(smem_u32(xa_g));
+      const uint64_t au_desc = umma_desc_rows<RK * 2>(smem_u32(xa_u));
       for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++item_no) {
         const long long t_lo = (item % ranges_n) * TILES_PER_RANGE;
         const long long t_hi = (t_lo + TILES_PER_RANGE) < tiles_n ? (t_lo + TILES_PER_RANGE) : tiles_n;
@@ -189,8 +210,8 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t b_addr = smem_u32(ring + s * STAGE_BYTES + 2 * EG_BYTES);
-          const uint64_t bg_desc = umma_desc(b_addr);
-          const uint64_t bu_desc = umma_desc(b_addr + B_BYTES);
+          const uint64_t bg_desc = umma_desc_rows<RK * 2>(b_addr);
+          const uint64_t bu_desc = umma_desc_rows<RK * 2>(b_addr + B_BYTES);
           const uint32_t d_gate = tmem_base + (uint32_t)b * 128u;
           for (int kk = 0; kk < k_steps; ++kk) {
             umma_bf16(d_gate, ag_desc + 2 * kk, bg_desc + 2 * kk, IDESC, kk != 0);
@@ -203,8 +224,9 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
       }
     }
   } else {
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;           // row of the tile owned by this thread
+    const int quarter = warp & 3;                   // TMEM lane quarter this warp may read
+    const int part = (warp - 2) >> 2;               // which CW of the tile's 64 columns it handles
+    const int row = quarter * 32 + lane;            // row of the tile owned by this thread
     const bool elected = (warp == 2 && lane == 0);
     const Consts one(1.0f, 1.0f);
     long long it = 0;
@@ -218,35 +240,44 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
         const int b = (int)(it & 1);
         unsigned char* e_tile = ring + s * STAGE_BYTES;
         unsigned char* g_tile = e_tile + EG_BYTES;
-        unsigned char* h_tile = outs + (it & 1) * EG_BYTES;
-        // the bulk store that last read h_tile (two tiles ago) must be done with it
-        if (elected) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        // Three h buffers: the store of tile i-2 is known to be complete once the barrier at the end of
+        // tile i has been passed (the storing thread waits for it before arriving there), so tile i+1 may
+        // overwrite that buffer without a second barrier.
+        unsigned char* h_tile = outs + (it % OUT_BUFS) * EG_BYTES;
         ok = mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1), p.status, 600 + s) &&
              mbar_wait(&acc_full[b], (uint32_t)((it >> 1) & 1), p.status, 300 + b);
-        // The 128 epilogue threads meet here and agree on the outcome, so that none is left waiting
-        // at a later barrier for a thread whose wait gave up.
-        ok = epilogue_all(ok);
-        if (!ok) break;
+        if (!__all_sync(0xffffffffu, ok)) ok = false;  // warp-uniform, for the warp-wide TMEM loads
+        if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)b * 128u;
-#pragma unroll 1
-        for (int c = 0; c < TN; c += 8) {
-          uint32_t lg[8], lu[8];
-          tmem_ld8(t_row + c, lg);
-          tmem_ld8(t_row + 64 + c, lu);
-          // 16-byte chunk c/8 of this row inside the 128-byte-swizzled tile
-          const int off = row * 128 + (((c >> 3) ^ (row & 7)) << 4);
+        const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)b * 128u + (uint32_t)(part * CW);
+        uint32_t lg[CW], lu[CW];
+        if constexpr (CW == 32) {
+          tmem_ld32(t_row, lg);
+          tmem_ld32(t_row + 64, lu);
+        } else {
+          static_assert(CW == 16 || CW == 32, "8 or 16 epilogue warps");
+          tmem_ld16(t_row, lg);
+          tmem_ld16(t_row + 64, lu);
+        }
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        // the adapter terms are in registers: TMEM buffer b can take the MMAs of the tile after next
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[b]);
+#pragma unroll
+        for (int c = 0; c < CW; c += 8) {
+          // 16-byte chunk (part*CW + c)/8 of this row inside the 128-byte-swizzled tile
+          const int off = row * 128 + ((((part * CW + c) >> 3) ^ (row & 7)) << 4);
           const uint4 e4 = *reinterpret_cast<const uint4*>(e_tile + off);
           const uint4 g4 = *reinterpret_cast<const uint4*>(g_tile + off);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           const uint32_t ew[4] = {e4.x, e4.y, e4.z, e4.w}, gw[4] = {g4.x, g4.y, g4.z, g4.w};
           uint32_t hw[4], eo[4], go[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const float e0 = fmaf(p.s_gate, __uint_as_float(lg[2 * j]), __uint_as_float(ew[j] << 16));
-            const float e1 = fmaf(p.s_gate, __uint_as_float(lg[2 * j + 1]), __uint_as_float(ew[j] & 0xffff0000u));
-            const float g0 = fmaf(p.s_up, __uint_as_float(lu[2 * j]), __uint_as_float(gw[j] << 16));
-            const float g1 = fmaf(p.s_up, __uint_as_float(lu[2 * j + 1]), __uint_as_float(gw[j] & 0xffff0000u));
+            const float e0 = fmaf(p.s_gate, __uint_as_float(lg[c + 2 * j]), __uint_as_float(ew[j] << 16));
+            const float e1 = fmaf(p.s_gate, __uint_as_float(lg[c + 2 * j + 1]), __uint_as_float(ew[j] & 0xffff0000u));
+            const float g0 = fmaf(p.s_up, __uint_as_float(lu[c + 2 * j]), __uint_as_float(gw[j] << 16));
+            const float g1 = fmaf(p.s_up, __uint_as_float(lu[c + 2 * j + 1]), __uint_as_float(gw[j] & 0xffff0000u));
             __nv_bfloat162 hb = __floats2bfloat162_rn(Math<true>::fwd(e0, g0, one), Math<true>::fwd(e1, g1, one));
             __nv_bfloat162 eb = __floats2bfloat162_rn(e0, e1);
             __nv_bfloat162 gb = __floats2bfloat162_rn(g0, g1);
@@ -260,12 +291,13 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
             *reinterpret_cast<uint4*>(g_tile + off) = make_uint4(go[0], go[1], go[2], go[3]);
           }
         }
-        // TMEM buffer b is drained; shared-memory tiles are complete
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[b]);
+        }
+        // The shared-memory tiles are complete: make them visible to the bulk stores.  All epilogue threads
+        // meet here once per tile and agree on the outcome of their waits, so that none is left at a later
+        // barrier waiting for a thread whose wait gave up.
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        epilogue_barrier();
+        ok = epilogue_all(ok);
+        if (!ok) break;
         if (elected) {
           const int n0 = (int)(t * TN);
           tma_store_2d(&map_h, n0, m0, h_tile);
@@ -277,6 +309,8 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
           // the stage may be refilled once nothing reads it any more
           if (p.save) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           mbar_arrive(&empty[s]);
+          // at most this tile's store stays pending: the previous one has released its h buffer
+          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
         }
       }
     }
@@ -311,7 +345,7 @@ int swiglu_b200_lora_swiglu_fwd(void* h, void* e_out, void* g_out, const void* e
                                 void* stream) {
   if (m < 0 || n < 0 || r < 0) return SWIGLU_B200_ERR_SHAPE;
   if (m == 0 || n == 0) return SWIGLU_B200_OK;
-  if (r == 0 || r > RK || r % 8 != 0 || n % 8 != 0) return SWIGLU_B200_ERR_SHAPE;
+  if (r == 0 || r > 64 || r % 8 != 0 || n % 8 != 0) return SWIGLU_B200_ERR_SHAPE;
   if (m > 0x7fffff00LL || n > 0x7fffff00LL) return SWIGLU_B200_ERR_SHAPE;
   if (!h || !e_base || !g_base || !xa_gate || !xa_up || !b_gate || !b_up || !status) return SWIGLU_B200_ERR_NULL;
   if ((e_out == nullptr) != (g_out == nullptr)) return SWIGLU_B200_ERR_NULL;
@@ -340,17 +374,23 @@ int swiglu_b200_lora_swiglu_fwd(void* h, void* e_out, void* g_out, const void* e
   if (cudaGetDevice(&dev) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
 
   const bool save = e_out != nullptr;
+  const int rk = r <= 16 ? 16 : r <= 32 ? 32 : 64;  // adapter tiles are padded to this rank by the loads' zero fill
   CUtensorMap me, mg, mxg, mxu, mbg, mbu, mh, meo, mgo;
   if (!make_map(&me, e_base, m, n, TM) || !make_map(&mg, g_base, m, n, TM) || !make_map(&mh, h, m, n, TM) ||
       !make_map(&meo, save ? e_out : h, m, n, TM) || !make_map(&mgo, save ? g_out : h, m, n, TM) ||
-      !make_map(&mxg, xa_gate, m, r, TM) || !make_map(&mxu, xa_up, m, r, TM) || !make_map(&mbg, b_gate, n, r, TN) ||
-      !make_map(&mbu, b_up, n, r, TN))
+      !make_map(&mxg, xa_gate, m, r, TM, rk) || !make_map(&mxu, xa_up, m, r, TM, rk) ||
+      !make_map(&mbg, b_gate, n, r, TN, rk) || !make_map(&mbu, b_up, n, r, TN, rk))
     return SWIGLU_B200_ERR_DEVICE;
 
   static std::atomic<int> sms[64];
   int n_sm = dev < 64 ? sms[dev].load(std::memory_order_acquire) : 0;
   if (n_sm == 0) {
-    if (cudaFuncSetAttribute(lora_swiglu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(lora_swiglu_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<16>::SMEM_BYTES) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(lora_swiglu_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<32>::SMEM_BYTES) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(lora_swiglu_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<64>::SMEM_BYTES) !=
+            cudaSuccess)
       return SWIGLU_B200_ERR_DEVICE;
     if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm < 1)
       return SWIGLU_B200_ERR_DEVICE;
@@ -361,9 +401,14 @@ int swiglu_b200_lora_swiglu_fwd(void* h, void* e_out, void* g_out, const void* e
   if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
   const long long tiles_n = (n + TN - 1) / TN;
   const long long items = ((m + TM - 1) / TM) * ((tiles_n + TILES_PER_RANGE - 1) / TILES_PER_RANGE);
-  const long long grid = items < n_sm ? items : n_sm;
+  const unsigned grid = (unsigned)(items < n_sm ? items : n_sm);
   LoraParams p{static_cast<int*>(status), m, n, (int)r, save ? 1 : 0, s_gate, s_up};
-  lora_swiglu_kernel<<<(unsigned)grid, THREADS, SMEM_BYTES, st>>>(me, mg, mxg, mxu, mbg, mbu, mh, meo, mgo, p);
+  if (rk == 16)
+    lora_swiglu_kernel<16><<<grid, THREADS, Cfg<16>::SMEM_BYTES, st>>>(me, mg, mxg, mxu, mbg, mbu, mh, meo, mgo, p);
+  else if (rk == 32)
+    lora_swiglu_kernel<32><<<grid, THREADS, Cfg<32>::SMEM_BYTES, st>>>(me, mg, mxg, mxu, mbg, mbu, mh, meo, mgo, p);
+  else
+    lora_swiglu_kernel<64><<<grid, THREADS, Cfg<64>::SMEM_BYTES, st>>>(me, mg, mxg, mxu, mbg, mbu, mh, meo, mgo, p);
   if (cudaGetLastError() != cudaSuccess) return SWIGLU_B200_ERR_LAUNCH;
   g_lora_launches.fetch_add(1, std::memory_order_relaxed);
   return SWIGLU_B200_OK;

@@ -60,6 +60,16 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
          (2ull << 61);
 }
 
+// Same for K-major tiles whose rows are ROW_BYTES = 32, 64 or 128 bytes long, stored with the swizzle of
+// that span (8-row groups 8 * ROW_BYTES apart).  Layout codes: 128-byte swizzle 2, 64-byte 4, 32-byte 6.
+template <int ROW_BYTES>
+__device__ __forceinline__ uint64_t umma_desc_rows(uint32_t smem_addr) {
+  static_assert(ROW_BYTES == 32 || ROW_BYTES == 64 || ROW_BYTES == 128, "swizzle spans are 32, 64 or 128 bytes");
+  constexpr uint64_t layout = ROW_BYTES == 128 ? 2 : ROW_BYTES == 64 ? 4 : 6;
+  return (uint64_t)((smem_addr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t)((8 * ROW_BYTES) >> 4) << 32) |
+         (1ull << 46) | (layout << 61);
+}
+
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                           uint32_t accumulate) {
   asm volatile(
@@ -174,16 +184,22 @@ inline EncodeTiled encode_fn() {
 }
 
 // [rows, k] bf16 row-major matrix, boxes of `box_rows` rows x 64 elements (128 bytes) along the contiguous
-// dimension, 128-byte swizzle, zero fill outside the matrix.
-inline bool make_map(CUtensorMap* map, const void* base, long long rows, long long k, int box_rows = 128) {
+// dimension (`box_cols` = 16 or 32 for narrower boxes), swizzle of the box's row length, zero fill outside
+// the matrix.
+inline bool make_map(CUtensorMap* map, const void* base, long long rows, long long k, int box_rows = 128,
+                     int box_cols = 64) {
   EncodeTiled enc = encode_fn();
   if (!enc) return false;
   cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t elem[2] = {1, 1};
+  // the swizzle span equals the box's row length: 64 elements -> 128 bytes, 32 -> 64, 16 -> 32
+  const CUtensorMapSwizzle swizzle = box_cols == 64   ? CU_TENSOR_MAP_SWIZZLE_128B
+                                     : box_cols == 32 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                      : CU_TENSOR_MAP_SWIZZLE_32B;
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
