@@ -102,7 +102,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
       : "r"(taddr) : "memory");
 }
 
-template <int RK>
+template <int RK, bool SAVE>
 __global__ void __launch_bounds__(THREADS, 1)
 lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_constant__ CUtensorMap map_g,
                    const __grid_constant__ CUtensorMap map_xag, const __grid_constant__ CUtensorMap map_xau,
@@ -279,14 +279,16 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
             const float g0 = fmaf(p.s_up, __uint_as_float(lu[c + 2 * j]), __uint_as_float(gw[j] << 16));
             const float g1 = fmaf(p.s_up, __uint_as_float(lu[c + 2 * j + 1]), __uint_as_float(gw[j] & 0xffff0000u));
             __nv_bfloat162 hb = __floats2bfloat162_rn(Math<true>::fwd(e0, g0, one), Math<true>::fwd(e1, g1, one));
-            __nv_bfloat162 eb = __floats2bfloat162_rn(e0, e1);
-            __nv_bfloat162 gb = __floats2bfloat162_rn(g0, g1);
             hw[j] = *reinterpret_cast<uint32_t*>(&hb);
-            eo[j] = *reinterpret_cast<uint32_t*>(&eb);
-            go[j] = *reinterpret_cast<uint32_t*>(&gb);
+            if constexpr (SAVE) {
+              __nv_bfloat162 eb = __floats2bfloat162_rn(e0, e1);
+              __nv_bfloat162 gb = __floats2bfloat162_rn(g0, g1);
+              eo[j] = *reinterpret_cast<uint32_t*>(&eb);
+              go[j] = *reinterpret_cast<uint32_t*>(&gb);
+            }
           }
           *reinterpret_cast<uint4*>(h_tile + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-          if (p.save) {
+          if constexpr (SAVE) {
             *reinterpret_cast<uint4*>(e_tile + off) = make_uint4(eo[0], eo[1], eo[2], eo[3]);
             *reinterpret_cast<uint4*>(g_tile + off) = make_uint4(go[0], go[1], go[2], go[3]);
           }
@@ -301,13 +303,13 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
         if (elected) {
           const int n0 = (int)(t * TN);
           tma_store_2d(&map_h, n0, m0, h_tile);
-          if (p.save) {
+          if constexpr (SAVE) {
             tma_store_2d(&map_eo, n0, m0, e_tile);
             tma_store_2d(&map_go, n0, m0, g_tile);
           }
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           // the stage may be refilled once nothing reads it any more
-          if (p.save) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          if constexpr (SAVE) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           mbar_arrive(&empty[s]);
           // at most this tile's store stays pending: the previous one has released its h buffer
           asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
@@ -385,13 +387,17 @@ int swiglu_b200_lora_swiglu_fwd(void* h, void* e_out, void* g_out, const void* e
   static std::atomic<int> sms[64];
   int n_sm = dev < 64 ? sms[dev].load(std::memory_order_acquire) : 0;
   if (n_sm == 0) {
-    if (cudaFuncSetAttribute(lora_swiglu_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<16>::SMEM_BYTES) !=
-            cudaSuccess ||
-        cudaFuncSetAttribute(lora_swiglu_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<32>::SMEM_BYTES) !=
-            cudaSuccess ||
-        cudaFuncSetAttribute(lora_swiglu_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<64>::SMEM_BYTES) !=
-            cudaSuccess)
-      return SWIGLU_B200_ERR_DEVICE;
+    bool attr_ok = true;
+    auto set = [&](auto kernel, int bytes) {
+      attr_ok = attr_ok && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+    };
+    set(lora_swiglu_kernel<16, false>, Cfg<16>::SMEM_BYTES);
+    set(lora_swiglu_kernel<16, true>, Cfg<16>::SMEM_BYTES);
+    set(lora_swiglu_kernel<32, false>, Cfg<32>::SMEM_BYTES);
+    set(lora_swiglu_kernel<32, true>, Cfg<32>::SMEM_BYTES);
+    set(lora_swiglu_kernel<64, false>, Cfg<64>::SMEM_BYTES);
+    set(lora_swiglu_kernel<64, true>, Cfg<64>::SMEM_BYTES);
+    if (!attr_ok) return SWIGLU_B200_ERR_DEVICE;
     if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm < 1)
       return SWIGLU_B200_ERR_DEVICE;
     if (dev < 64) sms[dev].store(n_sm, std::memory_order_release);
@@ -403,12 +409,15 @@ int swiglu_b200_lora_swiglu_fwd(void* h, void* e_out, void* g_out, const void* e
   const long long items = ((m + TM - 1) / TM) * ((tiles_n + TILES_PER_RANGE - 1) / TILES_PER_RANGE);
   const unsigned grid = (unsigned)(items < n_sm ? items : n_sm);
   LoraParams p{static_cast<int*>(status), m, n, (int)r, save ? 1 : 0, s_gate, s_up};
+  auto launch = [&](auto kernel, int bytes) {
+    kernel<<<grid, THREADS, bytes, st>>>(me, mg, mxg, mxu, mbg, mbu, mh, meo, mgo, p);
+  };
   if (rk == 16)
-    lora_swiglu_kernel<16><<<grid, THREADS, Cfg<16>::SMEM_BYTES, st>>>(me, mg, mxg, mxu, mbg, mbu, mh, meo, mgo, p);
+    save ? launch(lora_swiglu_kernel<16, true>, Cfg<16>::SMEM_BYTES) : launch(lora_swiglu_kernel<16, false>, Cfg<16>::SMEM_BYTES);
   else if (rk == 32)
-    lora_swiglu_kernel<32><<<grid, THREADS, Cfg<32>::SMEM_BYTES, st>>>(me, mg, mxg, mxu, mbg, mbu, mh, meo, mgo, p);
+    save ? launch(lora_swiglu_kernel<32, true>, Cfg<32>::SMEM_BYTES) : launch(lora_swiglu_kernel<32, false>, Cfg<32>::SMEM_BYTES);
   else
-    lora_swiglu_kernel<64><<<grid, THREADS, Cfg<64>::SMEM_BYTES, st>>>(me, mg, mxg, mxu, mbg, mbu, mh, meo, mgo, p);
+    save ? launch(lora_swiglu_kernel<64, true>, Cfg<64>::SMEM_BYTES) : launch(lora_swiglu_kernel<64, false>, Cfg<64>::SMEM_BYTES);
   if (cudaGetLastError() != cudaSuccess) return SWIGLU_B200_ERR_LAUNCH;
   g_lora_launches.fetch_add(1, std::memory_order_relaxed);
   return SWIGLU_B200_OK;
