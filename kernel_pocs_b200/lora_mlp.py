@@ -17,6 +17,24 @@ from .fused_mlp import _status
 from .swiglu import _as_float, swiglu_forward
 
 
+def fused_lora_swiglu_inplace(
+    e_base: torch.Tensor,
+    g_base: torch.Tensor,
+    xa_gate: Optional[torch.Tensor],
+    xa_up: Optional[torch.Tensor],
+    B_gate: Optional[torch.Tensor],
+    B_up: Optional[torch.Tensor],
+    s_gate: float = 1.0,
+    s_up: float = 1.0,
+    save_eg: bool = False,
+) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """``fused_lora_swiglu`` that, with ``save_eg``, writes e_full / g_full over ``e_base`` / ``g_base`` instead
+    of into fresh tensors (the reference's ``fused_lora_swiglu_inplace``,
+    kernels/lora_mlp/experiments/v6/lora_mlp_kernel_v6.py:81-160: it saves two M x N buffers of peak memory).
+    Safe because a tile of e_base / g_base is staged in shared memory in full before its e / g are stored."""
+    return fused_lora_swiglu(e_base, g_base, xa_gate, xa_up, B_gate, B_up, s_gate, s_up, save_eg, _inplace=True)
+
+
 def fused_lora_swiglu(
     e_base: torch.Tensor,
     g_base: torch.Tensor,
@@ -27,6 +45,7 @@ def fused_lora_swiglu(
     s_gate: float = 1.0,
     s_up: float = 1.0,
     save_eg: bool = False,
+    _inplace: bool = False,
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
     """Returns ``(h, e_full, g_full)`` with ``save_eg``, else ``(h, None, None)``; e_full/g_full are e and g
     with the adapter terms added, as the backward needs them."""
@@ -47,11 +66,13 @@ def fused_lora_swiglu(
     if r % 8 or not 8 <= r <= 64 or n % 8:
         raise ValueError("the kernel needs a rank that is a multiple of 8 in [8, 64] and N % 8 == 0")
     sg, su = _as_float("s_gate", s_gate), _as_float("s_up", s_up)
+    if _inplace and not (e_base.is_contiguous() and g_base.is_contiguous()):
+        raise ValueError("the in-place variant needs contiguous e_base and g_base")
     e_base, g_base = e_base.contiguous(), g_base.contiguous()
     xa_gate, xa_up, B_gate, B_up = (t.contiguous() for t in (xa_gate, xa_up, B_gate, B_up))
     h = torch.empty_like(e_base)
-    e_out = torch.empty_like(e_base) if save_eg else None
-    g_out = torch.empty_like(e_base) if save_eg else None
+    e_out = (e_base if _inplace else torch.empty_like(e_base)) if save_eg else None
+    g_out = (g_base if _inplace else torch.empty_like(e_base)) if save_eg else None
     _lib.check(
         "fused_lora_swiglu",
         _lib.lib.swiglu_b200_lora_swiglu_fwd(

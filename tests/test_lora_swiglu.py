@@ -10,7 +10,7 @@ import torch
 
 from kernel_pocs_b200 import _lib
 from kernel_pocs_b200.fused_mlp import check_status
-from kernel_pocs_b200.lora_mlp import fused_lora_swiglu
+from kernel_pocs_b200.lora_mlp import fused_lora_swiglu, fused_lora_swiglu_inplace
 from tests.test_fused_gemm import assert_close_bf16
 
 pytestmark = pytest.mark.gpu
@@ -77,3 +77,20 @@ def test_argument_errors():
         fused_lora_swiglu(e, g, xag, xau, bg[:32].contiguous(), bu)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         fused_lora_swiglu(e.cpu(), g.cpu(), xag.cpu(), xau.cpu(), bg.cpu(), bu.cpu())
+
+
+@pytest.mark.parametrize("m,n,r", [(200, 200, 24), (1024, 4104, 16)])
+def test_inplace_variant(m, n, r):
+    """e_full / g_full written over e_base / g_base (reference v6:81-160) equal the out-of-place results."""
+    e, g, xag, xau, bg, bu = operands(m, n, r, seed=11)
+    h_ref, e_ref, g_ref = fused_lora_swiglu(e, g, xag, xau, bg, bu, 2.0, 0.5, save_eg=True)
+    e2, g2 = e.clone(), g.clone()
+    h, e_full, g_full = fused_lora_swiglu_inplace(e2, g2, xag, xau, bg, bu, 2.0, 0.5, save_eg=True)
+    check_status(e.device)
+    assert e_full.data_ptr() == e2.data_ptr() and g_full.data_ptr() == g2.data_ptr()
+    assert torch.equal(h, h_ref) and torch.equal(e_full, e_ref) and torch.equal(g_full, g_ref)
+    # without save_eg nothing is overwritten
+    e3 = e.clone()
+    h3, none_e, none_g = fused_lora_swiglu_inplace(e3, g.clone(), xag, xau, bg, bu, 2.0, 0.5)
+    check_status(e.device)
+    assert none_e is None and none_g is None and torch.equal(e3, e) and torch.equal(h3, h_ref)
