@@ -307,17 +307,38 @@ def run_lora(args, device):
         g2.addmm_(xau, bu.t(), alpha=2.0)
         swiglu_forward(e2, g2)
 
-    for provider, fn, nbytes in (("b200-lora-epilogue", fused, 3 * m * n * 2),
-                                 ("b200-lora-epilogue+save", fused_save, 5 * m * n * 2),
-                                 ("addmm_x2+b200-swiglu", unfused, 3 * m * n * 2)):
-        mean, med, best = time_cuda(fn, lambda: None, args.warmup, args.rep)
+    # backward elementwise step of the LoRA MLP: (dh, e, g) -> (h, de, dg) in place, 6*M*N*2 bytes, against
+    # the two kernels that give the same three tensors (forward: 3 passes, backward in place: 5 passes)
+    from kernel_pocs_b200.swiglu import swiglu_backward, swiglu_backward_recompute
+
+    dh = mk(m, n)
+
+    def recompute():
+        swiglu_backward_recompute(dh, e2, g2)
+
+    def fwd_then_bwd():
+        swiglu_forward(e2, g2)
+        swiglu_backward(dh, e2, g2)
+
+    def reseed():
+        # in-place results feed the next repetition; keep the values in the range of the first
+        e2.copy_(e)
+        g2.copy_(gg)
+
+    for provider, fn, nbytes, mode, setup in (
+            ("b200-lora-epilogue", fused, 3 * m * n * 2, "forward", lambda: None),
+            ("b200-lora-epilogue+save", fused_save, 5 * m * n * 2, "forward", lambda: None),
+            ("addmm_x2+b200-swiglu", unfused, 3 * m * n * 2, "forward", lambda: None),
+            ("b200-bwd-recompute", recompute, 6 * m * n * 2, "backward", reseed),
+            ("b200-fwd+b200-bwd", fwd_then_bwd, 8 * m * n * 2, "backward", reseed)):
+        mean, med, best = time_cuda(fn, setup, args.warmup, args.rep)
         check_status(device)
-        r_ = {"config": "lora", "provider": provider, "mode": "forward", "dtype": "bfloat16", "m": m, "n": n, "r": r,
+        r_ = {"config": "lora", "provider": provider, "mode": mode, "dtype": "bfloat16", "m": m, "n": n, "r": r,
               "ms_mean_trimmed": mean, "ms_median": med, "ms_min": best, "algorithmic_bytes_per_gpu": nbytes,
               "gbs_per_gpu": nbytes / (mean * 1e-3) / 1e9, "tokens_per_s": m / (mean * 1e-3)}
         r_["frac_of_measured_copy"] = r_["gbs_per_gpu"] / peak
         rows.append(r_)
-        print(f"{'lora':>16} {provider:>24} forward bf16 M{m} N{n} r{r} {mean:9.4f} ms  {r_['gbs_per_gpu']:8.1f} GB/s  "
+        print(f"{'lora':>16} {provider:>24} {mode:>8} bf16 M{m} N{n} r{r} {mean:9.4f} ms  {r_['gbs_per_gpu']:8.1f} GB/s  "
               f"{100 * r_['frac_of_measured_copy']:6.1f}% of {kind} {peak:.0f}  {r_['tokens_per_s'] / 1e6:8.3f} Mtok/s", flush=True)
     return rows
 

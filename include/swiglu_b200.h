@@ -93,6 +93,17 @@ SWIGLU_B200_API int swiglu_b200_bwd(void* dgate, void* dup, const void* dout, co
                     int64_t cols, int64_t in_row_stride, int64_t grad_row_stride, int64_t dout_row_stride, int dtype,
                     float gm, float dm, int device, void* stream);
 
+/* Backward that also recomputes the forward output, in one pass over six flat tensors of n elements:
+ *   h = silu(gate*gm) * up * dm,  (dgate, dup) as swiglu_b200_bwd  -- each bit-identical to what
+ * swiglu_b200_fwd / swiglu_b200_bwd return for the same inputs.  Replaces the elementwise step of the
+ * reference's LoRA-MLP backward (swiglu_DWf_DW_dfg_kernel, called at
+ * kernels/lora_mlp/experiments/v3/lora_mlp_kernel_v3.py:324, which overwrites DW with h, e with the
+ * gradient of g and g with the gradient of e).  Each output may overwrite ONE input exactly (same address,
+ * any pairing); any other overlap returns SWIGLU_B200_ERR_ALIAS.  Pointers that are not all 16-byte aligned
+ * run at the widest access every one of them allows. */
+SWIGLU_B200_API int swiglu_b200_bwd_recompute(void* h, void* dgate, void* dup, const void* dout, const void* gate,
+                              const void* up, int64_t n, int dtype, float gm, float dm, int device, void* stream);
+
 /* Dry run of the access planning of swiglu_b200_fwd / swiglu_b200_bwd (and their GeGLU twins): which
  * access width and addressing a call with these pointers and strides would use.  No CUDA call is made and
  * no memory is touched, so the host-side planning can be tested without a device.  No counterpart in the

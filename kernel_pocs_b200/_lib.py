@@ -47,6 +47,11 @@ SIGNATURES = {
         [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_i64, _c_i64, ctypes.c_int,
          ctypes.c_int, ctypes.c_int, _c_ptr],
     ),
+    "swiglu_b200_bwd_recompute": (
+        ctypes.c_int,
+        [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, ctypes.c_int, ctypes.c_float, ctypes.c_float,
+         ctypes.c_int, _c_ptr],
+    ),
     "swiglu_b200_host_fwd_bwd": (
         ctypes.c_int,
         [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, ctypes.c_int, ctypes.c_float,

@@ -279,6 +279,16 @@ template <> struct Math<true, ACT_SILU> {
     dup = (dh * c.dm) * (z * sig);
     dgate = ((dh * c.gm_dm) * u) * (sig * fmaf(z, 1.0f - sig, 1.0f));
   }
+  // fwd and bwd of the same element off one exponential; each result is the expression above, bit for bit.
+  static __device__ __forceinline__ void bwd_h(float dh, float g, float u, const Consts& c, float& h, float& dgate,
+                                               float& dup) {
+    const float qr = quarter_recip(g, c);
+    const float sig = qr * 0.25f;
+    const float z = g * c.gm;
+    h = ((g * c.gm_dm_quarter) * qr) * u;
+    dup = (dh * c.dm) * (z * sig);
+    dgate = ((dh * c.gm_dm) * u) * (sig * fmaf(z, 1.0f - sig, 1.0f));
+  }
 };
 
 template <> struct Math<false, ACT_SILU> {
@@ -295,6 +305,17 @@ template <> struct Math<false, ACT_SILU> {
     float sig = 1.0f / den;
     float silu = z / den;
     float d = dh * c.dm;
+    dup = d * silu;
+    dgate = (((d * u) * sig) * (1.0f + z * (1.0f - sig))) * c.gm;
+  }
+  static __device__ __forceinline__ void bwd_h(float dh, float g, float u, const Consts& c, float& h, float& dgate,
+                                               float& dup) {
+    float z = g * c.gm;
+    float den = 1.0f + expf(-z);
+    float sig = 1.0f / den;
+    float silu = z / den;
+    float d = dh * c.dm;
+    h = (silu * u) * c.dm;
     dup = d * silu;
     dgate = (((d * u) * sig) * (1.0f + z * (1.0f - sig))) * c.gm;
   }
@@ -695,6 +716,79 @@ swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const v
       St<ES, ST_PLAIN>::st(byte(dgate) + off, vdg);
       St<ES, ST_PLAIN>::st(byte(dup) + off, vdu);
     }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Backward that also recomputes the forward output: (h, dgate, dup) from (dh, gate, up) in one
+// pass over flat, equally laid out tensors -- what a training step that kept gate and up but
+// not h needs (the LoRA-MLP backward, whose down-projection adapter gradients contract with h).
+// Every thread loads its three vectors before it stores, so each output may overwrite any one
+// of the inputs exactly; LDM must then be a coherent load mode.  `n_vec` vectors of BYTES
+// bytes, then `tail` scalar elements handled by the last CTA.
+// ---------------------------------------------------------------------------------------
+
+template <class T, int BYTES, bool FAST, int THREADS, int UNROLL, int LDM, int STM>
+__global__ void __launch_bounds__(THREADS)
+swiglu_bwd_recompute_kernel(void* h, void* dgate, void* dup, const void* dout, const void* gate, const void* up,
+                            long long n_vec, int tail, float gm, float dm) {
+  constexpr int EPV = BYTES / Codec<T>::kSize;
+  constexpr long long TILE = (long long)THREADS * UNROLL;
+  const long long n_tiles = (n_vec + TILE - 1) / TILE;
+  const Consts c(gm, dm);
+
+  for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const long long v0 = tile * TILE + threadIdx.x;
+    const bool full = (tile + 1) * TILE <= n_vec;
+    Vec<BYTES> d[UNROLL], g[UNROLL], u[UNROLL];
+#pragma unroll
+    for (int k = 0; k < UNROLL; ++k) {
+      const long long i = v0 + (long long)k * THREADS;
+      if (full || i < n_vec) {
+        d[k] = Ld<BYTES, LDM>::ld(cbyte(dout) + i * BYTES);
+        g[k] = Ld<BYTES, LDM>::ld(cbyte(gate) + i * BYTES);
+        u[k] = Ld<BYTES, LDM>::ld(cbyte(up) + i * BYTES);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < UNROLL; ++k) {
+      const long long i = v0 + (long long)k * THREADS;
+      if (full || i < n_vec) {
+        float fd[EPV], fg[EPV], fu[EPV], fh[EPV], fdg[EPV], fdu[EPV];
+        Codec<T>::template unpack<BYTES>(d[k], fd);
+        Codec<T>::template unpack<BYTES>(g[k], fg);
+        Codec<T>::template unpack<BYTES>(u[k], fu);
+#pragma unroll
+        for (int e = 0; e < EPV; ++e) Math<FAST, ACT_SILU>::bwd_h(fd[e], fg[e], fu[e], c, fh[e], fdg[e], fdu[e]);
+        Vec<BYTES> vh, vdg, vdu;
+        Codec<T>::template pack<BYTES>(fh, vh);
+        Codec<T>::template pack<BYTES>(fdg, vdg);
+        Codec<T>::template pack<BYTES>(fdu, vdu);
+        St<BYTES, STM>::st(byte(h) + i * BYTES, vh);
+        St<BYTES, STM>::st(byte(dgate) + i * BYTES, vdg);
+        St<BYTES, STM>::st(byte(dup) + i * BYTES, vdu);
+      }
+    }
+  }
+
+  if (blockIdx.x == gridDim.x - 1 && (int)threadIdx.x < tail) {
+    constexpr int ES = Codec<T>::kSize;
+    const long long off = (n_vec * EPV + threadIdx.x) * ES;
+    Vec<ES> vd = Ld<ES, LD_PLAIN>::ld(cbyte(dout) + off);
+    Vec<ES> vg = Ld<ES, LD_PLAIN>::ld(cbyte(gate) + off);
+    Vec<ES> vu = Ld<ES, LD_PLAIN>::ld(cbyte(up) + off);
+    float fd[1], fg[1], fu[1], fh[1], fdg[1], fdu[1];
+    Codec<T>::template unpack<ES>(vd, fd);
+    Codec<T>::template unpack<ES>(vg, fg);
+    Codec<T>::template unpack<ES>(vu, fu);
+    Math<FAST, ACT_SILU>::bwd_h(fd[0], fg[0], fu[0], c, fh[0], fdg[0], fdu[0]);
+    Vec<ES> vh, vdg, vdu;
+    Codec<T>::template pack<ES>(fh, vh);
+    Codec<T>::template pack<ES>(fdg, vdg);
+    Codec<T>::template pack<ES>(fdu, vdu);
+    St<ES, ST_PLAIN>::st(byte(h) + off, vh);
+    St<ES, ST_PLAIN>::st(byte(dgate) + off, vdg);
+    St<ES, ST_PLAIN>::st(byte(dup) + off, vdu);
   }
 }
 

@@ -5,6 +5,11 @@ same argument order, same return triple), the one kernel of its LoRA-MLP forward
 the base projections and the skinny ``x @ A.T`` products stay with cuBLAS, and this step adds the rank-r
 adapter terms and applies SwiGLU in one pass over e and g.  Here it is a TMA-fed tcgen05 kernel
 (``swiglu_b200_lora_swiglu_fwd``).  bf16 only; the rank must be a multiple of 8, at most 64.
+
+``LoRAMLP`` / ``lora_mlp`` put that kernel where the reference's ``LoRAMLPv3`` / ``lora_mlp_v3`` put theirs
+(same file, :244-357): library GEMMs for every projection, the fused epilogue in the forward (in place over
+the base projections, as in the reference's v6), and in the backward one elementwise pass
+(``swiglu_b200_bwd_recompute``) that turns (dh, e, g) into (h, de, dg).
 """
 from __future__ import annotations
 
@@ -14,7 +19,7 @@ import torch
 
 from . import _lib
 from .fused_mlp import _status
-from .swiglu import _as_float, swiglu_forward
+from .swiglu import _as_float, swiglu_backward_recompute, swiglu_forward
 
 
 def fused_lora_swiglu_inplace(
@@ -83,3 +88,101 @@ def fused_lora_swiglu(
         ),
     )
     return h, e_out, g_out
+
+
+def swiglu_DWf_DW_dfg_kernel(DW: torch.Tensor, e: torch.Tensor, g: torch.Tensor):
+    """The elementwise step of the reference's LoRA-MLP backward under its own name and buffer convention
+    (kernels/lora_mlp/reference/unsloth_baseline.py:155-170, called at experiments/v3/lora_mlp_kernel_v3.py:324):
+    overwrites ``DW`` with ``h = silu(e) * g``, ``e`` with ``DW * silu(e)`` (the gradient of g) and ``g`` with
+    ``DW * g * silu'(e)`` (the gradient of e), and returns the three buffers in that order."""
+    if not (DW.is_contiguous() and e.is_contiguous() and g.is_contiguous()):
+        raise ValueError("DW, e and g must be contiguous: they are overwritten in place")
+    if DW.shape != e.shape or e.shape != g.shape or DW.dtype != e.dtype or g.dtype != e.dtype:
+        raise ValueError("DW, e and g must share one shape and dtype")
+    if not e.is_cuda:
+        raise RuntimeError("swiglu_DWf_DW_dfg_kernel has a CUDA (sm_100a) kernel only; there is no CPU fallback")
+    from .swiglu import _DTYPE_CODE, _check_cuda_dtype, _stream
+
+    _check_cuda_dtype(e)
+    _lib.check(
+        "swiglu_DWf_DW_dfg_kernel",
+        _lib.lib.swiglu_b200_bwd_recompute(
+            DW.data_ptr(), g.data_ptr(), e.data_ptr(), DW.data_ptr(), e.data_ptr(), g.data_ptr(),
+            e.numel(), _DTYPE_CODE[e.dtype], 1.0, 1.0, e.device.index, _stream(e.device),
+        ),
+    )
+    return DW, e, g
+
+
+def _lora_mlp_forward(X, W_gate, A_gate, B_gate, s_gate, W_up, A_up, B_up, s_up, W_down, A_down, B_down, s_down,
+                      save_eg):
+    x2 = X.reshape(-1, X.shape[-1])
+    e = x2 @ W_gate.t()
+    g = x2 @ W_up.t()
+    r = A_gate.shape[0] if A_gate is not None else 0
+    if A_gate is not None and X.dtype == torch.bfloat16 and r % 8 == 0 and 8 <= r <= 64 and e.shape[1] % 8 == 0:
+        h, e, g = fused_lora_swiglu_inplace(e, g, x2 @ A_gate.t(), x2 @ A_up.t(), B_gate, B_up, s_gate, s_up,
+                                            save_eg=save_eg)
+    else:
+        # fp16 / fp32, or a rank the tensor-core epilogue does not take: adapter terms by library GEMMs
+        if A_gate is not None:
+            e.addmm_(x2 @ A_gate.t(), B_gate.t(), alpha=s_gate)
+            g.addmm_(x2 @ A_up.t(), B_up.t(), alpha=s_up)
+        h = swiglu_forward(e, g)[0]
+    out = h @ W_down.t()
+    if A_down is not None:
+        out.addmm_(h @ A_down.t(), B_down.t(), alpha=s_down)
+    return out.view(*X.shape[:-1], out.shape[-1]), e, g
+
+
+def lora_mlp(X, W_gate, A_gate, B_gate, s_gate, W_up, A_up, B_up, s_up, W_down, A_down, B_down, s_down):
+    """LoRA MLP forward without autograd: ``down(silu(gate(X)) * up(X))``, every projection ``X W^T + s (X A^T) B^T``
+    with W ``[out, in]``, A ``[r, in]``, B ``[out, r]``.  Argument order of the reference's ``lora_mlp_v3``
+    (kernels/lora_mlp/experiments/v3/lora_mlp_kernel_v3.py:244-256); adapters may be ``None``."""
+    with torch.no_grad():
+        return _lora_mlp_forward(X, W_gate, A_gate, B_gate, s_gate, W_up, A_up, B_up, s_up, W_down, A_down, B_down,
+                                 s_down, save_eg=False)[0]
+
+
+class LoRAMLP(torch.autograd.Function):
+    """Trainable LoRA MLP: gradients for X and the six adapter matrices, base weights frozen.  Same ``apply``
+    arguments and gradient tuple as the reference's ``LoRAMLPv3`` (lora_mlp_kernel_v3.py:259-357).  The forward
+    keeps X and the adapter-corrected e, g (not h); the backward recomputes h and overwrites the saved e and g
+    with their gradients, so a graph can be walked once."""
+
+    @staticmethod
+    def forward(ctx, X, W_gate, A_gate, B_gate, s_gate, W_up, A_up, B_up, s_up, W_down, A_down, B_down, s_down):
+        out, e, g = _lora_mlp_forward(X, W_gate, A_gate, B_gate, s_gate, W_up, A_up, B_up, s_up, W_down, A_down,
+                                      B_down, s_down, save_eg=True)
+        ctx.save_for_backward(X, e, g, A_gate, B_gate, A_up, B_up, A_down, B_down)
+        ctx.base_weights = (W_gate, W_up, W_down)
+        ctx.scales = (s_gate, s_up, s_down)
+        return out
+
+    @staticmethod
+    def backward(ctx, dY):
+        X, e, g, A_gate, B_gate, A_up, B_up, A_down, B_down = ctx.saved_tensors
+        W_gate, W_up, W_down = ctx.base_weights
+        s_gate, s_up, s_down = ctx.scales
+        x2 = X.reshape(-1, X.shape[-1])
+        dy = dY.reshape(-1, dY.shape[-1])
+
+        # through the down projection: dh = dY W_d + s_d (dY B_d) A_d
+        dyB = dy @ B_down                                   # [M, r]
+        dh = dy @ W_down
+        dh.addmm_(dyB, A_down, alpha=s_down)
+        h, de, dg = swiglu_backward_recompute(dh, e, g)     # in place: dh <- h, e <- de, g <- dg
+        dA_down = s_down * (dyB.t() @ h)                    # [r, I]
+        dB_down = s_down * (dy.t() @ (h @ A_down.t()))      # [H, r]
+
+        deB, dgB = de @ B_gate, dg @ B_up                   # [M, r]
+        dA_gate = s_gate * (deB.t() @ x2)                   # [r, H]
+        dB_gate = s_gate * (de.t() @ (x2 @ A_gate.t()))     # [I, r]
+        dA_up = s_up * (dgB.t() @ x2)
+        dB_up = s_up * (dg.t() @ (x2 @ A_up.t()))
+
+        dX = de @ W_gate
+        dX.addmm_(dg, W_up)
+        dX.addmm_(deB, A_gate, alpha=s_gate)
+        dX.addmm_(dgB, A_up, alpha=s_up)
+        return (dX.view_as(X), None, dA_gate, dB_gate, None, None, dA_up, dB_up, None, None, dA_down, dB_down, None)

@@ -189,6 +189,45 @@ def swiglu_backward(
     return dgate.view(shape), dup.view(shape)
 
 
+def swiglu_backward_recompute(
+    dout: torch.Tensor,
+    gate: torch.Tensor,
+    up: torch.Tensor,
+    gate_multiplier: float = 1.0,
+    down_multiplier: float = 1.0,
+    preserve_inputs: bool = False,
+):
+    """Returns ``(h, dgate, dup)`` from one pass over ``(dout, gate, up)``: the backward of ``swiglu`` together with
+    its forward output, for training steps that kept ``gate`` and ``up`` but not ``h`` (the reference's LoRA-MLP
+    backward, kernels/lora_mlp/experiments/v3/lora_mlp_kernel_v3.py:324).  Unless ``preserve_inputs`` is set, ``h`` is
+    written over ``dout``, ``dgate`` over ``gate`` and ``dup`` over ``up``.  No counterpart among the reference's
+    ``kernels.swiglu`` names."""
+    _check_same_shape_inputs(gate, up)
+    _check_cuda_dtype(gate)
+    _require_cuda(gate, "gate")
+    gm = _as_float("gate_multiplier", gate_multiplier)
+    dm = _as_float("down_multiplier", down_multiplier)
+    if dout.dtype != gate.dtype or dout.device != gate.device:
+        raise TypeError("dout must have the dtype and device of gate and up")
+    if dout.shape != gate.shape:
+        raise ValueError(f"dout of shape {tuple(dout.shape)} does not match gate of shape {tuple(gate.shape)}")
+    if preserve_inputs:
+        dout, gate, up = dout.contiguous(), gate.contiguous(), up.contiguous()
+        h, dgate, dup = torch.empty_like(dout), torch.empty_like(gate), torch.empty_like(up)
+    else:
+        if not (dout.is_contiguous() and gate.is_contiguous() and up.is_contiguous()):
+            raise ValueError("the in-place form needs contiguous dout, gate and up; pass preserve_inputs=True")
+        h, dgate, dup = dout, gate, up
+    _lib.check(
+        "swiglu_backward_recompute",
+        _lib.lib.swiglu_b200_bwd_recompute(
+            h.data_ptr(), dgate.data_ptr(), dup.data_ptr(), dout.data_ptr(), gate.data_ptr(), up.data_ptr(),
+            gate.numel(), _DTYPE_CODE[gate.dtype], gm, dm, gate.device.index, _stream(gate.device),
+        ),
+    )
+    return h, dgate, dup
+
+
 def swiglu_packed_forward(
     gate_up: torch.Tensor,
     gate_multiplier: float = 1.0,

@@ -1,0 +1,184 @@
+"""LoRA MLP (library GEMMs + the fused LoRA/SwiGLU epilogue + the backward-with-recompute kernel) against a
+plain PyTorch composite under autograd, with the structure of the reference's own tests for its LoRAMLPv3
+(kernels/lora_mlp/tests/test_lora_mlp.py:428-560: fp32 backward against the PyTorch reference, bf16 with its
+loose tolerances), and the recompute kernel against this library's forward and backward kernels, bit for bit."""
+import pytest
+import torch
+
+from kernel_pocs_b200 import _lib
+from kernel_pocs_b200.fused_mlp import check_status
+from kernel_pocs_b200.lora_mlp import LoRAMLP, lora_mlp, swiglu_DWf_DW_dfg_kernel
+from kernel_pocs_b200.swiglu import swiglu_backward, swiglu_backward_recompute, swiglu_forward
+
+pytestmark = pytest.mark.gpu
+DEVICE = "cuda"
+DTYPES = [torch.float32, torch.float16, torch.bfloat16]
+
+
+def rand3(shape, dtype, seed, offset=0):
+    g = torch.Generator(device=DEVICE).manual_seed(seed)
+    n = 1
+    for d in shape:
+        n *= d
+    out = []
+    for _ in range(3):
+        buf = (1.5 * torch.randn(n + 16, generator=g, device=DEVICE)).to(dtype)
+        out.append(buf[offset:offset + n].view(*shape))
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1,), (7,), (3, 5, 257), (64, 1024), (1000, 1101), (2048, 14336)])
+@pytest.mark.parametrize("multipliers", [(1.0, 1.0), (0.7, 1.3)])
+def test_recompute_equals_forward_and_backward(dtype, shape, multipliers):
+    gm, dm = multipliers
+    dh, gate, up = rand3(shape, dtype, seed=21)
+    h_ref = swiglu_forward(gate, up, gm, dm)[0]
+    dgate_ref, dup_ref = swiglu_backward(dh, gate, up, gm, dm, preserve_inputs=True)
+    before = _lib.launch_count()
+    h, dgate, dup = swiglu_backward_recompute(dh, gate, up, gm, dm, preserve_inputs=True)
+    assert _lib.launch_count() == before + 1
+    assert torch.equal(h.view(torch.uint8), h_ref.view(torch.uint8))
+    assert torch.equal(dgate.view(torch.uint8), dgate_ref.view(torch.uint8))
+    assert torch.equal(dup.view(torch.uint8), dup_ref.view(torch.uint8))
+    # in place: h over dh, dgate over gate, dup over up
+    dh2, gate2, up2 = dh.clone(), gate.clone(), up.clone()
+    h2, dgate2, dup2 = swiglu_backward_recompute(dh2, gate2, up2, gm, dm)
+    assert h2.data_ptr() == dh2.data_ptr() and dgate2.data_ptr() == gate2.data_ptr() and dup2.data_ptr() == up2.data_ptr()
+    assert torch.equal(h2.view(torch.uint8), h_ref.view(torch.uint8))
+    assert torch.equal(dgate2.view(torch.uint8), dgate_ref.view(torch.uint8))
+    assert torch.equal(dup2.view(torch.uint8), dup_ref.view(torch.uint8))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("offset", [1, 2, 4])
+def test_recompute_misaligned_buffers(dtype, offset):
+    dh, gate, up = rand3((33, 1001), dtype, seed=22, offset=offset)
+    h_ref = swiglu_forward(gate.clone(), up.clone())[0]
+    dgate_ref, dup_ref = swiglu_backward(dh.clone(), gate.clone(), up.clone(), preserve_inputs=True)
+    h, dgate, dup = swiglu_backward_recompute(dh, gate, up)   # in place, on the misaligned views
+    assert torch.equal(h.view(torch.uint8), h_ref.view(torch.uint8))
+    assert torch.equal(dgate.view(torch.uint8), dgate_ref.view(torch.uint8))
+    assert torch.equal(dup.view(torch.uint8), dup_ref.view(torch.uint8))
+
+
+def test_reference_buffer_convention():
+    """DW <- h, e <- gradient of g, g <- gradient of e (the cross pairing of the reference's backward step)."""
+    dw, e, g = rand3((256, 1536), torch.bfloat16, seed=23)
+    h_ref = swiglu_forward(e, g)[0]
+    de_ref, dg_ref = swiglu_backward(dw, e, g, preserve_inputs=True)
+    a, b, c = swiglu_DWf_DW_dfg_kernel(dw, e, g)
+    assert a is dw and b is e and c is g
+    assert torch.equal(dw, h_ref) and torch.equal(e, dg_ref) and torch.equal(g, de_ref)
+
+
+def test_recompute_alias_errors():
+    dh, gate, up = rand3((4, 64), torch.bfloat16, seed=24)
+    lib, st = _lib.lib, torch.cuda.current_stream().cuda_stream
+    out = torch.empty(3, 4 * 64, dtype=torch.bfloat16, device=DEVICE)
+    args = (4 * 64, 2, 1.0, 1.0, 0, st)
+    # two outputs on one buffer; an output overlapping an input at an offset
+    assert lib.swiglu_b200_bwd_recompute(out[0].data_ptr(), out[0].data_ptr(), out[2].data_ptr(), dh.data_ptr(),
+                                         gate.data_ptr(), up.data_ptr(), *args) == 5
+    assert lib.swiglu_b200_bwd_recompute(out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(),
+                                         out[0].data_ptr() + 32, gate.data_ptr(), up.data_ptr(), *args) == 5
+    assert lib.swiglu_b200_bwd_recompute(None, out[1].data_ptr(), out[2].data_ptr(), dh.data_ptr(),
+                                         gate.data_ptr(), up.data_ptr(), *args) == 2
+    assert lib.swiglu_b200_bwd_recompute(out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(), dh.data_ptr(),
+                                         gate.data_ptr(), up.data_ptr(), 0, 2, 1.0, 1.0, 0, st) == 0
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        swiglu_backward_recompute(dh.cpu(), gate.cpu(), up.cpu())
+
+
+# ------------------------------------------------------------------------------------------------ the MLP
+
+def make_params(hidden, inter, rank, dtype, seed=42):
+    g = torch.Generator(device=DEVICE).manual_seed(seed)
+    mk = lambda *s, std: (std * torch.randn(*s, generator=g, device=DEVICE)).to(dtype)
+    p = {}
+    for name, (o, i) in dict(gate=(inter, hidden), up=(inter, hidden), down=(hidden, inter)).items():
+        p[f"W_{name}"] = mk(o, i, std=i ** -0.5)
+        p[f"A_{name}"] = mk(rank, i, std=i ** -0.5)
+        p[f"B_{name}"] = mk(o, rank, std=0.3)      # non-zero, so that every gradient is exercised
+        p[f"s_{name}"] = 2.0
+    return p
+
+
+def composite(X, p):
+    proj = lambda x, n: x @ p[f"W_{n}"].t() + p[f"s_{n}"] * ((x @ p[f"A_{n}"].t()) @ p[f"B_{n}"].t())
+    return proj(torch.nn.functional.silu(proj(X, "gate")) * proj(X, "up"), "down")
+
+
+def args_of(X, p):
+    return (X, p["W_gate"], p["A_gate"], p["B_gate"], p["s_gate"], p["W_up"], p["A_up"], p["B_up"], p["s_up"],
+            p["W_down"], p["A_down"], p["B_down"], p["s_down"])
+
+
+GRADS = ["A_gate", "B_gate", "A_up", "B_up", "A_down", "B_down"]
+
+
+def run_with_grads(fn, X, p, dY):
+    X = X.detach().clone().requires_grad_(True)
+    q = {k: (v.detach().clone().requires_grad_(k in GRADS) if isinstance(v, torch.Tensor) else v)
+         for k, v in p.items()}
+    out = fn(X, q)
+    out.backward(dY)
+    return out.detach(), [X.grad] + [q[k].grad for k in GRADS]
+
+
+@pytest.mark.parametrize("shape,rank", [((2, 32, 128, 256), 8), ((1, 100, 192, 520), 16), ((3, 17, 64, 136), 24)])
+def test_mlp_fp32_matches_composite(shape, rank):
+    b, s, hidden, inter = shape
+    p = make_params(hidden, inter, rank, torch.float32)
+    X = torch.randn(b, s, hidden, device=DEVICE)
+    dY = torch.randn(b, s, hidden, device=DEVICE)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        out_ref, grads_ref = run_with_grads(composite, X, p, dY)
+        out, grads = run_with_grads(lambda x, q: LoRAMLP.apply(*args_of(x, q)), X, p, dY)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    torch.testing.assert_close(out, out_ref, rtol=1e-4, atol=1e-4)
+    for name, a, r in zip(["X"] + GRADS, grads, grads_ref):
+        torch.testing.assert_close(a, r, rtol=1e-3, atol=1e-3 * float(r.abs().max()), msg=lambda m: f"d{name}: {m}")
+
+
+@pytest.mark.parametrize("shape,rank", [((2, 32, 128, 256), 8), ((2, 256, 512, 1408), 16), ((1, 333, 256, 1096), 32),
+                                        ((4, 512, 1024, 2816), 64), ((1, 64, 128, 264), 12)])
+def test_mlp_bf16_matches_fp32_composite(shape, rank):
+    """bf16 run against the fp32 composite of the same bf16 parameters; bound per tensor: 3 % of its largest
+    magnitude (the reference's own bf16 check uses rtol 5e-2 with atol 2.0, test_lora_mlp.py:907-933)."""
+    b, s, hidden, inter = shape
+    p = make_params(hidden, inter, rank, torch.bfloat16)
+    g = torch.Generator(device=DEVICE).manual_seed(7)
+    X = torch.randn(b, s, hidden, generator=g, device=DEVICE).bfloat16()
+    dY = torch.randn(b, s, hidden, generator=g, device=DEVICE).bfloat16()
+    p32 = {k: (v.float() if isinstance(v, torch.Tensor) else v) for k, v in p.items()}
+    out_ref, grads_ref = run_with_grads(composite, X.float(), p32, dY.float())
+    before = _lib.lib.swiglu_b200_lora_launch_count()
+    out, grads = run_with_grads(lambda x, q: LoRAMLP.apply(*args_of(x, q)), X, p, dY)
+    check_status(X.device)
+    fused = rank % 8 == 0
+    assert _lib.lib.swiglu_b200_lora_launch_count() == before + (1 if fused else 0)
+    assert out.dtype == torch.bfloat16 and out.shape == X.shape
+    for name, a, r in zip(["out", "X"] + GRADS, [out] + grads, [out_ref] + grads_ref):
+        assert a.shape == r.shape and a.dtype == torch.bfloat16, name
+        err = (a.float() - r).abs().max().item()
+        assert err <= 0.03 * r.abs().max().item(), f"{name}: max err {err} against max |ref| {r.abs().max().item()}"
+    # inference entry: same forward, 2-D input, no autograd graph
+    out2 = lora_mlp(*args_of(X.view(-1, hidden), p))
+    assert out2.shape == (b * s, hidden) and not out2.requires_grad
+    assert torch.equal(out2.view_as(out), out)
+
+
+def test_mlp_without_adapters_and_determinism():
+    p = make_params(128, 256, 8, torch.bfloat16)
+    X = torch.randn(2, 16, 128, device=DEVICE).bfloat16()
+    q = dict(p, A_gate=None, B_gate=None, A_up=None, B_up=None, A_down=None, B_down=None)
+    out = lora_mlp(*args_of(X, q))
+    ref = (torch.nn.functional.silu(X.float() @ p["W_gate"].float().t()) * (X.float() @ p["W_up"].float().t())) \
+        @ p["W_down"].float().t()
+    assert (out.float() - ref).abs().max() <= 0.03 * ref.abs().max()
+    a, b = lora_mlp(*args_of(X, p)), lora_mlp(*args_of(X, p))
+    assert torch.equal(a, b) and torch.isfinite(a).all()
