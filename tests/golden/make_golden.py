@@ -8,6 +8,10 @@ kernels/swiglu/swiglu.py:396-397, with the backward by autograd).  Shapes, seeds
 and multipliers follow the reference's tests/test_swiglu.py:28-113; the extra cases are the
 benchmark configuration "fp32 [2,128,1024], seed 0" and wide-tailed N(0, 2^2) inputs.
 
+lora_mlp.npz comes from the reference's own ground truth for its LoRA-MLP kernels,
+kernels/lora_mlp/reference/lora_mlp_pytorch.py (``matmul_lora``, ``lora_swiglu_mlp`` and the autograd Function
+``LoRAMLP``, the comparators of kernels/lora_mlp/tests/test_lora_mlp.py), run on CPU in fp32 and bf16.
+
 The reference checkout is needed only to regenerate the vectors; the tests read the .npz
 files.  Arrays hold raw storage: float32, or uint16 bit patterns for fp16/bf16.
 """
@@ -159,6 +163,49 @@ def main() -> None:
             for name, t in dict(gate_up=gate_up, dout=dout, h=h.detach(), dgate_up=gu.grad).items():
                 out[f"{key}|{name}"] = bits(t)
     np.savez_compressed(HERE / "geglu.npz", **out)
+
+    # --- LoRA MLP: the reference's PyTorch ground truth (kernels/lora_mlp/reference/lora_mlp_pytorch.py) ------
+    sys.path.insert(0, str(Path(args.reference) / "kernels" / "lora_mlp"))
+    from reference import lora_mlp_pytorch as ref_lora  # as kernels/lora_mlp/tests/test_lora_mlp.py:21 imports it
+
+    assert Path(ref_lora.__file__).resolve().is_relative_to(Path(args.reference).resolve())
+    out = {}
+    for dname, dtype in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+        for b, s_, hidden, inter, rank in [(2, 32, 128, 256, 8), (1, 50, 64, 144, 16)]:
+            g = torch.Generator().manual_seed(42)
+            mk = lambda *shape, std: (std * torch.randn(*shape, generator=g)).to(dtype)
+            p = {}
+            for name, (o, i) in dict(gate=(inter, hidden), up=(inter, hidden), down=(hidden, inter)).items():
+                p[f"W_{name}"] = mk(o, i, std=i ** -0.5)
+                p[f"A_{name}"] = mk(rank, i, std=i ** -0.5).requires_grad_(True)
+                p[f"B_{name}"] = mk(o, rank, std=0.3).requires_grad_(True)
+                p[f"s_{name}"] = 2.0
+            X = mk(b, s_, hidden, std=1.0).requires_grad_(True)
+            dY = mk(b, s_, hidden, std=1.0)
+            y = ref_lora.LoRAMLP.apply(
+                X, p["W_gate"], p["A_gate"], p["B_gate"], p["s_gate"], p["W_up"], p["A_up"], p["B_up"], p["s_up"],
+                p["W_down"], p["A_down"], p["B_down"], p["s_down"])
+            y.backward(dY)
+            with torch.no_grad():
+                e = ref_lora.matmul_lora(X, p["W_gate"], p["A_gate"], p["B_gate"], p["s_gate"])
+                gg = ref_lora.matmul_lora(X, p["W_up"], p["A_up"], p["B_up"], p["s_up"])
+                h = torch.nn.functional.silu(e) * gg
+                y_fn = ref_lora.lora_swiglu_mlp(X, **p)
+                e0 = ref_lora.matmul_lora(X, p["W_gate"], None, None, 1.0)
+                g0 = ref_lora.matmul_lora(X, p["W_up"], None, None, 1.0)
+                h0 = torch.nn.functional.silu(e0) * g0
+                y0 = ref_lora.lora_swiglu_mlp(X, p["W_gate"], None, None, 1.0, p["W_up"], None, None, 1.0,
+                                              p["W_down"], None, None, 1.0)
+            key = f"{dname}|{b}x{s_}x{hidden}x{inter}x{rank}"
+            tensors = dict(X=X, dY=dY, out=y, out_functional=y_fn, e=e, g=gg, h=h, dX=X.grad,
+                           e_noadapter=e0, g_noadapter=g0, h_noadapter=h0, out_noadapter=y0)
+            for name in ("gate", "up", "down"):
+                tensors[f"W_{name}"] = p[f"W_{name}"]
+                tensors[f"A_{name}"], tensors[f"dA_{name}"] = p[f"A_{name}"], p[f"A_{name}"].grad
+                tensors[f"B_{name}"], tensors[f"dB_{name}"] = p[f"B_{name}"], p[f"B_{name}"].grad
+            for name, t in tensors.items():
+                out[f"{key}|{name}"] = bits(t)
+    np.savez_compressed(HERE / "lora_mlp.npz", **out)
 
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size, "bytes")

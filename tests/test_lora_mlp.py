@@ -182,3 +182,82 @@ def test_mlp_without_adapters_and_determinism():
     assert (out.float() - ref).abs().max() <= 0.03 * ref.abs().max()
     a, b = lora_mlp(*args_of(X, p)), lora_mlp(*args_of(X, p))
     assert torch.equal(a, b) and torch.isfinite(a).all()
+
+
+# ------------------------------------------------------------------- vectors produced by the reference itself
+
+def golden_cases(golden_dir):
+    import numpy as np
+
+    from tests.test_oracle_golden import _cases, load_lora_case
+    from tests._util import DTYPES as BY_NAME
+
+    z = np.load(golden_dir / "lora_mlp.npz")
+    for key in _cases(z):
+        dtype = BY_NAME[key.split("|")[0]]
+        t, p = load_lora_case(z, key, dtype)
+        yield key, dtype, {k: v.to(DEVICE) for k, v in t.items()}, \
+            {k: (v.to(DEVICE) if isinstance(v, torch.Tensor) else v) for k, v in p.items()}
+
+
+def test_mlp_matches_reference_vectors(golden_dir):
+    """LoRAMLP on the inputs of tests/golden/lora_mlp.npz against what the reference's own LoRAMLP (its PyTorch
+    ground truth, kernels/lora_mlp/reference/lora_mlp_pytorch.py:113-236) returned for them, and against the
+    float64 oracle: fp32 to 1e-4 of each tensor's largest magnitude, bf16 to 3 %."""
+    from oracle import lora_oracle as L
+
+    seen = 0
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        for key, dtype, t, p in golden_cases(golden_dir):
+            out, grads = run_with_grads(lambda x, q: LoRAMLP.apply(*args_of(x, q)), t["X"], p, t["dY"])
+            check_status(t["X"].device)
+            truth = L.lora_mlp_fwd_bwd(t["X"].double().cpu().numpy(),
+                                       {k: (v.double().cpu().numpy() if isinstance(v, torch.Tensor) else v)
+                                        for k, v in p.items()}, t["dY"].double().cpu().numpy())
+            bound = 1e-4 if dtype == torch.float32 else 3e-2
+            names = ["out", "dX"] + ["d" + n for n in GRADS]
+            for name, got in zip(names, [out] + grads):
+                ref = t[name].double().reshape(got.shape)
+                assert got.dtype == dtype
+                err = (got.double() - ref).abs().max().item()
+                assert err <= bound * ref.abs().max().item(), f"{key} {name} vs reference vectors: {err}"
+                tr = torch.from_numpy(truth[name]).to(DEVICE).reshape(got.shape)
+                err = (got.double() - tr).abs().max().item()
+                assert err <= bound * tr.abs().max().item(), f"{key} {name} vs float64 oracle: {err}"
+            seen += 1
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    assert seen == 4
+
+
+def test_epilogue_and_fused_projection_match_reference_vectors(golden_dir):
+    """bf16 vectors: the LoRA epilogue fed with cuBLAS base projections against the reference's e, g, h, and the
+    fused gate/up GEMM against its adapter-free h.  The reference rounds e and g to bf16 before the activation and
+    its CPU GEMMs accumulate differently, so the bound is the bf16 one: 2^-7 |ref| + 2^-7 rms(ref)."""
+    from kernel_pocs_b200.fused_mlp import gate_up_swiglu_forward
+    from kernel_pocs_b200.lora_mlp import fused_lora_swiglu
+
+    def close(got, ref, what):
+        ref = ref.float().reshape(got.shape)
+        err = (got.float() - ref).abs()
+        tol = 2.0 ** -7 * ref.abs() + 2.0 ** -7 * ref.pow(2).mean().sqrt()
+        assert bool((err <= tol).all()), f"{what}: worst excess {(err - tol).max().item()}"
+
+    seen = 0
+    for key, dtype, t, p in golden_cases(golden_dir):
+        if dtype != torch.bfloat16:
+            continue
+        x2 = t["X"].reshape(-1, t["X"].shape[-1])
+        h, e, g = fused_lora_swiglu(x2 @ p["W_gate"].t(), x2 @ p["W_up"].t(), x2 @ p["A_gate"].t(), x2 @ p["A_up"].t(),
+                                    p["B_gate"], p["B_up"], p["s_gate"], p["s_up"], save_eg=True)
+        check_status(x2.device)
+        close(e, t["e"], f"{key} e")
+        close(g, t["g"], f"{key} g")
+        close(h, t["h"], f"{key} h")
+        h0 = gate_up_swiglu_forward(x2, p["W_gate"], p["W_up"])
+        check_status(x2.device)
+        close(h0, t["h_noadapter"], f"{key} fused projection h")
+        seen += 1
+    assert seen == 2

@@ -173,3 +173,46 @@ def test_codecs_round_trip_and_round_to_nearest_even():
         out = torch.empty(x.numel(), dtype=torch.int16)
         L.swiglu_oracle_from_f32(code, x.numel(), x.data_ptr(), out.data_ptr())
         assert torch.equal(out, x.to(dtype).view(torch.int16)), dtype
+
+
+# ------------------------------------------------------------------------------------------ LoRA MLP
+
+LORA_NAMES = ["out", "e", "g", "h", "dX", "dA_gate", "dB_gate", "dA_up", "dB_up", "dA_down", "dB_down"]
+
+
+def load_lora_case(z, key, dtype):
+    names = {k.rsplit("|", 1)[1] for k in z.files if k.startswith(key + "|")}
+    t = {n: O.from_numpy_bits(z[f"{key}|{n}"], dtype) for n in names}
+    p = {k: v for k, v in t.items() if k[:2] in ("W_", "A_", "B_")}
+    p.update(s_gate=2.0, s_up=2.0, s_down=2.0)
+    return t, p
+
+
+def test_lora_mlp_oracle_matches_reference(golden_dir):
+    """The numpy restatement against outputs of the reference's own LoRAMLP / lora_swiglu_mlp / matmul_lora
+    (kernels/lora_mlp/reference/lora_mlp_pytorch.py) on the same inputs: fp32 vectors to 2e-5 of each
+    tensor's largest magnitude, bf16 vectors (every intermediate of the reference rounded to bf16) to 3 %."""
+    from oracle import lora_oracle as L
+
+    z = np.load(golden_dir / "lora_mlp.npz")
+    cases = _cases(z)
+    assert len(cases) == 4
+    for key in cases:
+        dname = key.split("|")[0]
+        dtype = DTYPES[dname]
+        t, p = load_lora_case(z, key, dtype)
+        np_p = {k: (v.double().numpy() if isinstance(v, torch.Tensor) else v) for k, v in p.items()}
+        r = L.lora_mlp_fwd_bwd(t["X"].double().numpy(), np_p, t["dY"].double().numpy())
+        bound = 2e-5 if dtype == torch.float32 else 3e-2
+        for n in LORA_NAMES:
+            ref = t[n].double().numpy().reshape(r[n].shape)
+            err = np.abs(r[n] - ref).max()
+            assert err <= bound * np.abs(ref).max(), f"{key} {n}: {err} vs max {np.abs(ref).max()}"
+        # the reference's functional forward and its autograd Function agree with each other
+        assert torch.equal(t["out"], t["out_functional"])
+        # without adapters
+        q = dict(np_p, A_gate=None, B_gate=None, A_up=None, B_up=None, A_down=None, B_down=None)
+        r0 = L.lora_mlp_fwd_bwd(t["X"].double().numpy(), q, t["dY"].double().numpy())
+        for n, m in (("h", "h_noadapter"), ("out", "out_noadapter")):
+            ref = t[m].double().numpy().reshape(r0[n].shape)
+            assert np.abs(r0[n] - ref).max() <= bound * np.abs(ref).max(), f"{key} {m}"
