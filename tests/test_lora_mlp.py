@@ -234,15 +234,17 @@ def test_mlp_matches_reference_vectors(golden_dir):
 
 def test_epilogue_and_fused_projection_match_reference_vectors(golden_dir):
     """bf16 vectors: the LoRA epilogue fed with cuBLAS base projections against the reference's e, g, h, and the
-    fused gate/up GEMM against its adapter-free h.  The reference rounds e and g to bf16 before the activation and
-    its CPU GEMMs accumulate differently, so the bound is the bf16 one: 2^-7 |ref| + 2^-7 rms(ref)."""
+    fused gate/up GEMM against its adapter-free h.  e and g carry one bf16 rounding on either side:
+    2^-7 |ref| + 2^-7 rms(ref).  The reference's h is computed from its ROUNDED e and g and rounded again (three
+    roundings, each up to 2^-9 relative, plus one here, and the roundings of e and g are relative to THEIR magnitude,
+    not to that of h), so h gets 2^-6 |ref| + 2^-6 rms(ref)."""
     from kernel_pocs_b200.fused_mlp import gate_up_swiglu_forward
     from kernel_pocs_b200.lora_mlp import fused_lora_swiglu
 
-    def close(got, ref, what):
+    def close(got, ref, what, rel=2.0 ** -7):
         ref = ref.float().reshape(got.shape)
         err = (got.float() - ref).abs()
-        tol = 2.0 ** -7 * ref.abs() + 2.0 ** -7 * ref.pow(2).mean().sqrt()
+        tol = rel * (ref.abs() + ref.pow(2).mean().sqrt())
         assert bool((err <= tol).all()), f"{what}: worst excess {(err - tol).max().item()}"
 
     seen = 0
@@ -255,9 +257,9 @@ def test_epilogue_and_fused_projection_match_reference_vectors(golden_dir):
         check_status(x2.device)
         close(e, t["e"], f"{key} e")
         close(g, t["g"], f"{key} g")
-        close(h, t["h"], f"{key} h")
+        close(h, t["h"], f"{key} h", rel=2.0 ** -6)
         h0 = gate_up_swiglu_forward(x2, p["W_gate"], p["W_up"])
         check_status(x2.device)
-        close(h0, t["h_noadapter"], f"{key} fused projection h")
+        close(h0, t["h_noadapter"], f"{key} fused projection h", rel=2.0 ** -6)
         seen += 1
     assert seen == 2
