@@ -17,9 +17,10 @@
 //   * Per tile the producer warp loads E, G (128 x 64) and Bg, Bu (64 rows) into a 3- or 4-stage ring.  One
 //     thread issues two M=128, N=64 MMAs per 16 ranks into TMEM (double buffered), which yield the adapter
 //     terms in the row-per-thread layout the epilogue reads.
-//   * Sixteen epilogue warps (four per TMEM lane quarter, 16 columns each) add the terms to E and G taken from the swizzled shared-memory tiles, apply
+//   * Sixteen epilogue warps, as two groups of eight that take alternate tiles (two warps per TMEM lane
+//     quarter, 32 columns each), add the terms to E and G taken from the swizzled shared-memory tiles, apply
 //     SwiGLU in fp32, write h (and e, g in place over the staged tiles) back to shared memory, and one
-//     thread stores the tiles with bulk tensor stores, which also clip at the matrix edge.
+//     thread per group stores the tiles with bulk tensor stores, which also clip at the matrix edge.
 // No load uses cluster multicast.  Every mbarrier wait is bounded; a wait that gives up records its code
 // in the status word, the other waits then leave, and the CTA drains its copies, frees TMEM and returns.
 #include "swiglu_b200.h"
@@ -46,26 +47,38 @@ constexpr int TN = 64;                          // output columns per tile (one 
 #endif
 constexpr int TILES_PER_RANGE = SWIGLU_LORA_TILES_PER_RANGE;  // 64-column tiles per work item
 constexpr int EG_BYTES = TM * TN * 2;           // 16 KiB
-constexpr int OUT_BUFS = 3;                     // h tiles waiting for their bulk store
+constexpr int OUT_BUFS_PER_GROUP = 2;           // h tiles of one epilogue group waiting for their bulk store
 constexpr int TMEM_COLS = 256;                  // 2 buffers x (64 gate + 64 up) fp32 columns
 #ifndef SWIGLU_LORA_EPI_WARPS
 #define SWIGLU_LORA_EPI_WARPS 16
 #endif
 constexpr int EPI_WARPS = SWIGLU_LORA_EPI_WARPS;  // EPI_WARPS / 4 warps share a TMEM lane quarter
-constexpr int CW = 64 / (EPI_WARPS / 4);         // columns of a tile handled by one warp
+#ifndef SWIGLU_LORA_GROUPS
+#define SWIGLU_LORA_GROUPS 2
+#endif
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
 // kind::f16, D fp32, A and B bf16 K-major, M = 128, N = 64
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
 
 // Shared-memory budget for a rank padded to RK (16, 32 or 64): the narrower the adapter tiles, the more
 // stages of E / G tiles fit, and bytes in flight are what this kernel's bandwidth comes from.
+//
+// GROUPS: the epilogue warps work as this many independent groups, each covering all four TMEM lane quarters
+// and taking every GROUPS-th tile, so that one group's waits, barrier and store issue overlap the other's
+// arithmetic, and a thread handles twice the columns per tile (half the per-tile bookkeeping per element).
 template <int RK>
 struct Cfg {
   static constexpr int XA_BYTES = TM * RK * 2;
   static constexpr int B_BYTES = TN * RK * 2;
   static constexpr int STAGE_BYTES = 2 * EG_BYTES + 2 * B_BYTES;
-  static constexpr int STAGES = RK == 64 ? 3 : 4;
+  static constexpr int GROUPS = RK == 64 ? 1 : SWIGLU_LORA_GROUPS;
+  static constexpr int STAGES = RK == 16 ? 4 : 3;
+  static constexpr int OUT_BUFS = GROUPS * OUT_BUFS_PER_GROUP;
+  static constexpr int GROUP_WARPS = EPI_WARPS / GROUPS;
+  static constexpr int CW = 64 / (GROUP_WARPS / 4);  // columns of a tile handled by one warp
   static constexpr int SMEM_BYTES = 2 * XA_BYTES + STAGES * STAGE_BYTES + OUT_BUFS * EG_BYTES + 1024 + 256;
+  static_assert(GROUPS == 1 || GROUPS == 2, "one or two epilogue groups");
+  static_assert(CW == 16 || CW == 32, "a warp reads 16 or 32 TMEM columns per accumulator");
   static_assert(SMEM_BYTES <= 227 * 1024, "exceeds the shared memory of an SM");
 };
 
@@ -81,11 +94,11 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int 
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y),
                "r"(smem_u32(smem_src)) : "memory");
 }
-// barrier over the epilogue threads that also ANDs a predicate across them
-__device__ __forceinline__ bool epilogue_all(bool ok) {
+// barrier `id` over the `threads` threads of one epilogue group that also ANDs a predicate across them
+__device__ __forceinline__ bool epilogue_all(bool ok, int id, int threads) {
   uint32_t all;
-  asm volatile("{ .reg .pred p, q; setp.ne.u32 q, %1, 0; bar.red.and.pred p, 1, %2, q; selp.u32 %0, 1, 0, p; }"
-               : "=r"(all) : "r"((uint32_t)ok), "n"(32 * EPI_WARPS) : "memory");
+  asm volatile("{ .reg .pred p, q; setp.ne.u32 q, %1, 0; bar.red.and.pred p, %2, %3, q; selp.u32 %0, 1, 0, p; }"
+               : "=r"(all) : "r"((uint32_t)ok), "r"(id), "r"(threads) : "memory");
   return all != 0;
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* b) {
@@ -112,7 +125,8 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int XA_BYTES = Cfg<RK>::XA_BYTES, B_BYTES = Cfg<RK>::B_BYTES, STAGE_BYTES = Cfg<RK>::STAGE_BYTES,
-                STAGES = Cfg<RK>::STAGES;
+                STAGES = Cfg<RK>::STAGES, GROUPS = Cfg<RK>::GROUPS, GROUP_WARPS = Cfg<RK>::GROUP_WARPS,
+                CW = Cfg<RK>::CW, OUT_BUFS = Cfg<RK>::OUT_BUFS;
   unsigned char* xa_g = smem;
   unsigned char* xa_u = smem + XA_BYTES;
   unsigned char* ring = smem + 2 * XA_BYTES;
@@ -120,7 +134,7 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
   uint64_t* full = reinterpret_cast<uint64_t*>(outs + OUT_BUFS * EG_BYTES);
   uint64_t* empty = full + STAGES;        // MMA commit + one epilogue thread
   uint64_t* acc_full = empty + STAGES;    // [2]
-  uint64_t* acc_empty = acc_full + 2;     // [2], every epilogue warp
+  uint64_t* acc_empty = acc_full + 2;     // [2], every warp of the group that reads the buffer
   uint64_t* xa_full = acc_empty + 2;
   uint64_t* xa_empty = xa_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xa_empty + 1);
@@ -139,7 +153,7 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], EPI_WARPS);
+      mbar_init(&acc_empty[b], GROUP_WARPS);  // with two groups, buffer b is read by group b only
     }
     mbar_init(xa_full, 1);
     mbar_init(xa_empty, 1);
@@ -225,25 +239,29 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
     }
   } else {
     const int quarter = warp & 3;                   // TMEM lane quarter this warp may read
-    const int part = (warp - 2) >> 2;               // which CW of the tile's 64 columns it handles
+    const int slot = (warp - 2) >> 2;               // 0 .. EPI_WARPS/4 - 1
+    const int group = slot % GROUPS;                // epilogue group: takes the tiles with it % GROUPS == group
+    const int part = slot / GROUPS;                 // which CW of the tile's 64 columns this warp handles
     const int row = quarter * 32 + lane;            // row of the tile owned by this thread
-    const bool elected = (warp == 2 && lane == 0);
+    const bool elected = (part == 0 && quarter == ((2 + 4 * group) & 3) && lane == 0);  // one thread per group
     const Consts one(1.0f, 1.0f);
     long long it = 0;
+    int mine = 0;                                   // tiles this group has handled
     bool ok = true;
     for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
       const int m0 = (int)(item / ranges_n) * TM;
       const long long t_lo = (item % ranges_n) * TILES_PER_RANGE;
       const long long t_hi = (t_lo + TILES_PER_RANGE) < tiles_n ? (t_lo + TILES_PER_RANGE) : tiles_n;
       for (long long t = t_lo; t < t_hi; ++t, ++it) {
+        if (GROUPS > 1 && (int)(it % GROUPS) != group) continue;
         const int s = (int)(it % STAGES);
         const int b = (int)(it & 1);
         unsigned char* e_tile = ring + s * STAGE_BYTES;
         unsigned char* g_tile = e_tile + EG_BYTES;
-        // Three h buffers: the store of tile i-2 is known to be complete once the barrier at the end of
-        // tile i has been passed (the storing thread waits for it before arriving there), so tile i+1 may
-        // overwrite that buffer without a second barrier.
-        unsigned char* h_tile = outs + (it % OUT_BUFS) * EG_BYTES;
+        // Two h buffers per group: before the group's barrier of this tile its storing thread has waited for
+        // the store of the previous tile to finish reading, so the next tile may overwrite that buffer.
+        unsigned char* h_tile = outs + (group * OUT_BUFS_PER_GROUP + (mine & 1)) * EG_BYTES;
+        ++mine;
         ok = mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1), p.status, 600 + s) &&
              mbar_wait(&acc_full[b], (uint32_t)((it >> 1) & 1), p.status, 300 + b);
         if (!__all_sync(0xffffffffu, ok)) ok = false;  // warp-uniform, for the warp-wide TMEM loads
@@ -255,7 +273,6 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
           tmem_ld32(t_row, lg);
           tmem_ld32(t_row + 64, lu);
         } else {
-          static_assert(CW == 16 || CW == 32, "8 or 16 epilogue warps");
           tmem_ld16(t_row, lg);
           tmem_ld16(t_row + 64, lu);
         }
@@ -294,11 +311,13 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
           }
         }
         }
-        // The shared-memory tiles are complete: make them visible to the bulk stores.  All epilogue threads
-        // meet here once per tile and agree on the outcome of their waits, so that none is left at a later
-        // barrier waiting for a thread whose wait gave up.
+        // The shared-memory tiles are complete: make them visible to the bulk stores.  The threads of the
+        // group meet here once per tile and agree on the outcome of their waits, so that none is left at a
+        // later barrier waiting for a thread whose wait gave up.
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        ok = epilogue_all(ok);
+        // the group's previous store has finished reading its h buffer, which the next tile overwrites
+        if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        ok = epilogue_all(ok, 1 + group, 32 * GROUP_WARPS);
         if (!ok) break;
         if (elected) {
           const int n0 = (int)(t * TN);
@@ -311,8 +330,6 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
           // the stage may be refilled once nothing reads it any more
           if constexpr (SAVE) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           mbar_arrive(&empty[s]);
-          // at most this tile's store stays pending: the previous one has released its h buffer
-          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
         }
       }
     }
