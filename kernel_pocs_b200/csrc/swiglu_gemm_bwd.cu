@@ -8,16 +8,16 @@
 // down_proj(swiglu(gate_proj(x), up_proj(x))) (forge/forge/patching/kernels/basic.py:97-102).
 //
 // Both products run on the CTA-pair scheme of the forward kernel (cluster of 2, cta_group::2 MMA with
-// M = 256, N = 256, K = 16, persistent over tiles, 6-stage ring, two accumulator buffers in TMEM), with
-// one new ingredient: operands whose contiguous dimension is NOT the contraction dimension.  Wg/Wu in dX
+// M = 256, N = 256, K = 16, persistent over tiles, a ring of operand stages, accumulators in TMEM; pair
+// tiles of 256 or 512 output columns, see Tile below), with one new ingredient: operands whose contiguous dimension is NOT the contraction dimension.  Wg/Wu in dX
 // (contraction over n, contiguous along k) and all three operands of dW (contraction over m) are such
 // "MN-major" operands; they are loaded as 64-element x 64-row boxes and described to the MMA with the
 // MN-major shared-memory descriptor, so no transposed copy of any matrix is ever made.
 //
-//   dX : pair tile 256 (m) x 256 (k).  A = dgate rows then dup rows (K-major, 128 rows per CTA),
+//   dX : pair tile 256 (m) x 256 or 512 (k).  A = dgate rows then dup rows (K-major, 128 rows per CTA),
 //        B = Wg then Wu (MN-major, each CTA loads 128 of the 256 output columns); the contraction runs
 //        over n for the gate pair and then over n again for the up pair into the same accumulator.
-//   dW : pair tile {dWg, dWu} x 128 (n) x 256 (k).  CTA 0 of the pair accumulates dWg, CTA 1 dWu: the
+//   dW : pair tile {dWg, dWu} x 128 (n) x 256 or 512 (k).  CTA 0 of the pair accumulates dWg, CTA 1 dWu: the
 //        "M = 256" of the MMA is 128 columns of dgate stacked on the same 128 columns of dup (both
 //        MN-major), B = X (MN-major, each CTA loads 128 of the 256 output columns); contraction over m.
 // Every mbarrier wait is bounded; a wait that gives up records its code in the status word.
@@ -28,8 +28,14 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdlib>
+#include <cstring>
 
 #include "tcgen05_common.cuh"
+
+#ifndef SWIGLU_GEMM_BWD_WIDE_COST
+#define SWIGLU_GEMM_BWD_WIDE_COST 0.91
+#endif
 
 namespace {
 
@@ -37,16 +43,27 @@ using namespace swiglu_b200::tc;
 
 constexpr int BK = 64;                        // contraction elements per stage
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 6;
 constexpr int A_BYTES = 128 * BK * 2;         // 16 KiB: 128 rows (or columns) x 64 contraction elements
 constexpr int B_BYTES = 128 * BK * 2;         // 16 KiB: 64 contraction rows x 128 output columns
 constexpr int CHUNK_BYTES = 64 * BK * 2;      // 8 KiB: one 64-column chunk of an MN-major tile
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int ACC_BUFS = 2;
-constexpr int TMEM_COLS = 512;                // two accumulators of 256 fp32 columns
-constexpr int TILE_N = 256;                   // output columns per tile
+constexpr int TMEM_COLS = 512;                // all of it: two accumulators of 256 fp32 columns, or one of 512
 constexpr int THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+
+// NT = output columns of a pair tile.  256: one MMA of N = 256 per 16 contraction elements, two accumulator
+// buffers, so a tile's epilogue overlaps the next tile's MMAs.  512: two such MMAs share the A operand, which
+// cuts the operand bytes per flop by a quarter (A 16 KiB + B 32 KiB per CTA and K block instead of 2 x
+// (16 + 16)); the single 512-column accumulator leaves the epilogue exposed, a percent or two of a tile.
+template <int NT>
+struct Tile {
+  static_assert(NT == 256 || NT == 512, "one or two N = 256 MMAs per step");
+  static constexpr int HALVES = NT / 256;
+  static constexpr int STAGE_BYTES = A_BYTES + HALVES * B_BYTES;
+  static constexpr int STAGES = NT == 256 ? 6 : 4;
+  static constexpr int ACC_BUFS = 512 / NT;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static_assert(SMEM_BYTES <= 227 * 1024, "exceeds the shared memory of an SM");
+};
+constexpr int MAX_STAGES = 6;
 
 enum Mode : int { MODE_DX = 0, MODE_DW = 1 };
 
@@ -66,8 +83,8 @@ struct BwdParams {
 // Tiles in bands of 8 row-tiles so that the operands in flight stay in L2.
 struct Walk {
   long long tiles_r, tiles_c, total;
-  __device__ __forceinline__ Walk(long long rows, long long row_tile, long long cols)
-      : tiles_r((rows + row_tile - 1) / row_tile), tiles_c((cols + TILE_N - 1) / TILE_N), total(tiles_r * tiles_c) {}
+  __device__ __forceinline__ Walk(long long rows, long long row_tile, long long cols, long long col_tile)
+      : tiles_r((rows + row_tile - 1) / row_tile), tiles_c((cols + col_tile - 1) / col_tile), total(tiles_r * tiles_c) {}
   __device__ __forceinline__ void at(long long t, long long& tr, long long& tc) const {
     const long long per_band = 8 * tiles_c;
     const long long band = t / per_band;
@@ -80,18 +97,20 @@ struct Walk {
 
 // MODE_DX: maps = {dgate (K-major boxes of 128 rows), dup (same), Wg (MN boxes), Wu (MN boxes)}
 // MODE_DW: maps = {dgate (MN boxes), dup (MN boxes), X (MN boxes), unused}
-template <int MODE>
+template <int MODE, int NT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                        const __grid_constant__ CUtensorMap map2, const __grid_constant__ CUtensorMap map3,
                        const BwdParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int STAGES = Tile<NT>::STAGES, STAGE_BYTES = Tile<NT>::STAGE_BYTES, ACC_BUFS = Tile<NT>::ACC_BUFS,
+                HALVES = Tile<NT>::HALVES;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);  // used in the leader only
-  uint64_t* empty = full + STAGES;
-  uint64_t* acc_full = empty + STAGES;
-  uint64_t* acc_empty = acc_full + ACC_BUFS;                                  // used in the leader only
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
+  uint64_t* empty = full + MAX_STAGES;
+  uint64_t* acc_full = empty + MAX_STAGES;
+  uint64_t* acc_empty = acc_full + 2;                                         // used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -101,7 +120,7 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
 
   // output rows per pair tile: 256 rows of dX, or 128 rows of each of dWg and dWu
   const long long out_rows = MODE == MODE_DX ? p.m : p.n;
-  const Walk walk(out_rows, MODE == MODE_DX ? 256 : 128, p.k);
+  const Walk walk(out_rows, MODE == MODE_DX ? 256 : 128, p.k, NT);
   // K blocks of one tile: dX contracts over n twice (gate pair, then up pair), dW over m once
   const int blocks_per_pass = (int)(((MODE == MODE_DX ? p.n : p.m) + BK - 1) / BK);
   const int k_blocks = MODE == MODE_DX ? 2 * blocks_per_pass : blocks_per_pass;
@@ -136,7 +155,7 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
       for (long long t = pair_id; t < walk.total && ok; t += n_pairs) {
         long long tr, tc;
         walk.at(t, tr, tc);
-        const int col0 = (int)(tc * TILE_N) + (int)rank * 128;  // this CTA's 128 output columns of B
+        const int col0 = (int)(tc * NT) + (int)rank * 128;  // this CTA's 128 output columns of B (first MMA)
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = (int)(it % STAGES);
           if (it >= STAGES) {
@@ -152,10 +171,13 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
             const int c0 = (up_pass ? kb - blocks_per_pass : kb) * BK;  // contraction offset (n)
             // A: 128 rows of dgate / dup, 64 n; one K-major box
             tma_load_2d_pair(a_dst, up_pass ? &map1 : &map0, c0, (int)(tr * 256) + (int)rank * 128, leader_full);
-            // B: 64 n-rows x 128 k-columns of Wg / Wu; two MN-major boxes
+            // B: 64 n-rows x 128 k-columns of Wg / Wu per MMA; two MN-major boxes each
             const CUtensorMap* w = up_pass ? &map3 : &map2;
-            tma_load_2d_pair(b_dst, w, col0, c0, leader_full);
-            tma_load_2d_pair(b_dst + CHUNK_BYTES, w, col0 + 64, c0, leader_full);
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) {
+              tma_load_2d_pair(b_dst + h * B_BYTES, w, col0 + h * 256, c0, leader_full);
+              tma_load_2d_pair(b_dst + h * B_BYTES + CHUNK_BYTES, w, col0 + h * 256 + 64, c0, leader_full);
+            }
           } else {
             const int c0 = kb * BK;  // contraction offset (m)
             // A: 64 m-rows x 128 n-columns of dgate (CTA 0) or dup (CTA 1); two MN-major boxes
@@ -163,9 +185,12 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
             const int n0 = (int)(tr * 128);
             tma_load_2d_pair(a_dst, g, n0, c0, leader_full);
             tma_load_2d_pair(a_dst + CHUNK_BYTES, g, n0 + 64, c0, leader_full);
-            // B: 64 m-rows x 128 k-columns of X; two MN-major boxes
-            tma_load_2d_pair(b_dst, &map2, col0, c0, leader_full);
-            tma_load_2d_pair(b_dst + CHUNK_BYTES, &map2, col0 + 64, c0, leader_full);
+            // B: 64 m-rows x 128 k-columns of X per MMA; two MN-major boxes each
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) {
+              tma_load_2d_pair(b_dst + h * B_BYTES, &map2, col0 + h * 256, c0, leader_full);
+              tma_load_2d_pair(b_dst + h * B_BYTES + CHUNK_BYTES, &map2, col0 + h * 256 + 64, c0, leader_full);
+            }
           }
         }
       }
@@ -176,30 +201,28 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
       long long it = 0, i = 0;
       bool ok = true;
       for (long long t = pair_id; t < walk.total && ok; t += n_pairs, ++i) {
-        const int b = (int)(i & 1);
+        const int b = (int)(i % ACC_BUFS);
         if (i >= ACC_BUFS) {
-          ok = wait<true>(&acc_empty[b], (uint32_t)(((i >> 1) - 1) & 1), p.status, 400 + b);
+          ok = wait<true>(&acc_empty[b], (uint32_t)((i / ACC_BUFS - 1) & 1), p.status, 400 + b);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
-        const uint32_t tmem_d = tmem_base + (uint32_t)b * 256u;
+        const uint32_t tmem_d = tmem_base + (uint32_t)b * 256u;  // NT = 512: b is 0, the halves at +0 and +256
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = (int)(it % STAGES);
           ok = wait<false>(&full[s], (uint32_t)((it / STAGES) & 1), p.status, 200 + s);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-          const uint64_t b_desc = umma_desc_mn(a_addr + A_BYTES, CHUNK_BYTES);
-          if (MODE == MODE_DX) {
-            const uint64_t a_desc = umma_desc(a_addr);
+          const uint64_t a_desc = MODE == MODE_DX ? umma_desc(a_addr) : umma_desc_mn(a_addr, CHUNK_BYTES);
+          constexpr int A_STEP = MODE == MODE_DX ? 2 : 128;  // descriptor advance per 16 contraction elements
 #pragma unroll
-            for (int kk = 0; kk < BK / UMMA_K; ++kk)
-              umma_pair(tmem_d, a_desc + 2 * kk, b_desc + 128 * kk, kIdesc, (kb | kk) != 0);
-          } else {
-            const uint64_t a_desc = umma_desc_mn(a_addr, CHUNK_BYTES);
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
 #pragma unroll
-            for (int kk = 0; kk < BK / UMMA_K; ++kk)
-              umma_pair(tmem_d, a_desc + 128 * kk, b_desc + 128 * kk, kIdesc, (kb | kk) != 0);
+            for (int h = 0; h < HALVES; ++h) {
+              const uint64_t b_desc = umma_desc_mn(a_addr + A_BYTES + h * B_BYTES, CHUNK_BYTES);
+              umma_pair(tmem_d + (uint32_t)h * 256u, a_desc + A_STEP * kk, b_desc + 128 * kk, kIdesc, (kb | kk) != 0);
+            }
           }
           commit_both(&empty[s]);
         }
@@ -213,18 +236,18 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
     for (long long t = pair_id; t < walk.total && ok; t += n_pairs, ++i) {
       long long tr, tc;
       walk.at(t, tr, tc);
-      const int b = (int)(i & 1);
-      ok = wait<false>(&acc_full[b], (uint32_t)((i >> 1) & 1), p.status, 300 + b);
+      const int b = (int)(i % ACC_BUFS);
+      ok = wait<false>(&acc_full[b], (uint32_t)((i / ACC_BUFS) & 1), p.status, 300 + b);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // dX: CTA r owns rows tr*256 + r*128 ..; dW: CTA 0 writes dWg rows tr*128 .., CTA 1 the same rows of dWu
       const long long row = MODE == MODE_DX ? tr * 256 + (long long)rank * 128 + quarter * 32 + lane
                                             : tr * 128 + quarter * 32 + lane;
       __nv_bfloat16* out = (MODE == MODE_DW && rank == 1) ? p.out1 : p.out0;
-      const int col_base = (int)(tc * TILE_N);
+      const int col_base = (int)(tc * NT);
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)b * 256u;
 #pragma unroll 1
-      for (int c = 0; c < TILE_N; c += 16) {
+      for (int c = 0; c < NT; c += 16) {
         uint32_t v[16];
         tmem_ld16(t_row + c, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -263,8 +286,9 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
 
 std::atomic<uint64_t> g_bwd_launches{0};
 
-template <int MODE>
+template <int MODE, int NT>
 int resident_clusters(int dev, int* out) {
+  constexpr int SMEM_BYTES = Tile<NT>::SMEM_BYTES;
   static std::atomic<int> cache[64];
   if (dev < 64) {
     const int c = cache[dev].load(std::memory_order_acquire);
@@ -273,7 +297,7 @@ int resident_clusters(int dev, int* out) {
       return SWIGLU_B200_OK;
     }
   }
-  auto kernel = swiglu_gemm_bwd_kernel<MODE>;
+  auto kernel = swiglu_gemm_bwd_kernel<MODE, NT>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
     return SWIGLU_B200_ERR_DEVICE;
   cudaLaunchConfig_t cfg = {};
@@ -292,6 +316,44 @@ int resident_clusters(int dev, int* out) {
   if (dev < 64) cache[dev].store(n, std::memory_order_release);
   *out = n;
   return SWIGLU_B200_OK;
+}
+
+
+template <int MODE, int NT>
+int launch_tile(int dev, long long row_tiles, long long k, const CUtensorMap& m0, const CUtensorMap& m1,
+                const CUtensorMap& m2, const CUtensorMap& m3, const BwdParams& p, cudaStream_t st) {
+  int clusters = 0;
+  int rc = resident_clusters<MODE, NT>(dev, &clusters);
+  if (rc != SWIGLU_B200_OK) return rc;
+  const long long tiles = row_tiles * ((k + NT - 1) / NT);
+  const long long use = tiles < clusters ? tiles : clusters;
+  swiglu_gemm_bwd_kernel<MODE, NT><<<(unsigned)(2 * use), THREADS, Tile<NT>::SMEM_BYTES, st>>>(m0, m1, m2, m3, p);
+  if (cudaGetLastError() != cudaSuccess) return SWIGLU_B200_ERR_LAUNCH;
+  g_bwd_launches.fetch_add(1, std::memory_order_relaxed);
+  return SWIGLU_B200_OK;
+}
+
+// Tile width: 512 columns where its waves over the resident pairs cost less than those of 256 columns.  A
+// 512-column tile does the work of two 256-column tiles in kWide512Cost of their time (measured: fewer
+// operand bytes per flop).  SWIGLU_B200_GEMM_BWD_TILE=256|512 in the environment forces one, for experiments.
+constexpr double kWide512Cost = SWIGLU_GEMM_BWD_WIDE_COST;
+
+template <int MODE>
+int launch_mode(int dev, long long row_tiles, long long k, const CUtensorMap& m0, const CUtensorMap& m1,
+                const CUtensorMap& m2, const CUtensorMap& m3, const BwdParams& p, cudaStream_t st) {
+  int clusters = 0;
+  int rc = resident_clusters<MODE, 256>(dev, &clusters);
+  if (rc != SWIGLU_B200_OK) return rc;
+  const long long t256 = row_tiles * ((k + 255) / 256), t512 = row_tiles * ((k + 511) / 512);
+  const double cost256 = (double)((t256 + clusters - 1) / clusters);
+  const double cost512 = (double)((t512 + clusters - 1) / clusters) * 2.0 * kWide512Cost;
+  bool wide = cost512 < cost256;
+  if (const char* force = std::getenv("SWIGLU_B200_GEMM_BWD_TILE")) {
+    if (std::strcmp(force, "256") == 0) wide = false;
+    if (std::strcmp(force, "512") == 0) wide = true;
+  }
+  return wide ? launch_tile<MODE, 512>(dev, row_tiles, k, m0, m1, m2, m3, p, st)
+              : launch_tile<MODE, 256>(dev, row_tiles, k, m0, m1, m2, m3, p, st);
 }
 
 }  // namespace
@@ -344,31 +406,19 @@ int swiglu_b200_gemm_bwd(void* dx, void* dw_gate, void* dw_up, const void* dgate
     if (!make_map(&mg, dgate, m, n, 128) || !make_map(&mu, dup, m, n, 128) || !make_map(&mwg, w_gate, n, k, 64) ||
         !make_map(&mwu, w_up, n, k, 64))
       return SWIGLU_B200_ERR_DEVICE;
-    int clusters = 0;
-    int rc = resident_clusters<MODE_DX>(dev, &clusters);
-    if (rc != SWIGLU_B200_OK) return rc;
-    const long long tiles = ((m + 255) / 256) * ((k + TILE_N - 1) / TILE_N);
-    const long long use = tiles < clusters ? tiles : clusters;
     BwdParams p{static_cast<__nv_bfloat16*>(dx), nullptr, static_cast<int*>(status), m, n, k};
-    swiglu_gemm_bwd_kernel<MODE_DX><<<(unsigned)(2 * use), THREADS, SMEM_BYTES, st>>>(mg, mu, mwg, mwu, p);
-    if (cudaGetLastError() != cudaSuccess) return SWIGLU_B200_ERR_LAUNCH;
-    g_bwd_launches.fetch_add(1, std::memory_order_relaxed);
+    int rc = launch_mode<MODE_DX>(dev, (m + 255) / 256, k, mg, mu, mwg, mwu, p, st);
+    if (rc != SWIGLU_B200_OK) return rc;
   }
   if (dw_gate) {
     CUtensorMap mg, mu, mx;
     // all three as boxes of 64 m-rows x 64 contiguous elements
     if (!make_map(&mg, dgate, m, n, 64) || !make_map(&mu, dup, m, n, 64) || !make_map(&mx, x, m, k, 64))
       return SWIGLU_B200_ERR_DEVICE;
-    int clusters = 0;
-    int rc = resident_clusters<MODE_DW>(dev, &clusters);
-    if (rc != SWIGLU_B200_OK) return rc;
-    const long long tiles = ((n + 127) / 128) * ((k + TILE_N - 1) / TILE_N);
-    const long long use = tiles < clusters ? tiles : clusters;
     BwdParams p{static_cast<__nv_bfloat16*>(dw_gate), static_cast<__nv_bfloat16*>(dw_up), static_cast<int*>(status),
                 m, n, k};
-    swiglu_gemm_bwd_kernel<MODE_DW><<<(unsigned)(2 * use), THREADS, SMEM_BYTES, st>>>(mg, mu, mx, mx, p);
-    if (cudaGetLastError() != cudaSuccess) return SWIGLU_B200_ERR_LAUNCH;
-    g_bwd_launches.fetch_add(1, std::memory_order_relaxed);
+    int rc = launch_mode<MODE_DW>(dev, (n + 127) / 128, k, mg, mu, mx, mx, p, st);
+    if (rc != SWIGLU_B200_OK) return rc;
   }
   return SWIGLU_B200_OK;
 }

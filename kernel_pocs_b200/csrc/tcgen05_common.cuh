@@ -186,8 +186,8 @@ inline EncodeTiled encode_fn() {
 // [rows, k] bf16 row-major matrix, boxes of `box_rows` rows x 64 elements (128 bytes) along the contiguous
 // dimension (`box_cols` = 16 or 32 for narrower boxes), swizzle of the box's row length, zero fill outside
 // the matrix.
-inline bool make_map(CUtensorMap* map, const void* base, long long rows, long long k, int box_rows = 128,
-                     int box_cols = 64) {
+inline bool make_map_uncached(CUtensorMap* map, const void* base, long long rows, long long k, int box_rows,
+                              int box_cols) {
   EncodeTiled enc = encode_fn();
   if (!enc) return false;
   cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
@@ -201,6 +201,40 @@ inline bool make_map(CUtensorMap* map, const void* base, long long rows, long lo
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// A descriptor depends on nothing but these arguments, and encoding one costs about a microsecond of host
+// time, nine times per LoRA launch; training loops present the same buffers again and again (a caching
+// allocator hands the same addresses back), so each host thread keeps the last descriptors it built.
+inline bool make_map(CUtensorMap* map, const void* base, long long rows, long long k, int box_rows = 128,
+                     int box_cols = 64) {
+  struct Entry {
+    CUtensorMap map;
+    const void* base;
+    long long rows, k;
+    int box_rows, box_cols;
+    bool valid;
+  };
+  constexpr int kEntries = 64;
+  thread_local Entry cache[kEntries] = {};
+  const unsigned long long a = (unsigned long long)(uintptr_t)base;
+  const unsigned long long hsh = (a >> 9) ^ (a >> 21) ^ ((unsigned long long)rows * 0x9e3779b97f4a7c15ull) ^
+                                 ((unsigned long long)k << 7) ^ (unsigned long long)(box_rows * 31 + box_cols);
+  Entry& slot = cache[hsh % kEntries];
+  if (slot.valid && slot.base == base && slot.rows == rows && slot.k == k && slot.box_rows == box_rows &&
+      slot.box_cols == box_cols) {
+    *map = slot.map;
+    return true;
+  }
+  if (!make_map_uncached(map, base, rows, k, box_rows, box_cols)) return false;
+  slot.map = *map;
+  slot.base = base;
+  slot.rows = rows;
+  slot.k = k;
+  slot.box_rows = box_rows;
+  slot.box_cols = box_cols;
+  slot.valid = true;
+  return true;
 }
 
 }  // namespace tc

@@ -140,12 +140,19 @@ def test_single_cta_kernel_variant_agrees():
     assert torch.equal(outs[0], outs[1])
 
 
+@pytest.mark.parametrize("tile", ["auto", "256", "512"])
 @pytest.mark.parametrize("m,n,k", [(256, 128, 256), (512, 256, 512), (300, 136, 80), (1000, 2064, 1040),
-                                   (4096, 1408, 1024)])
-def test_backward_gemms_match_fp32_reference(m, n, k):
+                                   (4096, 1408, 1024), (8192, 1024, 2048)])
+def test_backward_gemms_match_fp32_reference(m, n, k, tile, monkeypatch):
     """dx, dw_gate, dw_up from the tcgen05 backward kernels (operands whose contiguous dimension is not the
     contraction dimension, i.e. MN-major shared-memory descriptors) against fp32 matmuls of the same bf16
-    operands; one bf16 rounding plus accumulation noise relative to the spread of the result."""
+    operands; one bf16 rounding plus accumulation noise relative to the spread of the result.  Both tile
+    widths (256 columns with two accumulators, 512 columns with one) are forced in turn, besides the
+    library's own choice."""
+    if tile == "auto":
+        monkeypatch.delenv("SWIGLU_B200_GEMM_BWD_TILE", raising=False)
+    else:
+        monkeypatch.setenv("SWIGLU_B200_GEMM_BWD_TILE", tile)
     g = torch.Generator(device=DEVICE).manual_seed(5)
     x = torch.randn(m, k, generator=g, device=DEVICE).bfloat16()
     wg = (0.05 * torch.randn(n, k, generator=g, device=DEVICE)).bfloat16()
