@@ -81,17 +81,39 @@ struct BwdParams {
 };
 
 // Tiles in bands of 8 row-tiles so that the operands in flight stay in L2.
+//
+// Tail split (512-column tiles only): when the tiles left over after the last full wave of the resident pairs
+// number at most half the pairs, each of them is handed out as two 256-column halves, so that the last wave
+// costs one narrow tile instead of one wide tile on a few pairs while the others idle.  `split_from` is the
+// index of the first such tile (= the number of wide tiles), `total` counts work items.
 struct Walk {
-  long long tiles_r, tiles_c, total;
-  __device__ __forceinline__ Walk(long long rows, long long row_tile, long long cols, long long col_tile)
-      : tiles_r((rows + row_tile - 1) / row_tile), tiles_c((cols + col_tile - 1) / col_tile), total(tiles_r * tiles_c) {}
-  __device__ __forceinline__ void at(long long t, long long& tr, long long& tc) const {
+  long long tiles_r, tiles_c, total, split_from;
+  int col_tile;
+  __device__ __forceinline__ Walk(long long rows, long long row_tile, long long cols, int col_tile_, long long pairs)
+      : tiles_r((rows + row_tile - 1) / row_tile), tiles_c((cols + col_tile_ - 1) / col_tile_), col_tile(col_tile_) {
+    const long long tiles = tiles_r * tiles_c;
+    const long long rest = tiles % pairs;
+    const bool split = col_tile_ == 512 && rest > 0 && 2 * rest <= pairs && tiles > pairs;
+    split_from = split ? tiles - rest : tiles;
+    total = split ? tiles + rest : tiles;
+  }
+  // item t -> row tile, first output column, number of 256-column MMAs
+  __device__ __forceinline__ void at(long long t, long long& tr, int& col, int& halves) const {
+    long long tile = t;
+    int half = 0;
+    halves = col_tile / 256;
+    if (t >= split_from) {
+      tile = split_from + ((t - split_from) >> 1);
+      half = (int)((t - split_from) & 1);
+      halves = 1;
+    }
     const long long per_band = 8 * tiles_c;
-    const long long band = t / per_band;
-    const long long r = t - band * per_band;
+    const long long band = tile / per_band;
+    const long long r = tile - band * per_band;
     const long long in_band = (tiles_r - band * 8) < 8 ? (tiles_r - band * 8) : 8;
-    tc = r / in_band;
+    const long long tc = r / in_band;
     tr = band * 8 + (r - tc * in_band);
+    col = (int)(tc * col_tile) + half * 256;
   }
 };
 
@@ -120,7 +142,7 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
 
   // output rows per pair tile: 256 rows of dX, or 128 rows of each of dWg and dWu
   const long long out_rows = MODE == MODE_DX ? p.m : p.n;
-  const Walk walk(out_rows, MODE == MODE_DX ? 256 : 128, p.k, NT);
+  const Walk walk(out_rows, MODE == MODE_DX ? 256 : 128, p.k, NT, n_pairs);
   // K blocks of one tile: dX contracts over n twice (gate pair, then up pair), dW over m once
   const int blocks_per_pass = (int)(((MODE == MODE_DX ? p.n : p.m) + BK - 1) / BK);
   const int k_blocks = MODE == MODE_DX ? 2 * blocks_per_pass : blocks_per_pass;
@@ -153,9 +175,10 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
       long long it = 0;
       bool ok = true;
       for (long long t = pair_id; t < walk.total && ok; t += n_pairs) {
-        long long tr, tc;
-        walk.at(t, tr, tc);
-        const int col0 = (int)(tc * NT) + (int)rank * 128;  // this CTA's 128 output columns of B (first MMA)
+        long long tr;
+        int col, halves;
+        walk.at(t, tr, col, halves);
+        const int col0 = col + (int)rank * 128;  // this CTA's 128 output columns of B (first MMA)
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = (int)(it % STAGES);
           if (it >= STAGES) {
@@ -163,7 +186,7 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
             if (!ok) break;
           }
           const uint32_t leader_full = map_to_rank(smem_u32(&full[s]), 0);
-          remote_expect_tx(leader_full, STAGE_BYTES);
+          remote_expect_tx(leader_full, (uint32_t)(A_BYTES + halves * B_BYTES));
           unsigned char* a_dst = smem + s * STAGE_BYTES;
           unsigned char* b_dst = a_dst + A_BYTES;
           if (MODE == MODE_DX) {
@@ -175,8 +198,10 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
             const CUtensorMap* w = up_pass ? &map3 : &map2;
 #pragma unroll
             for (int h = 0; h < HALVES; ++h) {
-              tma_load_2d_pair(b_dst + h * B_BYTES, w, col0 + h * 256, c0, leader_full);
-              tma_load_2d_pair(b_dst + h * B_BYTES + CHUNK_BYTES, w, col0 + h * 256 + 64, c0, leader_full);
+              if (h < halves) {
+                tma_load_2d_pair(b_dst + h * B_BYTES, w, col0 + h * 256, c0, leader_full);
+                tma_load_2d_pair(b_dst + h * B_BYTES + CHUNK_BYTES, w, col0 + h * 256 + 64, c0, leader_full);
+              }
             }
           } else {
             const int c0 = kb * BK;  // contraction offset (m)
@@ -188,8 +213,10 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
             // B: 64 m-rows x 128 k-columns of X per MMA; two MN-major boxes each
 #pragma unroll
             for (int h = 0; h < HALVES; ++h) {
-              tma_load_2d_pair(b_dst + h * B_BYTES, &map2, col0 + h * 256, c0, leader_full);
-              tma_load_2d_pair(b_dst + h * B_BYTES + CHUNK_BYTES, &map2, col0 + h * 256 + 64, c0, leader_full);
+              if (h < halves) {
+                tma_load_2d_pair(b_dst + h * B_BYTES, &map2, col0 + h * 256, c0, leader_full);
+                tma_load_2d_pair(b_dst + h * B_BYTES + CHUNK_BYTES, &map2, col0 + h * 256 + 64, c0, leader_full);
+              }
             }
           }
         }
@@ -201,6 +228,9 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
       long long it = 0, i = 0;
       bool ok = true;
       for (long long t = pair_id; t < walk.total && ok; t += n_pairs, ++i) {
+        long long tr_unused;
+        int col_unused, halves;
+        walk.at(t, tr_unused, col_unused, halves);
         const int b = (int)(i % ACC_BUFS);
         if (i >= ACC_BUFS) {
           ok = wait<true>(&acc_empty[b], (uint32_t)((i / ACC_BUFS - 1) & 1), p.status, 400 + b);
@@ -220,8 +250,11 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
 #pragma unroll
             for (int h = 0; h < HALVES; ++h) {
-              const uint64_t b_desc = umma_desc_mn(a_addr + A_BYTES + h * B_BYTES, CHUNK_BYTES);
-              umma_pair(tmem_d + (uint32_t)h * 256u, a_desc + A_STEP * kk, b_desc + 128 * kk, kIdesc, (kb | kk) != 0);
+              if (h < halves) {
+                const uint64_t b_desc = umma_desc_mn(a_addr + A_BYTES + h * B_BYTES, CHUNK_BYTES);
+                umma_pair(tmem_d + (uint32_t)h * 256u, a_desc + A_STEP * kk, b_desc + 128 * kk, kIdesc,
+                          (kb | kk) != 0);
+              }
             }
           }
           commit_both(&empty[s]);
@@ -234,8 +267,9 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
     long long i = 0;
     bool ok = true;
     for (long long t = pair_id; t < walk.total && ok; t += n_pairs, ++i) {
-      long long tr, tc;
-      walk.at(t, tr, tc);
+      long long tr;
+      int col_base, halves;
+      walk.at(t, tr, col_base, halves);
       const int b = (int)(i % ACC_BUFS);
       ok = wait<false>(&acc_full[b], (uint32_t)((i / ACC_BUFS) & 1), p.status, 300 + b);
       if (!ok) break;
@@ -244,10 +278,9 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
       const long long row = MODE == MODE_DX ? tr * 256 + (long long)rank * 128 + quarter * 32 + lane
                                             : tr * 128 + quarter * 32 + lane;
       __nv_bfloat16* out = (MODE == MODE_DW && rank == 1) ? p.out1 : p.out0;
-      const int col_base = (int)(tc * NT);
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)b * 256u;
 #pragma unroll 1
-      for (int c = 0; c < NT; c += 16) {
+      for (int c = 0; c < halves * 256; c += 16) {
         uint32_t v[16];
         tmem_ld16(t_row + c, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -346,7 +379,10 @@ int launch_mode(int dev, long long row_tiles, long long k, const CUtensorMap& m0
   if (rc != SWIGLU_B200_OK) return rc;
   const long long t256 = row_tiles * ((k + 255) / 256), t512 = row_tiles * ((k + 511) / 512);
   const double cost256 = (double)((t256 + clusters - 1) / clusters);
-  const double cost512 = (double)((t512 + clusters - 1) / clusters) * 2.0 * kWide512Cost;
+  // the kernel hands a short last wave out as 256-column halves (see Walk)
+  const long long rest = t512 % clusters;
+  const double tail = rest == 0 ? 0.0 : (2 * rest <= clusters && t512 > clusters) ? 1.0 : 2.0 * kWide512Cost;
+  const double cost512 = (double)(t512 / clusters) * 2.0 * kWide512Cost + tail;
   bool wide = cost512 < cost256;
   if (const char* force = std::getenv("SWIGLU_B200_GEMM_BWD_TILE")) {
     if (std::strcmp(force, "256") == 0) wide = false;

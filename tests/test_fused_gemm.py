@@ -142,7 +142,9 @@ def test_single_cta_kernel_variant_agrees():
 
 @pytest.mark.parametrize("tile", ["auto", "256", "512"])
 @pytest.mark.parametrize("m,n,k", [(256, 128, 256), (512, 256, 512), (300, 136, 80), (1000, 2064, 1040),
-                                   (4096, 1408, 1024), (8192, 1024, 2048)])
+                                   (4096, 1408, 1024), (8192, 1024, 2048),
+                                   (6400, 3456, 1536)])  # the last: 75 and 81 wide tiles, so the tail of the
+                                                         # last wave is handed out as 256-column halves
 def test_backward_gemms_match_fp32_reference(m, n, k, tile, monkeypatch):
     """dx, dw_gate, dw_up from the tcgen05 backward kernels (operands whose contiguous dimension is not the
     contraction dimension, i.e. MN-major shared-memory descriptors) against fp32 matmuls of the same bf16
