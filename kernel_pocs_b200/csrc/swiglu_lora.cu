@@ -60,7 +60,7 @@ constexpr int THREADS = 64 + 32 * EPI_WARPS;
 // kind::f16, D fp32, A and B bf16 K-major, M = 128, N = 64
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
 
-// Shared-memory budget for a rank padded to RK (16, 32 or 64): the narrower the adapter tiles, the more
+// Shared-memory layout for a rank padded to RK (16, 32 or 64): the narrower the adapter tiles, the more
 // stages of E / G tiles fit, and bytes in flight are what this kernel's bandwidth comes from.
 //
 // GROUPS: the epilogue warps work as this many independent groups, each covering all four TMEM lane quarters

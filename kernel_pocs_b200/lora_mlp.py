@@ -4,7 +4,8 @@ Mirrors ``fused_lora_swiglu`` of the reference (kernels/lora_mlp/experiments/v3/
 same argument order, same return triple), the one kernel of its LoRA-MLP forward that is not a library GEMM:
 the base projections and the skinny ``x @ A.T`` products stay with cuBLAS, and this step adds the rank-r
 adapter terms and applies SwiGLU in one pass over e and g.  Here it is a TMA-fed tcgen05 kernel
-(``swiglu_b200_lora_swiglu_fwd``).  bf16 only; the rank must be a multiple of 8, at most 64.
+(``swiglu_b200_lora_swiglu_fwd``) for bf16 with a rank that is a multiple of 8 up to 64; other dtypes and
+ranks take library GEMMs for the adapter terms followed by the streaming SwiGLU kernel.
 
 ``LoRAMLP`` / ``lora_mlp`` put that kernel where the reference's ``LoRAMLPv3`` / ``lora_mlp_v3`` put theirs
 (same file, :244-357): library GEMMs for every projection, the fused epilogue in the forward (in place over
@@ -62,14 +63,22 @@ def fused_lora_swiglu(
         # no adapters: plain SwiGLU of the base projections
         h = swiglu_forward(e_base, g_base)[0]
         return (h, e_base, g_base) if save_eg else (h, None, None)
-    if e_base.dtype != torch.bfloat16 or any(t.dtype != torch.bfloat16 for t in (g_base, xa_gate, xa_up, B_gate, B_up)):
-        raise TypeError("fused_lora_swiglu supports bf16 tensors only")
+    if any(t.dtype != e_base.dtype for t in (g_base, xa_gate, xa_up, B_gate, B_up)):
+        raise TypeError("fused_lora_swiglu needs all tensors in one dtype")
     m, n = e_base.shape
     r = xa_gate.shape[1]
     if xa_gate.shape != (m, r) or xa_up.shape != (m, r) or B_gate.shape != (n, r) or B_up.shape != (n, r):
         raise ValueError("expected xa_gate, xa_up of shape [M, r] and B_gate, B_up of shape [N, r]")
-    if r % 8 or not 8 <= r <= 64 or n % 8:
-        raise ValueError("the kernel needs a rank that is a multiple of 8 in [8, 64] and N % 8 == 0")
+    if e_base.dtype != torch.bfloat16 or r % 8 or not 8 <= r <= 64 or n % 8:
+        # fp16 / fp32, or a shape the tensor-core epilogue does not take (rank not a multiple of 8 in
+        # [8, 64], N not a multiple of 8): adapter terms by library GEMMs, then the streaming SwiGLU kernel
+        sg, su = _as_float("s_gate", s_gate), _as_float("s_up", s_up)
+        e = e_base if _inplace else e_base.clone()
+        g = g_base if _inplace else g_base.clone()
+        e.addmm_(xa_gate, B_gate.t(), alpha=sg)
+        g.addmm_(xa_up, B_up.t(), alpha=su)
+        h = swiglu_forward(e, g)[0]
+        return (h, e, g) if save_eg else (h, None, None)
     sg, su = _as_float("s_gate", s_gate), _as_float("s_up", s_up)
     if _inplace and not (e_base.is_contiguous() and g_base.is_contiguous()):
         raise ValueError("the in-place variant needs contiguous e_base and g_base")
@@ -119,15 +128,10 @@ def _lora_mlp_forward(X, W_gate, A_gate, B_gate, s_gate, W_up, A_up, B_up, s_up,
     x2 = X.reshape(-1, X.shape[-1])
     e = x2 @ W_gate.t()
     g = x2 @ W_up.t()
-    r = A_gate.shape[0] if A_gate is not None else 0
-    if A_gate is not None and X.dtype == torch.bfloat16 and r % 8 == 0 and 8 <= r <= 64 and e.shape[1] % 8 == 0:
+    if A_gate is not None:
         h, e, g = fused_lora_swiglu_inplace(e, g, x2 @ A_gate.t(), x2 @ A_up.t(), B_gate, B_up, s_gate, s_up,
                                             save_eg=save_eg)
     else:
-        # fp16 / fp32, or a rank the tensor-core epilogue does not take: adapter terms by library GEMMs
-        if A_gate is not None:
-            e.addmm_(x2 @ A_gate.t(), B_gate.t(), alpha=s_gate)
-            g.addmm_(x2 @ A_up.t(), B_up.t(), alpha=s_up)
         h = swiglu_forward(e, g)[0]
     out = h @ W_down.t()
     if A_down is not None:

@@ -68,15 +68,39 @@ def test_two_calls_and_no_adapter_path():
 
 def test_argument_errors():
     e, g, xag, xau, bg, bu = operands(128, 64, 16)
-    with pytest.raises(ValueError, match="rank"):
-        fused_lora_swiglu(e, g, xag[:, :12].contiguous(), xau[:, :12].contiguous(), bg[:, :12].contiguous(),
-                          bu[:, :12].contiguous())
-    with pytest.raises(TypeError, match="bf16"):
-        fused_lora_swiglu(e.float(), g.float(), xag.float(), xau.float(), bg.float(), bu.float())
+    with pytest.raises(TypeError, match="one dtype"):
+        fused_lora_swiglu(e, g, xag.float(), xau.float(), bg, bu)
     with pytest.raises(ValueError, match="shape"):
         fused_lora_swiglu(e, g, xag, xau, bg[:32].contiguous(), bu)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         fused_lora_swiglu(e.cpu(), g.cpu(), xag.cpu(), xau.cpu(), bg.cpu(), bu.cpu())
+
+
+@pytest.mark.parametrize("dtype,r,n", [(torch.float32, 16, 64), (torch.float16, 8, 200), (torch.bfloat16, 12, 64),
+                                       (torch.bfloat16, 16, 36), (torch.bfloat16, 72, 128)])
+def test_other_dtypes_and_ranks_take_library_gemms(dtype, r, n):
+    """fp32 / fp16 (the reference's kernel takes them, lora_mlp_kernel_v3.py:141-200 has no dtype check) and ranks
+    or widths outside what the tensor-core epilogue handles: same results, no launch of that kernel."""
+    e, g, xag, xau, bg, bu = (t.to(dtype) for t in operands(160, n, 80, seed=13))
+    xag, xau, bg, bu = (t[:, :r].contiguous() for t in (xag, xau, bg, bu))
+    e0 = e.clone()
+    before = _lib.lib.swiglu_b200_lora_launch_count()
+    h, e_full, g_full = fused_lora_swiglu(e, g, xag, xau, bg, bu, 2.0, 0.5, save_eg=True)
+    assert _lib.lib.swiglu_b200_lora_launch_count() == before
+    assert torch.equal(e, e0), "inputs must not be modified"
+    rh, re, rg = reference(e, g, xag, xau, bg, bu, 2.0, 0.5)
+    if dtype == torch.float32:
+        torch.testing.assert_close(h, rh, rtol=1e-4, atol=1e-4)
+        torch.testing.assert_close(e_full, re, rtol=1e-4, atol=1e-4)
+    else:
+        # h is computed from the ROUNDED e and g here (they are materialised in the I/O dtype)
+        rh16 = torch.nn.functional.silu(e_full.float()) * g_full.float()
+        assert_close_bf16(e_full, re, "e_full") if dtype == torch.bfloat16 else torch.testing.assert_close(
+            e_full.float(), re, rtol=2e-3, atol=2e-3)
+        torch.testing.assert_close(h.float(), rh16, rtol=2.0 ** -7, atol=1e-3)
+    e2 = e.clone()
+    h2, e_in, _ = fused_lora_swiglu_inplace(e2, g.clone(), xag, xau, bg, bu, 2.0, 0.5, save_eg=True)
+    assert e_in.data_ptr() == e2.data_ptr() and torch.equal(h2, h) and torch.equal(e_in, e_full)
 
 
 @pytest.mark.parametrize("m,n,r", [(200, 200, 24), (1024, 4104, 16)])
