@@ -339,7 +339,7 @@ swiglu_gemm_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __g
       int m0, n0;
       walk.at(t, m0, n0);
       const int b = (int)(i & 1);
-      ok = wait<false>(&acc_full[b], (uint32_t)((i >> 1) & 1), p.status, 300 + b);
+      ok = wait<false, 200>(&acc_full[b], (uint32_t)((i >> 1) & 1), p.status, 300 + b);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int row = m0 + (int)rank * BM + quarter * 32 + lane;

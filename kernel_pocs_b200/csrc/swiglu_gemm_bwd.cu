@@ -47,7 +47,8 @@ constexpr int A_BYTES = 128 * BK * 2;         // 16 KiB: 128 rows (or columns) x
 constexpr int B_BYTES = 128 * BK * 2;         // 16 KiB: 64 contraction rows x 128 output columns
 constexpr int CHUNK_BYTES = 64 * BK * 2;      // 8 KiB: one 64-column chunk of an MN-major tile
 constexpr int TMEM_COLS = 512;                // all of it: two accumulators of 256 fp32 columns, or one of 512
-constexpr int THREADS = 192;
+constexpr int EPI_PARTS = 2;                  // epilogue warps per TMEM lane quarter; they split a tile's columns
+constexpr int THREADS = 64 + 128 * EPI_PARTS;
 
 // NT = output columns of a pair tile.  256: one MMA of N = 256 per 16 contraction elements, two accumulator
 // buffers, so a tile's epilogue overlaps the next tile's MMAs.  512: two such MMAs share the A operand, which
@@ -154,7 +155,7 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
     }
     for (int b = 0; b < ACC_BUFS; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 8);
+      mbar_init(&acc_empty[b], 8 * EPI_PARTS);  // every epilogue warp of both CTAs
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -264,6 +265,7 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
     }
   } else {
     const int quarter = warp & 3;
+    const int part = (warp - 2) >> 2;
     long long i = 0;
     bool ok = true;
     for (long long t = pair_id; t < walk.total && ok; t += n_pairs, ++i) {
@@ -271,7 +273,7 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
       int col_base, halves;
       walk.at(t, tr, col_base, halves);
       const int b = (int)(i % ACC_BUFS);
-      ok = wait<false>(&acc_full[b], (uint32_t)((i / ACC_BUFS) & 1), p.status, 300 + b);
+      ok = wait<false, 200>(&acc_full[b], (uint32_t)((i / ACC_BUFS) & 1), p.status, 300 + b);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // dX: CTA r owns rows tr*256 + r*128 ..; dW: CTA 0 writes dWg rows tr*128 .., CTA 1 the same rows of dWu
@@ -279,21 +281,30 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
                                             : tr * 128 + quarter * 32 + lane;
       __nv_bfloat16* out = (MODE == MODE_DW && rank == 1) ? p.out1 : p.out0;
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)b * 256u;
+      // 64 columns per wait: the loads' latency, not their count, is what an epilogue thread spends its time on,
+      // and with a single 512-column accumulator that time is not hidden behind the next tile's MMAs
 #pragma unroll 1
-      for (int c = 0; c < halves * 256; c += 16) {
-        uint32_t v[16];
-        tmem_ld16(t_row + c, v);
+      for (int c = part * 64; c < halves * 256; c += 64 * EPI_PARTS) {
+        uint32_t v[64];
+        tmem_ld32(t_row + c, v);
+        tmem_ld32(t_row + c + 32, v + 32);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < out_rows && col_base + c < p.k) {
-          uint32_t o[8];
+        if (row < out_rows) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            __nv_bfloat162 x = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
-            o[j] = *reinterpret_cast<uint32_t*>(&x);
+          for (int q = 0; q < 4; ++q) {
+            if (col_base + c + 16 * q < p.k) {  // k is a multiple of 16: groups of 16 columns are all in or all out
+              uint32_t o[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                __nv_bfloat162 x = __floats2bfloat162_rn(__uint_as_float(v[16 * q + 2 * j]),
+                                                         __uint_as_float(v[16 * q + 2 * j + 1]));
+                o[j] = *reinterpret_cast<uint32_t*>(&x);
+              }
+              uint4* dst = reinterpret_cast<uint4*>(out + row * p.k + col_base + c + 16 * q);
+              dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+              dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+            }
           }
-          uint4* dst = reinterpret_cast<uint4*>(out + row * p.k + col_base + c);
-          dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-          dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

@@ -57,6 +57,10 @@ constexpr int EPI_WARPS = SWIGLU_LORA_EPI_WARPS;  // EPI_WARPS / 4 warps share a
 #define SWIGLU_LORA_GROUPS 2
 #endif
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
+#ifndef SWIGLU_LORA_EPI_SLEEP_NS
+#define SWIGLU_LORA_EPI_SLEEP_NS 0
+#endif
+constexpr int EPI_SLEEP_NS = SWIGLU_LORA_EPI_SLEEP_NS;  // pause between an epilogue warp's polls of a barrier
 // kind::f16, D fp32, A and B bf16 K-major, M = 128, N = 64
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
 
@@ -103,16 +107,6 @@ __device__ __forceinline__ bool epilogue_all(bool ok, int id, int threads) {
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* b) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
-      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
 }
 
 template <int RK, bool SAVE>
@@ -262,8 +256,8 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
         // the store of the previous tile to finish reading, so the next tile may overwrite that buffer.
         unsigned char* h_tile = outs + (group * OUT_BUFS_PER_GROUP + (mine & 1)) * EG_BYTES;
         ++mine;
-        ok = mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1), p.status, 600 + s) &&
-             mbar_wait(&acc_full[b], (uint32_t)((it >> 1) & 1), p.status, 300 + b);
+        ok = mbar_wait<EPI_SLEEP_NS>(&full[s], (uint32_t)((it / STAGES) & 1), p.status, 600 + s) &&
+             mbar_wait<EPI_SLEEP_NS>(&acc_full[b], (uint32_t)((it >> 1) & 1), p.status, 300 + b);
         if (!__all_sync(0xffffffffu, ok)) ok = false;  // warp-uniform, for the warp-wide TMEM loads
         if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

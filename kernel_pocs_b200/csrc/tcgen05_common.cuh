@@ -32,10 +32,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
 
 // Bounded wait.  Returns false when the barrier did not flip within WAIT_CYCLES or when another
 // thread has already reported a failure; the first failure stores `code` in *status.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int* status, int code) {
   if (mbar_try_wait(b, parity)) return true;
   const long long t0 = clock64();
   for (int spin = 0;; ++spin) {
+    if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);  // many warps polling flat out load the shared-memory pipe
     if (mbar_try_wait(b, parity)) return true;
     if ((spin & 63) == 63) {
       if (*reinterpret_cast<volatile int*>(status) != 0) return false;
@@ -87,6 +89,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
 
 // Shared-memory matrix descriptor for an operand whose contiguous dimension is M or N ("MN-major"),
 // stored as chunks of 64 contiguous elements (128 bytes, 128-byte swizzle) by 8-row groups along K:
@@ -129,12 +141,16 @@ __device__ __forceinline__ bool try_wait_cluster(uint64_t* b, uint32_t parity) {
       : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
   return ok != 0;
 }
-template <bool CLUSTER_SCOPE>
+// SLEEP_NS > 0: pause that long between polls.  For waits that last a whole tile (the epilogue warps waiting for
+// an accumulator): every poll is a shared-memory access, and several warps polling flat out take bandwidth from
+// the operand traffic of the MMAs they are waiting for.
+template <bool CLUSTER_SCOPE, int SLEEP_NS = 0>
 __device__ __forceinline__ bool wait(uint64_t* b, uint32_t parity, int* status, int code) {
   auto poll = [&] { return CLUSTER_SCOPE ? try_wait_cluster(b, parity) : mbar_try_wait(b, parity); };
   if (poll()) return true;
   const long long t0 = clock64();
   for (int spin = 0;; ++spin) {
+    if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
     if (poll()) return true;
     if ((spin & 63) == 63) {
       if (*reinterpret_cast<volatile int*>(status) != 0) return false;

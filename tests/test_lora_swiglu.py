@@ -95,8 +95,9 @@ def test_other_dtypes_and_ranks_take_library_gemms(dtype, r, n):
     else:
         # h is computed from the ROUNDED e and g here (they are materialised in the I/O dtype)
         rh16 = torch.nn.functional.silu(e_full.float()) * g_full.float()
-        assert_close_bf16(e_full, re, "e_full") if dtype == torch.bfloat16 else torch.testing.assert_close(
-            e_full.float(), re, rtol=2e-3, atol=2e-3)
+        # the library's 16-bit addmm_ may round the product before it adds e: errors scale with the terms, not the sum
+        eps = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+        assert bool(((e_full.float() - re).abs() <= eps * (re.abs() + re.pow(2).mean().sqrt())).all()), "e_full"
         torch.testing.assert_close(h.float(), rh16, rtol=2.0 ** -7, atol=1e-3)
     e2 = e.clone()
     h2, e_in, _ = fused_lora_swiglu_inplace(e2, g.clone(), xag, xau, bg, bu, 2.0, 0.5, save_eg=True)
