@@ -72,6 +72,39 @@ def test_argument_errors_need_no_device():
     assert b(dg, du, dg, g, u, 4, 8, 8, 8, 8, _lib.F32, 1.0, 1.0, -1, None) == c["ERR_ALIAS"]  # dgate over dout
 
 
+def test_recompute_and_tensor_core_entries_argument_errors_need_no_device():
+    """swiglu_b200_bwd_recompute and the GEMM / LoRA entries reject bad arguments before any CUDA call."""
+    c = _codes()
+    r = _lib.lib.swiglu_b200_bwd_recompute
+    p = 0x1000
+    h, dg, du, d, g, u = (p + i * 0x10000 for i in range(6))
+    assert r(h, dg, du, d, g, u, 64, 5, 1.0, 1.0, -1, None) == c["ERR_DTYPE"]
+    assert r(h, dg, du, d, g, u, -1, _lib.BF16, 1.0, 1.0, -1, None) == c["ERR_SHAPE"]
+    assert r(None, None, None, None, None, None, 0, _lib.BF16, 1.0, 1.0, -1, None) == 0
+    assert r(h, dg, None, d, g, u, 64, _lib.BF16, 1.0, 1.0, -1, None) == c["ERR_NULL"]
+    assert r(h + 1, dg, du, d, g, u, 64, _lib.BF16, 1.0, 1.0, -1, None) == c["ERR_ALIGN"]
+    assert r(h, h, du, d, g, u, 64, _lib.BF16, 1.0, 1.0, -1, None) == c["ERR_ALIAS"]       # two outputs, one buffer
+    assert r(d + 32, dg, du, d, g, u, 64, _lib.BF16, 1.0, 1.0, -1, None) == c["ERR_ALIAS"]  # partial overlap
+
+    gf, gb, lo = _lib.lib.swiglu_b200_gemm_fwd, _lib.lib.swiglu_b200_gemm_bwd, _lib.lib.swiglu_b200_lora_swiglu_fwd
+    st = p + 0x70000
+    assert gf(h, None, None, d, g, u, -1, 128, 64, 1.0, 1.0, st, -1, None) == c["ERR_SHAPE"]
+    assert gf(h, None, None, d, g, u, 128, 120, 64, 1.0, 1.0, st, -1, None) == c["ERR_SHAPE"]   # n % 16
+    assert gf(h, None, None, d, g, u, 128, 128, 60, 1.0, 1.0, st, -1, None) == c["ERR_SHAPE"]   # k % 8
+    assert gf(None, None, None, d, g, u, 128, 128, 64, 1.0, 1.0, st, -1, None) == c["ERR_NULL"]
+    assert gf(h, dg, None, d, g, u, 128, 128, 64, 1.0, 1.0, st, -1, None) == c["ERR_NULL"]      # gate_out without up_out
+    assert gf(h + 8, None, None, d, g, u, 128, 128, 64, 1.0, 1.0, st, -1, None) == c["ERR_ALIGN"]
+    assert gf(None, None, None, None, None, None, 0, 128, 64, 1.0, 1.0, None, -1, None) == 0
+    assert gb(h, dg, du, d, g, u, p + 0x80000, p + 0x90000, 128, 128, 72, st, -1, None) == c["ERR_SHAPE"]  # k % 16
+    assert gb(h, dg, None, d, g, u, p + 0x80000, p + 0x90000, 128, 128, 64, st, -1, None) == c["ERR_NULL"]
+    assert gb(h, None, None, d, g, None, None, None, 128, 128, 64, st, -1, None) == c["ERR_NULL"]  # dx needs weights
+    assert lo(h, None, None, d, g, u, u, dg, du, 128, 64, 12, 1.0, 1.0, st, -1, None) == c["ERR_SHAPE"]   # rank % 8
+    assert lo(h, None, None, d, g, u, u, dg, du, 128, 64, 72, 1.0, 1.0, st, -1, None) == c["ERR_SHAPE"]   # rank > 64
+    assert lo(h, dg, None, d, g, u, u, dg, du, 128, 64, 16, 1.0, 1.0, st, -1, None) == c["ERR_NULL"]
+    assert lo(h, None, None, d, g, u, u, dg, du, 128, 64, 16, 1.0, 1.0, None, -1, None) == c["ERR_NULL"]
+    assert lo(None, None, None, None, None, None, None, None, None, 0, 64, 16, 1.0, 1.0, None, -1, None) == 0
+
+
 def test_host_entry_argument_errors_need_no_device():
     c = _codes()
     f = _lib.lib.swiglu_b200_host_fwd_bwd
