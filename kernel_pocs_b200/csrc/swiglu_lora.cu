@@ -57,10 +57,6 @@ constexpr int EPI_WARPS = SWIGLU_LORA_EPI_WARPS;  // EPI_WARPS / 4 warps share a
 #define SWIGLU_LORA_GROUPS 2
 #endif
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
-#ifndef SWIGLU_LORA_EPI_SLEEP_NS
-#define SWIGLU_LORA_EPI_SLEEP_NS 0
-#endif
-constexpr int EPI_SLEEP_NS = SWIGLU_LORA_EPI_SLEEP_NS;  // pause between an epilogue warp's polls of a barrier
 // kind::f16, D fp32, A and B bf16 K-major, M = 128, N = 64
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
 
@@ -256,8 +252,8 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
         // the store of the previous tile to finish reading, so the next tile may overwrite that buffer.
         unsigned char* h_tile = outs + (group * OUT_BUFS_PER_GROUP + (mine & 1)) * EG_BYTES;
         ++mine;
-        ok = mbar_wait<EPI_SLEEP_NS>(&full[s], (uint32_t)((it / STAGES) & 1), p.status, 600 + s) &&
-             mbar_wait<EPI_SLEEP_NS>(&acc_full[b], (uint32_t)((it >> 1) & 1), p.status, 300 + b);
+        ok = mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1), p.status, 600 + s) &&
+             mbar_wait(&acc_full[b], (uint32_t)((it >> 1) & 1), p.status, 300 + b);
         if (!__all_sync(0xffffffffu, ok)) ok = false;  // warp-uniform, for the warp-wide TMEM loads
         if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

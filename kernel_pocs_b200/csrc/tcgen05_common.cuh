@@ -32,12 +32,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
 
 // Bounded wait.  Returns false when the barrier did not flip within WAIT_CYCLES or when another
 // thread has already reported a failure; the first failure stores `code` in *status.
-template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int* status, int code) {
   if (mbar_try_wait(b, parity)) return true;
   const long long t0 = clock64();
   for (int spin = 0;; ++spin) {
-    if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);  // many warps polling flat out load the shared-memory pipe
     if (mbar_try_wait(b, parity)) return true;
     if ((spin & 63) == 63) {
       if (*reinterpret_cast<volatile int*>(status) != 0) return false;
