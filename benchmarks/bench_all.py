@@ -340,6 +340,62 @@ def run_lora(args, device):
         rows.append(r_)
         print(f"{'lora':>16} {provider:>24} {mode:>8} bf16 M{m} N{n} r{r} {mean:9.4f} ms  {r_['gbs_per_gpu']:8.1f} GB/s  "
               f"{100 * r_['frac_of_measured_copy']:6.1f}% of {kind} {peak:.0f}  {r_['tokens_per_s'] / 1e6:8.3f} Mtok/s", flush=True)
+    # the whole gate/up stage of a LoRA MLP from X: one launch (projections + adapters + SwiGLU) against two
+    # cuBLAS GEMMs, two skinny GEMMs and the epilogue kernel above
+    from kernel_pocs_b200.fused_mlp import lora_gate_up_swiglu_forward
+
+    k = C4["k"]
+    x = mk(m, k)
+    wg, wu = mk(n, k, std=0.02), mk(n, k, std=0.02)
+    ag, au = mk(r, k, std=0.02), mk(r, k, std=0.02)
+    burst, _, kind_t = tensor_peak()
+
+    def one_launch():
+        lora_gate_up_swiglu_forward(x, wg, wu, ag, bg, 2.0, au, bu, 2.0)
+
+    def gemms_then_epilogue():
+        fused_lora_swiglu(x @ wg.t(), x @ wu.t(), x @ ag.t(), x @ au.t(), bg, bu, 2.0, 2.0)
+
+    flops = 4.0 * m * n * k
+    for provider, fn in (("b200-lora-gemm-1-launch", one_launch), ("cublas-x2+b200-lora-epilogue", gemms_then_epilogue)):
+        mean, med, best = time_cuda(fn, lambda: None, args.warmup, args.rep)
+        check_status(device)
+        r_ = {"config": "lora", "provider": provider, "mode": "forward-from-x", "dtype": "bfloat16", "m": m, "n": n,
+              "k": k, "r": r, "ms_mean_trimmed": mean, "ms_median": med, "ms_min": best, "flops": flops,
+              "tflops": flops / (mean * 1e-3) / 1e12, "tokens_per_s": m / (mean * 1e-3)}
+        r_["frac_of_measured_bf16_burst"] = r_["tflops"] / burst
+        rows.append(r_)
+        print(f"{'lora':>16} {provider:>28} from-x bf16 M{m} N{n} K{k} r{r} {mean:9.4f} ms  {r_['tflops']:8.1f} TFLOP/s  "
+              f"{100 * r_['frac_of_measured_bf16_burst']:5.1f}% of {kind_t} cuBLAS burst {burst:.0f}  "
+              f"{r_['tokens_per_s'] / 1e6:8.3f} Mtok/s", flush=True)
+    # whole LoRA MLP, forward + backward (gradients for X and the six adapter matrices, base weights frozen):
+    # this library's LoRAMLP against the same block written with PyTorch operators under autograd
+    from kernel_pocs_b200.lora_mlp import LoRAMLP
+
+    wd = mk(k, n, std=0.02)
+    ad, bd = mk(r, n, std=0.02), mk(k, r, std=0.3)
+    dy = mk(m, k)
+    train = [t.clone().requires_grad_(True) for t in (x, ag, bg, au, bu, ad, bd)]
+
+    def own_mlp():
+        xx, a1, b1, a2, b2, a3, b3 = train
+        y = LoRAMLP.apply(xx, wg, a1, b1, 2.0, wu, a2, b2, 2.0, wd, a3, b3, 2.0)
+        torch.autograd.grad(y, train, dy)
+
+    def torch_mlp():
+        xx, a1, b1, a2, b2, a3, b3 = train
+        proj = lambda t, w, a, b_: torch.addmm(t @ w.t(), t @ a.t(), b_.t(), alpha=2.0)
+        y = proj(torch.nn.functional.silu(proj(xx, wg, a1, b1)) * proj(xx, wu, a2, b2), wd, a3, b3)
+        torch.autograd.grad(y, train, dy)
+
+    for provider, fn in (("b200-lora-mlp", own_mlp), ("torch-autograd-lora-mlp", torch_mlp)):
+        mean, med, best = time_cuda(fn, lambda: None, max(2, args.warmup // 2), max(5, args.rep // 2))
+        check_status(device)
+        r_ = {"config": "lora", "provider": provider, "mode": "mlp-fwd+bwd", "dtype": "bfloat16", "m": m, "n": n, "k": k,
+              "r": r, "ms_mean_trimmed": mean, "ms_median": med, "ms_min": best, "tokens_per_s": m / (mean * 1e-3)}
+        rows.append(r_)
+        print(f"{'lora':>16} {provider:>28} mlp fwd+bwd bf16 M{m} N{n} K{k} r{r} {mean:9.4f} ms  "
+              f"{r_['tokens_per_s'] / 1e6:8.3f} Mtok/s", flush=True)
     return rows
 
 

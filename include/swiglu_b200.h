@@ -195,6 +195,21 @@ SWIGLU_B200_API int swiglu_b200_gemm_fwd(void* h, void* gate_out, void* up_out, 
 SWIGLU_B200_API int swiglu_b200_gemm_fwd_noalloc(void* h, const void* x, const void* w_gate, const void* w_up, int64_t m, int64_t n,
                                  int64_t k, float gm, float dm, int* status_host, int device, void* stream);
 
+/* Fused gate/up projection WITH LoRA adapters + SwiGLU, one launch:
+ *   e = x.w_gate^T + s_g (x.A_g^T).B_g^T,  g = x.w_up^T + s_u (x.A_u^T).B_u^T,  h = silu(e*gm) * g * dm.
+ * Replaces the reference's Triton dual GEMM with fused LoRA, _fused_gate_up_swiglu_kernel / fused_gate_up_swiglu
+ * (kernels/lora_mlp/experiments/v2/lora_mlp_kernel_v2.py:32-209), and, against its v3 path, the two base GEMMs
+ * plus fused_lora_swiglu (v3:141-200) without e and g ever leaving the chip unless asked for.
+ *   xa_scaled [m, 2r]  = [s_g * x.A_g^T | s_u * x.A_u^T], bf16, prepared by the caller (a skinny library GEMM)
+ *   b_gate, b_up [n, r] the adapters' second factors; r a multiple of 8, at most 64 (r = 0: no adapters)
+ *   e_out, g_out       NULL, or where to store e and g (bf16) for a backward pass
+ * The adapter terms are extra steps of the same contraction (see csrc/swiglu_gemm.cu); other arguments and
+ * requirements as swiglu_b200_gemm_fwd. */
+SWIGLU_B200_API int swiglu_b200_lora_gemm_fwd(void* h, void* e_out, void* g_out, const void* x, const void* w_gate,
+                              const void* w_up, const void* xa_scaled, const void* b_gate, const void* b_up, int64_t m,
+                              int64_t n, int64_t k, int64_t r, float gm, float dm, void* status, int device,
+                              void* stream);
+
 /* Backward GEMMs of the fused projection, from dgate/dup (the outputs of swiglu_b200_bwd on the
  * saved pre-activations):
  *     dx      [m, k] = dgate . w_gate + dup . w_up        (skipped when dx is NULL)

@@ -62,6 +62,7 @@ struct GemmParams {
   int* status;
   long long m, n, k;
   float gm, dm;
+  int r;  // rank of the LoRA adapters added to both projections (pair kernel only), 0 for none
 };
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -210,6 +211,13 @@ swiglu_gemm_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 // 48 KiB.  Clusters walk the tiles persistently; TMEM holds two accumulator buffers so the
 // epilogue of one tile overlaps the MMAs of the next.  Tiles are visited in bands of 8 row-tiles
 // so that the X band and the weight tiles in flight stay in L2.
+//
+// LoRA adapters (p.r > 0): e = X.Wg^T + s_g (X.Ag^T).Bg^T and g likewise are ONE longer contraction,
+//   [X | XA'] . [Wg | Bg']^T   with XA' = [s_g X.Ag^T | s_u X.Au^T]  (M x 2r, prepared by the caller),
+// where the gate half of the MMA's N dimension sees Bg' = [Bg | 0] and the up half Bu' = [0 | Bu].  So after the
+// K blocks of X come ceil(2r / 64) blocks whose A tile is loaded from XA' and whose B tile is loaded from Bg at
+// column 64 j (rank 0) or from Bu at column 64 j - r (rank 1): the tiled loads fill whatever lies outside
+// the r columns of the adapter matrix, to the left (negative coordinates) as to the right, with zeros.
 namespace pair {
 
 #ifndef SWIGLU_GEMM_PAIR_STAGES
@@ -241,7 +249,9 @@ struct TileWalk {
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 swiglu_gemm_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wg,
-                            const __grid_constant__ CUtensorMap map_wu, const GemmParams p) {
+                            const __grid_constant__ CUtensorMap map_wu, const __grid_constant__ CUtensorMap map_xa,
+                            const __grid_constant__ CUtensorMap map_bg, const __grid_constant__ CUtensorMap map_bu,
+                            const GemmParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);  // used in the leader only
@@ -256,7 +266,8 @@ swiglu_gemm_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __g
   const long long pair_id = blockIdx.x >> 1;
   const long long n_pairs = gridDim.x >> 1;
   const TileWalk walk(p.m, p.n);
-  const int k_blocks = (int)((p.k + BK - 1) / BK);
+  const int main_blocks = (int)((p.k + BK - 1) / BK);
+  const int k_blocks = main_blocks + (p.r > 0 ? (2 * p.r + BK - 1) / BK : 0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -298,8 +309,15 @@ swiglu_gemm_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __g
           const uint32_t leader_full = map_to_rank(smem_u32(&full[s]), 0);
           remote_expect_tx(leader_full, STAGE_BYTES);
           unsigned char* stage = smem + s * STAGE_BYTES;
-          tma_load_2d_pair(stage, &map_x, kb * BK, m0 + (int)rank * BM, leader_full);
-          tma_load_2d_pair(stage + TILE_BYTES, map_w, kb * BK, n0, leader_full);
+          if (kb < main_blocks) {
+            tma_load_2d_pair(stage, &map_x, kb * BK, m0 + (int)rank * BM, leader_full);
+            tma_load_2d_pair(stage + TILE_BYTES, map_w, kb * BK, n0, leader_full);
+          } else {
+            const int c0 = (kb - main_blocks) * BK;  // column of XA' this block starts at
+            tma_load_2d_pair(stage, &map_xa, c0, m0 + (int)rank * BM, leader_full);
+            tma_load_2d_pair(stage + TILE_BYTES, rank == 0 ? &map_bg : &map_bu, rank == 0 ? c0 : c0 - p.r, n0,
+                             leader_full);
+          }
         }
       }
     }
@@ -453,14 +471,10 @@ int pair_clusters(int dev, int* out) {
   return SWIGLU_B200_OK;
 }
 
-}  // namespace
-
-extern "C" {
-
-uint64_t swiglu_b200_gemm_launch_count(void) { return g_gemm_launches.load(std::memory_order_relaxed); }
-
-int swiglu_b200_gemm_fwd(void* h, void* gate_out, void* up_out, const void* x, const void* w_gate, const void* w_up,
-                         int64_t m, int64_t n, int64_t k, float gm, float dm, void* status, int device, void* stream) {
+// Shared by swiglu_b200_gemm_fwd (r = 0) and swiglu_b200_lora_gemm_fwd (adapters of rank r, pair kernel only).
+int gemm_fwd_impl(void* h, void* gate_out, void* up_out, const void* x, const void* w_gate, const void* w_up,
+                  const void* xa_scaled, const void* b_gate, const void* b_up, int64_t m, int64_t n, int64_t k, int r,
+                  float gm, float dm, void* status, int device, void* stream) {
   if (m < 0 || n < 0 || k < 0) return SWIGLU_B200_ERR_SHAPE;
   if (m == 0 || n == 0) return SWIGLU_B200_OK;
   // 16-byte global strides for the tiled copies and 32-byte output groups
@@ -489,9 +503,18 @@ int swiglu_b200_gemm_fwd(void* h, void* gate_out, void* up_out, const void* x, c
     }
   } restore{switched, prev};
 
-  CUtensorMap map_x, map_wg, map_wu;
+  CUtensorMap map_x, map_wg, map_wu, map_xa, map_bg, map_bu;
   if (!make_map(&map_x, x, m, k) || !make_map(&map_wg, w_gate, n, k) || !make_map(&map_wu, w_up, n, k))
     return SWIGLU_B200_ERR_DEVICE;
+  if (r > 0) {
+    // boxes as wide as a K block over matrices of only 2r / r columns: the loads fill the rest with zeros
+    if (!make_map(&map_xa, xa_scaled, m, 2 * r) || !make_map(&map_bg, b_gate, n, r) || !make_map(&map_bu, b_up, n, r))
+      return SWIGLU_B200_ERR_DEVICE;
+  } else {
+    map_xa = map_x;  // never read
+    map_bg = map_wg;
+    map_bu = map_wu;
+  }
 
   static std::atomic<bool> attr_set[64];
   int dev = 0;
@@ -505,27 +528,54 @@ int swiglu_b200_gemm_fwd(void* h, void* gate_out, void* up_out, const void* x, c
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
-  if (use_pair_kernel()) {
+  if (use_pair_kernel() || r > 0) {
     int clusters = 0;
     const int rc = pair_clusters(dev, &clusters);
     if (rc != SWIGLU_B200_OK) return rc;
     GemmParams pp{static_cast<__nv_bfloat16*>(h), static_cast<__nv_bfloat16*>(gate_out),
-                  static_cast<__nv_bfloat16*>(up_out), static_cast<int*>(status), m, n, k, gm, dm};
+                  static_cast<__nv_bfloat16*>(up_out), static_cast<int*>(status), m, n, k, gm, dm, r};
     const long long pair_tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
     const long long use = pair_tiles < clusters ? pair_tiles : clusters;
-    pair::swiglu_gemm_fwd_pair_kernel<<<(unsigned)(2 * use), THREADS, pair::SMEM_BYTES, st>>>(map_x, map_wg, map_wu, pp);
+    pair::swiglu_gemm_fwd_pair_kernel<<<(unsigned)(2 * use), THREADS, pair::SMEM_BYTES, st>>>(map_x, map_wg, map_wu, map_xa, map_bg,
+                                                                                             map_bu, pp);
     if (cudaGetLastError() != cudaSuccess) return SWIGLU_B200_ERR_LAUNCH;
     g_gemm_launches.fetch_add(1, std::memory_order_relaxed);
     return SWIGLU_B200_OK;
   }
   GemmParams p{static_cast<__nv_bfloat16*>(h), static_cast<__nv_bfloat16*>(gate_out), static_cast<__nv_bfloat16*>(up_out),
-               static_cast<int*>(status), m, n, k, gm, dm};
+               static_cast<int*>(status), m, n, k, gm, dm, 0};
   const long long tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   if (tiles > 0x7fffffffLL) return SWIGLU_B200_ERR_SHAPE;
   swiglu_gemm_fwd_kernel<<<(unsigned)tiles, THREADS, SMEM_BYTES, st>>>(map_x, map_wg, map_wu, p);
   if (cudaGetLastError() != cudaSuccess) return SWIGLU_B200_ERR_LAUNCH;
   g_gemm_launches.fetch_add(1, std::memory_order_relaxed);
   return SWIGLU_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+uint64_t swiglu_b200_gemm_launch_count(void) { return g_gemm_launches.load(std::memory_order_relaxed); }
+
+int swiglu_b200_gemm_fwd(void* h, void* gate_out, void* up_out, const void* x, const void* w_gate, const void* w_up,
+                         int64_t m, int64_t n, int64_t k, float gm, float dm, void* status, int device, void* stream) {
+  return gemm_fwd_impl(h, gate_out, up_out, x, w_gate, w_up, nullptr, nullptr, nullptr, m, n, k, 0, gm, dm, status,
+                       device, stream);
+}
+
+int swiglu_b200_lora_gemm_fwd(void* h, void* e_out, void* g_out, const void* x, const void* w_gate, const void* w_up,
+                              const void* xa_scaled, const void* b_gate, const void* b_up, int64_t m, int64_t n,
+                              int64_t k, int64_t r, float gm, float dm, void* status, int device, void* stream) {
+  if (r < 0) return SWIGLU_B200_ERR_SHAPE;
+  if (r == 0)
+    return gemm_fwd_impl(h, e_out, g_out, x, w_gate, w_up, nullptr, nullptr, nullptr, m, n, k, 0, gm, dm, status,
+                         device, stream);
+  if (r > 64 || r % 8 != 0) return SWIGLU_B200_ERR_SHAPE;
+  if (m > 0 && n > 0 && (!xa_scaled || !b_gate || !b_up)) return SWIGLU_B200_ERR_NULL;
+  if (((uintptr_t)xa_scaled | (uintptr_t)b_gate | (uintptr_t)b_up) % 16) return SWIGLU_B200_ERR_ALIGN;
+  return gemm_fwd_impl(h, e_out, g_out, x, w_gate, w_up, xa_scaled, b_gate, b_up, m, n, k, (int)r, gm, dm, status,
+                       device, stream);
 }
 
 

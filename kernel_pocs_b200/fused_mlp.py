@@ -79,6 +79,44 @@ def gate_up_swiglu_forward(x, w_gate, w_up, gate_multiplier=1.0, down_multiplier
     return h
 
 
+def lora_gate_up_swiglu_forward(x, w_gate, w_up, A_gate, B_gate, s_gate, A_up, B_up, s_up, save_eg=False):
+    """``h = silu(e) * g`` with ``e = x W_g^T + s_g (x A_g^T) B_g^T`` and ``g`` likewise, in ONE tcgen05 launch
+    (``swiglu_b200_lora_gemm_fwd``): the adapter terms ride along as extra steps of the projections' contraction.
+    The counterpart of the reference's ``fused_gate_up_swiglu`` (kernels/lora_mlp/experiments/v2/
+    lora_mlp_kernel_v2.py:141-209).  W ``[n, k]``, A ``[r, k]``, B ``[n, r]``, all bf16; r a multiple of 8 up to 64.
+    Returns ``(h, e, g)`` with ``save_eg`` (e, g rounded to bf16, for a backward pass), else ``(h, None, None)``."""
+    _check_operands(x, w_gate, w_up)
+    n, k = w_gate.shape
+    r = A_gate.shape[0]
+    if A_gate.shape != (r, k) or A_up.shape != (r, k) or B_gate.shape != (n, r) or B_up.shape != (n, r):
+        raise ValueError("expected A_gate, A_up of shape [r, k] and B_gate, B_up of shape [n, r]")
+    if any(t.dtype != torch.bfloat16 for t in (A_gate, A_up, B_gate, B_up)):
+        raise TypeError("fused gate/up SwiGLU supports bf16 operands only")
+    if r % 8 or not 8 <= r <= 64:
+        raise ValueError("the fused kernel needs a rank that is a multiple of 8 in [8, 64]")
+    sg, su = _as_float("s_gate", s_gate), _as_float("s_up", s_up)
+    x2 = x.contiguous().view(-1, k)
+    m = x2.shape[0]
+    # [s_g x A_g^T | s_u x A_u^T]: one skinny library GEMM against the stacked A matrices, scaled per half in fp32
+    xa = (x2 @ torch.cat((A_gate, A_up), dim=0).t()).float()
+    xa[:, :r] *= sg
+    xa[:, r:] *= su
+    xa = xa.to(torch.bfloat16)
+    wg, wu, bg, bu = w_gate.contiguous(), w_up.contiguous(), B_gate.contiguous(), B_up.contiguous()
+    h = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    e = torch.empty_like(h) if save_eg else None
+    g = torch.empty_like(h) if save_eg else None
+    _lib.check(
+        "lora_gate_up_swiglu_forward",
+        _lib.lib.swiglu_b200_lora_gemm_fwd(
+            h.data_ptr(), e.data_ptr() if save_eg else None, g.data_ptr() if save_eg else None, x2.data_ptr(),
+            wg.data_ptr(), wu.data_ptr(), xa.data_ptr(), bg.data_ptr(), bu.data_ptr(), m, n, k, r, 1.0, 1.0,
+            _status(x.device).data_ptr(), x.device.index, torch.cuda.current_stream(x.device).cuda_stream,
+        ),
+    )
+    return h.view(*x.shape[:-1], n), e, g
+
+
 def gate_up_swiglu_backward_gemms(dgate, dup, x, w_gate, w_up, need_dx=True, need_dw=True):
     """``(dx, dw_gate, dw_up)`` from the activation gradients, by this library's tcgen05 kernels
     (``swiglu_b200_gemm_bwd``); entries that are not needed are ``None``."""

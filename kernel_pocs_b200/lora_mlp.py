@@ -7,10 +7,12 @@ adapter terms and applies SwiGLU in one pass over e and g.  Here it is a TMA-fed
 (``swiglu_b200_lora_swiglu_fwd``) for bf16 with a rank that is a multiple of 8 up to 64; other dtypes and
 ranks take library GEMMs for the adapter terms followed by the streaming SwiGLU kernel.
 
-``LoRAMLP`` / ``lora_mlp`` put that kernel where the reference's ``LoRAMLPv3`` / ``lora_mlp_v3`` put theirs
-(same file, :244-357): library GEMMs for every projection, the fused epilogue in the forward (in place over
-the base projections, as in the reference's v6), and in the backward one elementwise pass
-(``swiglu_b200_bwd_recompute``) that turns (dh, e, g) into (h, de, dg).
+``LoRAMLP`` / ``lora_mlp`` are the whole block with the interface of the reference's ``LoRAMLPv3`` /
+``lora_mlp_v3`` (same file, :244-357).  Forward: for bf16 the gate and up projections, both adapters and SwiGLU
+are ONE tcgen05 launch (``swiglu_b200_lora_gemm_fwd``, what the reference's v2 attempted in Triton); other
+dtypes and ranks take library GEMMs and the epilogue above, in place over the base projections as in the
+reference's v6.  Backward: library GEMMs around one elementwise pass (``swiglu_b200_bwd_recompute``) that turns
+(dh, e, g) into (h, de, dg).
 """
 from __future__ import annotations
 
@@ -123,16 +125,32 @@ def swiglu_DWf_DW_dfg_kernel(DW: torch.Tensor, e: torch.Tensor, g: torch.Tensor)
     return DW, e, g
 
 
+def _one_launch_ok(X, W_gate, A_gate) -> bool:
+    """Shapes and dtypes the fused projection + adapters + SwiGLU kernel takes."""
+    if A_gate is None or X.dtype != torch.bfloat16:
+        return False
+    n, k = W_gate.shape
+    r = A_gate.shape[0]
+    return r % 8 == 0 and 8 <= r <= 64 and k % 8 == 0 and n % 16 == 0
+
+
 def _lora_mlp_forward(X, W_gate, A_gate, B_gate, s_gate, W_up, A_up, B_up, s_up, W_down, A_down, B_down, s_down,
                       save_eg):
     x2 = X.reshape(-1, X.shape[-1])
-    e = x2 @ W_gate.t()
-    g = x2 @ W_up.t()
-    if A_gate is not None:
-        h, e, g = fused_lora_swiglu_inplace(e, g, x2 @ A_gate.t(), x2 @ A_up.t(), B_gate, B_up, s_gate, s_up,
-                                            save_eg=save_eg)
+    if _one_launch_ok(X, W_gate, A_gate):
+        # gate and up projections, both adapters and SwiGLU in one tcgen05 launch; e and g leave the chip only
+        # when a backward pass needs them
+        from .fused_mlp import lora_gate_up_swiglu_forward
+
+        h, e, g = lora_gate_up_swiglu_forward(x2, W_gate, W_up, A_gate, B_gate, s_gate, A_up, B_up, s_up, save_eg)
     else:
-        h = swiglu_forward(e, g)[0]
+        e = x2 @ W_gate.t()
+        g = x2 @ W_up.t()
+        if A_gate is not None:
+            h, e, g = fused_lora_swiglu_inplace(e, g, x2 @ A_gate.t(), x2 @ A_up.t(), B_gate, B_up, s_gate, s_up,
+                                                save_eg=save_eg)
+        else:
+            h = swiglu_forward(e, g)[0]
     out = h @ W_down.t()
     if A_down is not None:
         out.addmm_(h @ A_down.t(), B_down.t(), alpha=s_down)
@@ -185,8 +203,15 @@ class LoRAMLP(torch.autograd.Function):
         dA_up = s_up * (dgB.t() @ x2)
         dB_up = s_up * (dg.t() @ (x2 @ A_up.t()))
 
-        dX = de @ W_gate
-        dX.addmm_(dg, W_up)
+        n, k = W_gate.shape
+        if X.dtype == torch.bfloat16 and k % 16 == 0 and n % 8 == 0:
+            # de W_g + dg W_u as ONE contraction of length 2n on this library's tcgen05 kernel
+            from .fused_mlp import gate_up_swiglu_backward_gemms
+
+            dX = gate_up_swiglu_backward_gemms(de, dg, x2, W_gate, W_up, need_dx=True, need_dw=False)[0]
+        else:
+            dX = de @ W_gate
+            dX.addmm_(dg, W_up)
         dX.addmm_(deB, A_gate, alpha=s_gate)
         dX.addmm_(dgB, A_up, alpha=s_up)
         return (dX.view_as(X), None, dA_gate, dB_gate, None, None, dA_up, dB_up, None, None, dA_down, dB_down, None)
