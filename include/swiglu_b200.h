@@ -195,6 +195,15 @@ SWIGLU_B200_API int swiglu_b200_gemm_fwd(void* h, void* gate_out, void* up_out, 
 SWIGLU_B200_API int swiglu_b200_gemm_fwd_noalloc(void* h, const void* x, const void* w_gate, const void* w_up, int64_t m, int64_t n,
                                  int64_t k, float gm, float dm, int* status_host, int device, void* stream);
 
+/* swiglu_b200_gemm_fwd with the GELU of the GeGLU sibling in the epilogue: h = gelu(x.w_gate^T) * (x.w_up^T),
+ * tanh approximation when approximate_tanh != 0, else the erf form; no multipliers.  One launch for the
+ * gate/up stage of the reference's geglu_mlp (kernels/geglu/geglu.py:322-377: one or two library GEMMs followed
+ * by its GeGLU kernel).  A packed [2n, k] weight (pack_geglu_gate_up_weight, :275-286) is passed as
+ * w_gate = packed, w_up = packed + n*k.  Other arguments and requirements as swiglu_b200_gemm_fwd. */
+SWIGLU_B200_API int swiglu_b200_geglu_gemm_fwd(void* h, void* gate_out, void* up_out, const void* x, const void* w_gate,
+                               const void* w_up, int64_t m, int64_t n, int64_t k, int approximate_tanh, void* status,
+                               int device, void* stream);
+
 /* Fused gate/up projection WITH LoRA adapters + SwiGLU, one launch:
  *   e = x.w_gate^T + s_g (x.A_g^T).B_g^T,  g = x.w_up^T + s_u (x.A_u^T).B_u^T,  h = silu(e*gm) * g * dm.
  * Replaces the reference's Triton dual GEMM with fused LoRA, _fused_gate_up_swiglu_kernel / fused_gate_up_swiglu

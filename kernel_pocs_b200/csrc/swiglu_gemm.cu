@@ -38,6 +38,9 @@ namespace {
 
 using namespace swiglu_b200::tc;
 
+using swiglu_b200::ACT_GELU_ERF;
+using swiglu_b200::ACT_GELU_TANH;
+using swiglu_b200::ACT_SILU;
 using swiglu_b200::Consts;
 using swiglu_b200::Math;
 
@@ -247,6 +250,8 @@ struct TileWalk {
   }
 };
 
+// ACT: the gate activation of the epilogue (SiLU, or one of the two GELU forms of the GeGLU sibling).
+template <int ACT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 swiglu_gemm_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wg,
                             const __grid_constant__ CUtensorMap map_wu, const __grid_constant__ CUtensorMap map_xa,
@@ -374,7 +379,7 @@ swiglu_gemm_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __g
           for (int j = 0; j < 8; ++j) {
             const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
             const float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
-            __nv_bfloat162 hb = __floats2bfloat162_rn(Math<true>::fwd(g0, u0, cst), Math<true>::fwd(g1, u1, cst));
+            __nv_bfloat162 hb = __floats2bfloat162_rn(Math<true, ACT>::fwd(g0, u0, cst), Math<true, ACT>::fwd(g1, u1, cst));
             __nv_bfloat162 gb = __floats2bfloat162_rn(g0, g1);
             __nv_bfloat162 ub = __floats2bfloat162_rn(u0, u1);
             hv[j] = *reinterpret_cast<uint32_t*>(&hb);
@@ -442,8 +447,12 @@ int pair_clusters(int dev, int* out) {
       return SWIGLU_B200_OK;
     }
   }
-  if (cudaFuncSetAttribute(pair::swiglu_gemm_fwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           pair::SMEM_BYTES) != cudaSuccess)
+  if (cudaFuncSetAttribute(pair::swiglu_gemm_fwd_pair_kernel<ACT_SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           pair::SMEM_BYTES) != cudaSuccess ||
+      cudaFuncSetAttribute(pair::swiglu_gemm_fwd_pair_kernel<ACT_GELU_TANH>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES) != cudaSuccess ||
+      cudaFuncSetAttribute(pair::swiglu_gemm_fwd_pair_kernel<ACT_GELU_ERF>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES) != cudaSuccess)
     return SWIGLU_B200_ERR_DEVICE;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * 148, 1, 1);
@@ -457,7 +466,7 @@ int pair_clusters(int dev, int* out) {
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, pair::swiglu_gemm_fwd_pair_kernel, &cfg) != cudaSuccess || n < 1)
+  if (cudaOccupancyMaxActiveClusters(&n, pair::swiglu_gemm_fwd_pair_kernel<ACT_SILU>, &cfg) != cudaSuccess || n < 1)
     return SWIGLU_B200_ERR_DEVICE;
   if (const char* dbg = getenv("SWIGLU_B200_DEBUG")) {
     if (dbg[0] == '1') fprintf(stderr, "swiglu_b200: %d resident 2-CTA clusters on device %d\n", n, dev);
@@ -474,7 +483,7 @@ int pair_clusters(int dev, int* out) {
 // Shared by swiglu_b200_gemm_fwd (r = 0) and swiglu_b200_lora_gemm_fwd (adapters of rank r, pair kernel only).
 int gemm_fwd_impl(void* h, void* gate_out, void* up_out, const void* x, const void* w_gate, const void* w_up,
                   const void* xa_scaled, const void* b_gate, const void* b_up, int64_t m, int64_t n, int64_t k, int r,
-                  float gm, float dm, void* status, int device, void* stream) {
+                  float gm, float dm, void* status, int device, void* stream, int act = ACT_SILU) {
   if (m < 0 || n < 0 || k < 0) return SWIGLU_B200_ERR_SHAPE;
   if (m == 0 || n == 0) return SWIGLU_B200_OK;
   // 16-byte global strides for the tiled copies and 32-byte output groups
@@ -528,7 +537,7 @@ int gemm_fwd_impl(void* h, void* gate_out, void* up_out, const void* x, const vo
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
-  if (use_pair_kernel() || r > 0) {
+  if (use_pair_kernel() || r > 0 || act != ACT_SILU) {
     int clusters = 0;
     const int rc = pair_clusters(dev, &clusters);
     if (rc != SWIGLU_B200_OK) return rc;
@@ -536,8 +545,16 @@ int gemm_fwd_impl(void* h, void* gate_out, void* up_out, const void* x, const vo
                   static_cast<__nv_bfloat16*>(up_out), static_cast<int*>(status), m, n, k, gm, dm, r};
     const long long pair_tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
     const long long use = pair_tiles < clusters ? pair_tiles : clusters;
-    pair::swiglu_gemm_fwd_pair_kernel<<<(unsigned)(2 * use), THREADS, pair::SMEM_BYTES, st>>>(map_x, map_wg, map_wu, map_xa, map_bg,
-                                                                                             map_bu, pp);
+    const unsigned grid = (unsigned)(2 * use);
+    if (act == ACT_GELU_TANH)
+      pair::swiglu_gemm_fwd_pair_kernel<ACT_GELU_TANH><<<grid, THREADS, pair::SMEM_BYTES, st>>>(
+          map_x, map_wg, map_wu, map_xa, map_bg, map_bu, pp);
+    else if (act == ACT_GELU_ERF)
+      pair::swiglu_gemm_fwd_pair_kernel<ACT_GELU_ERF><<<grid, THREADS, pair::SMEM_BYTES, st>>>(
+          map_x, map_wg, map_wu, map_xa, map_bg, map_bu, pp);
+    else
+      pair::swiglu_gemm_fwd_pair_kernel<ACT_SILU><<<grid, THREADS, pair::SMEM_BYTES, st>>>(
+          map_x, map_wg, map_wu, map_xa, map_bg, map_bu, pp);
     if (cudaGetLastError() != cudaSuccess) return SWIGLU_B200_ERR_LAUNCH;
     g_gemm_launches.fetch_add(1, std::memory_order_relaxed);
     return SWIGLU_B200_OK;
@@ -562,6 +579,13 @@ int swiglu_b200_gemm_fwd(void* h, void* gate_out, void* up_out, const void* x, c
                          int64_t m, int64_t n, int64_t k, float gm, float dm, void* status, int device, void* stream) {
   return gemm_fwd_impl(h, gate_out, up_out, x, w_gate, w_up, nullptr, nullptr, nullptr, m, n, k, 0, gm, dm, status,
                        device, stream);
+}
+
+int swiglu_b200_geglu_gemm_fwd(void* h, void* gate_out, void* up_out, const void* x, const void* w_gate,
+                               const void* w_up, int64_t m, int64_t n, int64_t k, int approximate_tanh, void* status,
+                               int device, void* stream) {
+  return gemm_fwd_impl(h, gate_out, up_out, x, w_gate, w_up, nullptr, nullptr, nullptr, m, n, k, 0, 1.0f, 1.0f, status,
+                       device, stream, approximate_tanh ? ACT_GELU_TANH : ACT_GELU_ERF);
 }
 
 int swiglu_b200_lora_gemm_fwd(void* h, void* e_out, void* g_out, const void* x, const void* w_gate, const void* w_up,

@@ -84,6 +84,32 @@ def test_host_api_without_gpu():
         dropin.geglu(torch.randn(2, 3), torch.randn(2, 3))
     g, u = torch.randn(4, 9), torch.randn(4, 9)
     assert torch.equal(dropin.torch_geglu_reference(g, u, "none"), torch.nn.functional.gelu(g) * u)
+    # MLP-level helpers (reference tests/test_geglu.py:289-297 and the packing rules of geglu.py:275-308)
+    with pytest.raises(ValueError, match="either packed_gate_up_weight or separate"):
+        dropin.geglu_mlp(torch.randn(2, 3), torch.randn(3, 4), gate_weight=torch.randn(4, 3), up_weight=torch.randn(4, 3),
+                         packed_gate_up_weight=torch.randn(8, 3))
+    with pytest.raises(ValueError, match="separate path requires"):
+        dropin.geglu_mlp(torch.randn(2, 3), torch.randn(3, 4), gate_weight=torch.randn(4, 3))
+    with pytest.raises(ValueError, match="must be even"):
+        dropin.geglu_mlp(torch.randn(2, 3), torch.randn(3, 4), packed_gate_up_weight=torch.randn(7, 3))
+    with pytest.raises(ValueError, match="use packed_gate_up_bias"):
+        dropin.geglu_mlp(torch.randn(2, 3), torch.randn(3, 4), packed_gate_up_weight=torch.randn(8, 3),
+                         gate_bias=torch.randn(4))
+    with pytest.raises(TypeError, match="dtype"):
+        dropin.geglu_mlp(torch.randn(2, 3), torch.randn(3, 4), gate_weight=torch.randn(4, 3).half(),
+                         up_weight=torch.randn(4, 3).half())
+    with pytest.raises(ValueError, match="same shape"):
+        dropin.pack_geglu_gate_up_weight(torch.randn(4, 3), torch.randn(5, 3))
+    with pytest.raises(ValueError, match="both be None or both be tensors"):
+        dropin.pack_geglu_gate_up_bias(torch.randn(4), None)
+    wg, wu = torch.randn(4, 3), torch.randn(4, 3)
+    packed = dropin.pack_geglu_gate_up_weight(wg, wu)
+    assert packed.shape == (8, 3) and torch.equal(packed[:4], wg) and torch.equal(packed[4:], wu)
+    assert dropin.pack_geglu_gate_up_bias(None, None) is None
+    assert torch.equal(dropin.pack_geglu_gate_up_bias(torch.ones(4), torch.zeros(4)), torch.tensor([1.0] * 4 + [0.0] * 4))
+    x, wd = torch.randn(2, 5, 3), torch.randn(3, 4)
+    ref = dropin.torch_geglu_mlp_reference(x, wg, wu, wd, approximate="none")
+    assert torch.allclose(ref, (torch.nn.functional.gelu(x @ wg.t()) * (x @ wu.t())) @ wd.t(), atol=1e-6)
 
 
 def _check(h, dgate, dup, gate, up, dout, approximate, what):
@@ -198,3 +224,88 @@ def test_geglu_wide_rows_and_tails(dname, approximate):
     dgate, dup = geglu_backward(dout0.to(DEVICE), gate_flat, up_flat, approximate)
     assert dgate.data_ptr() == gate.data_ptr()
     _check(h, dgate, dup, gate0, up0, dout0, approximate, f"geglu wide {dname} {approximate}")
+
+
+# ------------------------------------------------------------------------------------------ MLP level
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("use_bias", [False, True])
+@pytest.mark.parametrize("approximate", ["tanh", "none"])
+@pytest.mark.parametrize("intermediate", [257, 272])
+@pytest.mark.parametrize("dtype, atol, rtol", [(torch.float32, 2e-5, 2e-5), (torch.float16, 3e-2, 3e-2),
+                                               (torch.bfloat16, 4e-2, 4e-2)])
+def test_geglu_mlp_packed_matches_separate_and_reference(use_bias, approximate, intermediate, dtype, atol, rtol):
+    """Parametrisation, seed, sizes and tolerances of the reference's test of the same name
+    (tests/test_geglu.py:160-270); width 272 is added because bias-free bf16 at that width takes the one-launch
+    tcgen05 path for the gate/up stage, while 257 (the reference's width) takes library GEMMs + the GeGLU kernels."""
+    from kernel_pocs_b200 import _lib
+    from kernels.geglu import geglu_mlp, pack_geglu_gate_up_bias, pack_geglu_gate_up_weight, torch_geglu_mlp_reference
+
+    torch.manual_seed(3)
+    batch, seq, hidden = 2, 7, 128
+    mk = lambda *shape: (torch.randn(*shape, device=DEVICE, dtype=dtype) * 0.02)
+    x0 = torch.randn(batch, seq, hidden, device=DEVICE, dtype=dtype)
+    wg0, wu0, wd0 = mk(intermediate, hidden), mk(intermediate, hidden), mk(hidden, intermediate)
+    bg0, bu0, bd0 = (mk(intermediate), mk(intermediate), mk(hidden)) if use_bias else (None, None, None)
+    leaf = lambda t: None if t is None else t.detach().clone().requires_grad_(True)
+
+    x_r, wg_r, wu_r, wd_r, bg_r, bu_r, bd_r = map(leaf, (x0, wg0, wu0, wd0, bg0, bu0, bd0))
+    out_ref = torch_geglu_mlp_reference(x_r, wg_r, wu_r, wd_r, bg_r, bu_r, bd_r, approximate)
+    x_s, wg_s, wu_s, wd_s, bg_s, bu_s, bd_s = map(leaf, (x0, wg0, wu0, wd0, bg0, bu0, bd0))
+    before = _lib.lib.swiglu_b200_gemm_launch_count()
+    out_sep = geglu_mlp(x_s, wd_s, gate_weight=wg_s, up_weight=wu_s, gate_bias=bg_s, up_bias=bu_s, down_bias=bd_s,
+                        approximate=approximate, preserve_inputs=False)
+    x_p, wd_p, bd_p = leaf(x0), leaf(wd0), leaf(bd0)
+    w_p = pack_geglu_gate_up_weight(wg0, wu0).requires_grad_(True)
+    b_p = pack_geglu_gate_up_bias(bg0, bu0)
+    if b_p is not None:
+        b_p.requires_grad_(True)
+    out_packed = geglu_mlp(x_p, wd_p, packed_gate_up_weight=w_p, packed_gate_up_bias=b_p, down_bias=bd_p,
+                           approximate=approximate, preserve_inputs=False)
+    one_launch = dtype == torch.bfloat16 and not use_bias and intermediate % 16 == 0
+    assert _lib.lib.swiglu_b200_gemm_launch_count() == before + (2 if one_launch else 0)
+    torch.testing.assert_close(out_sep, out_ref, atol=atol, rtol=rtol)
+    torch.testing.assert_close(out_packed, out_ref, atol=atol, rtol=rtol)
+
+    grad = torch.randn_like(out_ref)
+    out_ref.backward(grad)
+    out_sep.backward(grad)
+    out_packed.backward(grad)
+    close = lambda a, b: torch.testing.assert_close(a, b, atol=atol, rtol=rtol)
+    close(x_s.grad, x_r.grad)
+    close(x_p.grad, x_r.grad)
+    close(wg_s.grad, wg_r.grad)
+    close(wu_s.grad, wu_r.grad)
+    close(wd_s.grad, wd_r.grad)
+    close(w_p.grad[:intermediate], wg_r.grad)
+    close(w_p.grad[intermediate:], wu_r.grad)
+    close(wd_p.grad, wd_r.grad)
+    if use_bias:
+        close(bg_s.grad, bg_r.grad)
+        close(bu_s.grad, bu_r.grad)
+        close(bd_s.grad, bd_r.grad)
+        close(b_p.grad[:intermediate], bg_r.grad)
+        close(b_p.grad[intermediate:], bu_r.grad)
+        close(bd_p.grad, bd_r.grad)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("approximate", ["tanh", "none"])
+@pytest.mark.parametrize("m,n,k", [(256, 128, 256), (300, 272, 200), (2048, 2064, 1024)])
+def test_one_launch_gate_up_geglu(m, n, k, approximate):
+    """swiglu_b200_geglu_gemm_fwd against fp32 PyTorch on the same bf16 operands, and its saved projections."""
+    from kernel_pocs_b200.fused_mlp import check_status
+    from kernel_pocs_b200.geglu import gate_up_geglu_forward
+    from tests.test_fused_gemm import assert_close_bf16
+
+    g = torch.Generator(device=DEVICE).manual_seed(17)
+    x = torch.randn(m, k, generator=g, device=DEVICE).bfloat16()
+    wg = (2.0 * k ** -0.5 * torch.randn(n, k, generator=g, device=DEVICE)).bfloat16()
+    wu = (k ** -0.5 * torch.randn(n, k, generator=g, device=DEVICE)).bfloat16()
+    h, gate, up = gate_up_geglu_forward(x, wg, wu, approximate, save_preactivations=True)
+    check_status(x.device)
+    gate_ref, up_ref = x.float() @ wg.float().t(), x.float() @ wu.float().t()
+    assert_close_bf16(gate, gate_ref, "gate")
+    assert_close_bf16(up, up_ref, "up")
+    assert_close_bf16(h, torch.nn.functional.gelu(gate_ref, approximate=approximate) * up_ref, "h")
+    assert torch.equal(gate_up_geglu_forward(x, wg, wu, approximate), h)
