@@ -1,18 +1,20 @@
-"""Model-level adapter for the SwiGLU path: ``patch(model)`` / ``unpatch(model)``.
+"""Model-level adapter for the SwiGLU path and its GeGLU sibling: ``patch(model)`` / ``unpatch(model)``.
 
 Covers the part of the reference's ``forge.patch`` that calls this path
-(forge/forge/patching/core.py:152-267 for the orchestration, qwen3.py:49-50 for the class mapping,
-kernels/basic.py:88-104 for the closure): every ``Qwen2MLP`` / ``Qwen3MLP`` instance of a Hugging Face
-model gets the forward ``down_proj(swiglu(gate_proj(x), up_proj(x)))`` bound to the CUDA kernels of this
-package, with the original bound method kept for a bit-exact ``unpatch``.  Book-keeping attributes
+(forge/forge/patching/core.py:152-267 for the orchestration, qwen3.py:49-50 and gemma.py:31-32 for the class
+mappings, kernels/basic.py:88-104 and :49-85 for the closures): every ``Qwen2MLP`` / ``Qwen3MLP`` instance of a
+Hugging Face model gets the forward ``down_proj(swiglu(gate_proj(x), up_proj(x)))``, every ``GemmaMLP`` /
+``Gemma2MLP`` the forward ``down_proj(geglu(gate_proj(x), up_proj(x), approximate))`` with the GELU form read
+from the model's config, bound to the CUDA kernels of this package, with the original bound method kept for a
+bit-exact ``unpatch``.  Book-keeping attributes
 (``_forge_patched``, ``_forge_originals``, ``_forge_patched_counts``, ``_forge_arch``) and error types follow the
 reference.  The other kernels of the reference's registry (rmsnorm, rope, embedding, cross entropy, LoRA)
 are not part of this package; asking for them raises ``KeyError``.
 
 One kernel is added that the reference does not have: ``"fused_gate_up"`` replaces the two projection GEMMs
-and the activation by the single tcgen05 kernel of ``fused_mlp`` when the module's projections are plain
-bias-free bf16 ``nn.Linear`` layers (otherwise the module is left to ``"swiglu"``).  It is opt-in:
-``patch(model, kernels=["fused_gate_up", "swiglu"])``.
+and the activation by the single tcgen05 kernel of ``fused_mlp`` (SiLU) or ``geglu`` (GELU) when the module's
+projections are plain bias-free bf16 ``nn.Linear`` layers (otherwise the module is left to the next kernel in the
+list).  It is opt-in: ``patch(model, kernels=["fused_gate_up", "swiglu"])`` or ``[..., "geglu"]``.
 """
 from __future__ import annotations
 
@@ -21,11 +23,19 @@ from typing import Callable, Dict, List, Optional
 import torch
 
 from .fused_mlp import fused_gate_up_swiglu
+from .geglu import FusedGateUpGEGLUFunction, geglu
 from .swiglu import swiglu
 
-SUPPORTED_MODEL_TYPES = ("qwen2", "qwen3")
-MLP_CLASSES = ("Qwen2MLP", "Qwen3MLP")
-DEFAULT_KERNELS = ("swiglu",)
+# model_type -> (MLP class names, kernels tried by default)
+ARCHITECTURES = {
+    "qwen2": (("Qwen2MLP", "Qwen3MLP"), ("swiglu",)),
+    "qwen3": (("Qwen2MLP", "Qwen3MLP"), ("swiglu",)),
+    "gemma": (("GemmaMLP", "Gemma2MLP"), ("geglu",)),
+    "gemma2": (("GemmaMLP", "Gemma2MLP"), ("geglu",)),
+}
+SUPPORTED_MODEL_TYPES = tuple(ARCHITECTURES)
+GELU_EXACT = ("gelu", "gelu_python")
+GELU_TANH = ("gelu_pytorch_tanh", "gelu_new")
 
 
 class SkipPatch(Exception):
@@ -43,9 +53,23 @@ def _model_config(model):
 
 
 def _activation_name(module) -> str:
+    """``hidden_activation`` (Gemma) or ``hidden_act`` of the module's config; ``"silu"`` when it has neither."""
     cfg = getattr(module, "config", None)
-    name = getattr(cfg, "hidden_act", None) if cfg is not None else None
+    name = None
+    if cfg is not None:
+        name = getattr(cfg, "hidden_activation", None) or getattr(cfg, "hidden_act", None)
     return name or "silu"
+
+
+def _gelu_form(module) -> str:
+    """``"tanh"`` or ``"none"`` for ``geglu(..., approximate=...)``, inferred as the reference does
+    (forge/forge/patching/kernels/basic.py:58-78)."""
+    name = _activation_name(module)
+    if name in GELU_EXACT:
+        return "none"
+    if name in GELU_TANH:
+        return "tanh"
+    raise NotImplementedError(f"patch: the geglu kernel cannot infer the GELU variant for hidden_activation={name!r}")
 
 
 def make_swiglu_forward(module) -> Callable:
@@ -60,8 +84,18 @@ def make_swiglu_forward(module) -> Callable:
     return forward
 
 
+def make_geglu_forward(module) -> Callable:
+    approximate = _gelu_form(module)
+
+    def forward(x):
+        return module.down_proj(geglu(module.gate_proj(x), module.up_proj(x), approximate=approximate))
+
+    return forward
+
+
 def make_fused_gate_up_forward(module) -> Callable:
-    if _activation_name(module) != "silu":
+    act = _activation_name(module)
+    if act != "silu" and act not in GELU_EXACT + GELU_TANH:
         raise SkipPatch
     for proj in (module.gate_proj, module.up_proj):
         if type(proj) is not torch.nn.Linear or proj.bias is not None or proj.weight.dtype != torch.bfloat16:
@@ -70,15 +104,23 @@ def make_fused_gate_up_forward(module) -> Callable:
     if k % 8 or n % 16:
         raise SkipPatch
 
-    def forward(x):
-        # weights are read at call time, so optimiser updates and .to() moves are seen
-        return module.down_proj(fused_gate_up_swiglu(x, module.gate_proj.weight, module.up_proj.weight))
+    # weights are read at call time, so optimiser updates and .to() moves are seen
+    if act == "silu":
+        def forward(x):
+            return module.down_proj(fused_gate_up_swiglu(x, module.gate_proj.weight, module.up_proj.weight))
+    else:
+        approximate = _gelu_form(module)
+
+        def forward(x):
+            return module.down_proj(
+                FusedGateUpGEGLUFunction.apply(x, module.gate_proj.weight, module.up_proj.weight, approximate))
 
     return forward
 
 
 FORWARD_MAKERS: Dict[str, Callable] = {
     "swiglu": make_swiglu_forward,
+    "geglu": make_geglu_forward,
     "fused_gate_up": make_fused_gate_up_forward,
 }
 
@@ -87,7 +129,7 @@ def patch(model, kernels: Optional[List[str]] = None):
     """Rebinds the MLP forwards of ``model`` in place and returns it.
 
     ``kernels``: ordered list of kernel names to try per MLP; the first whose factory accepts the module
-    wins.  ``None`` means ``["swiglu"]``.
+    wins.  ``None`` means ``["swiglu"]`` for Qwen2 / Qwen3 and ``["geglu"]`` for Gemma / Gemma 2.
     """
     if getattr(model, "_forge_patched", False):
         raise RuntimeError("Model already patched. Call unpatch(model) first.")
@@ -96,7 +138,8 @@ def patch(model, kernels: Optional[List[str]] = None):
         raise ValueError(
             f"patch: no mapping for model_type={model_type!r}. Supported: {sorted(SUPPORTED_MODEL_TYPES)}."
         )
-    wanted = list(DEFAULT_KERNELS if kernels is None else kernels)
+    mlp_classes, default_kernels = ARCHITECTURES[model_type]
+    wanted = list(default_kernels if kernels is None else kernels)
     for name in wanted:  # validate before touching any module
         if name not in FORWARD_MAKERS:
             raise KeyError(f"patch: unknown kernel {name!r}. Known: {sorted(FORWARD_MAKERS)}.")
@@ -104,7 +147,7 @@ def patch(model, kernels: Optional[List[str]] = None):
     originals: dict = {}
     counts: Dict[str, int] = {}
     for _name, module in model.named_modules():
-        if type(module).__name__ not in MLP_CLASSES:
+        if type(module).__name__ not in mlp_classes:
             continue
         for name in wanted:
             try:

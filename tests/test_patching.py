@@ -23,6 +23,33 @@ def tiny_qwen3(dtype=torch.float32, device="cpu", layers=2):
     return transformers.Qwen3ForCausalLM(cfg).to(device=device, dtype=dtype)
 
 
+def tiny_gemma2(dtype=torch.float32, device="cpu", layers=2, act="gelu_pytorch_tanh"):
+    cfg = transformers.Gemma2Config(
+        vocab_size=512, hidden_size=128, intermediate_size=384, num_hidden_layers=layers, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=32, max_position_embeddings=128, hidden_activation=act,
+    )
+    torch.manual_seed(0)
+    return transformers.Gemma2ForCausalLM(cfg).to(device=device, dtype=dtype)
+
+
+def test_gemma_mlps_get_the_geglu_forward():
+    model = tiny_gemma2()
+    mlps = [m for m in model.modules() if type(m).__name__ == "Gemma2MLP"]
+    patching.patch(model)
+    assert model._forge_arch == "gemma2" and model._forge_patched_counts == {"geglu": len(mlps)} and len(mlps) == 2
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        model(torch.randint(0, 512, (1, 8)))
+    patching.unpatch(model)
+    ids = torch.randint(0, 512, (1, 8))
+    assert torch.equal(model(ids).logits, tiny_gemma2()(ids).logits)
+    # the GELU form comes from the config; an activation that is not a GELU is refused
+    assert patching._gelu_form(mlps[0]) == "tanh"
+    assert patching._gelu_form([m for m in tiny_gemma2(act="gelu").modules() if type(m).__name__ == "Gemma2MLP"][0]) == "none"
+    odd = tiny_gemma2(act="relu")
+    with pytest.raises(NotImplementedError, match="cannot infer the GELU variant"):
+        patching.patch(odd)
+
+
 def test_patch_rebinds_every_mlp_and_unpatch_restores_them():
     model = tiny_qwen3()
     mlps = [m for m in model.modules() if type(m).__name__ == "Qwen3MLP"]
@@ -59,9 +86,13 @@ def test_patch_validates_before_mutating():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("kernels,expected", [(None, "swiglu"), (["fused_gate_up", "swiglu"], "fused_gate_up")])
-def test_patched_logits_and_gradients_match(kernels, expected):
-    model = tiny_qwen3(torch.bfloat16, "cuda", layers=3)
+@pytest.mark.parametrize("make,kernels,expected", [
+    (tiny_qwen3, None, "swiglu"), (tiny_qwen3, ["fused_gate_up", "swiglu"], "fused_gate_up"),
+    (tiny_gemma2, None, "geglu"), (tiny_gemma2, ["fused_gate_up", "geglu"], "fused_gate_up"),
+    (lambda *a, **k: tiny_gemma2(*a, act="gelu", **k), ["fused_gate_up", "geglu"], "fused_gate_up"),
+])
+def test_patched_logits_and_gradients_match(make, kernels, expected):
+    model = make(torch.bfloat16, "cuda", layers=3)
     ids = torch.randint(0, 512, (4, 64), device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
 
     def run():
