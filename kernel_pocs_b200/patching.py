@@ -11,6 +11,14 @@ bit-exact ``unpatch``.  Book-keeping attributes
 reference.  The other kernels of the reference's registry (rmsnorm, rope, embedding, cross entropy, LoRA)
 are not part of this package; asking for them raises ``KeyError``.
 
+``"lora_mlp"`` is the reference's adapter for PEFT-wrapped MLPs (kernels/lora.py:147-188): it accepts a module only
+when its three projections carry an active, unmerged LoRA adapter without dropout, and then routes the activation
+through ``swiglu`` / ``geglu`` while the wrapped projections compute their own adapter terms; any other module is left
+to the next kernel in the list.  PEFT itself is not needed: the wrappers are recognised by their attributes
+(``base_layer``, ``lora_A``, ``lora_B``, ``scaling``, ``lora_dropout``).  ``"lora_mlp_fused"`` (opt-in, not in the
+reference's final mapping) goes further for bias-free bf16 SiLU MLPs: the whole block runs through ``LoRAMLP`` of
+``lora_mlp`` (projections, adapters and SwiGLU in one tcgen05 launch; hand-written backward).
+
 One kernel is added that the reference does not have: ``"fused_gate_up"`` replaces the two projection GEMMs
 and the activation by the single tcgen05 kernel of ``fused_mlp`` (SiLU) or ``geglu`` (GELU) when the module's
 projections are plain bias-free bf16 ``nn.Linear`` layers (otherwise the module is left to the next kernel in the
@@ -28,10 +36,10 @@ from .swiglu import swiglu
 
 # model_type -> (MLP class names, kernels tried by default)
 ARCHITECTURES = {
-    "qwen2": (("Qwen2MLP", "Qwen3MLP"), ("swiglu",)),
-    "qwen3": (("Qwen2MLP", "Qwen3MLP"), ("swiglu",)),
-    "gemma": (("GemmaMLP", "Gemma2MLP"), ("geglu",)),
-    "gemma2": (("GemmaMLP", "Gemma2MLP"), ("geglu",)),
+    "qwen2": (("Qwen2MLP", "Qwen3MLP"), ("lora_mlp", "swiglu")),
+    "qwen3": (("Qwen2MLP", "Qwen3MLP"), ("lora_mlp", "swiglu")),
+    "gemma": (("GemmaMLP", "Gemma2MLP"), ("lora_mlp", "geglu")),
+    "gemma2": (("GemmaMLP", "Gemma2MLP"), ("lora_mlp", "geglu")),
 }
 SUPPORTED_MODEL_TYPES = tuple(ARCHITECTURES)
 GELU_EXACT = ("gelu", "gelu_python")
@@ -118,10 +126,80 @@ def make_fused_gate_up_forward(module) -> Callable:
     return forward
 
 
+def _active_adapter(linear):
+    """Name of the LoRA adapter a PEFT-style wrapped linear would apply, or ``None``."""
+    lora_a, lora_b = getattr(linear, "lora_A", None), getattr(linear, "lora_B", None)
+    if not lora_a or not lora_b:
+        return None
+    active = getattr(linear, "active_adapters", None)
+    if active is None:
+        active = getattr(linear, "active_adapter", None)
+    if callable(active):
+        active = active()
+    if isinstance(active, str):
+        active = [active]
+    for name in (active or list(lora_a.keys())):
+        if name in lora_a and name in lora_b:
+            return name
+    return None
+
+
+def _lora_parts(linear, allow_bias: bool = False):
+    """``(W, A, B, scaling, bias)`` of a wrapped linear whose adapter can be applied exactly by a fused kernel
+    (active, not merged, not disabled, no dropout); ``SkipPatch`` otherwise.  Same policy as the reference's
+    ``_lora_tensors`` (forge/forge/patching/kernels/lora.py:54-79)."""
+    name = _active_adapter(linear)
+    if name is None or getattr(linear, "disable_adapters", False) or getattr(linear, "merged", False):
+        raise SkipPatch
+    base = getattr(linear, "base_layer", linear)
+    bias = getattr(base, "bias", None)
+    if bias is not None and not allow_bias:
+        raise SkipPatch
+    dropouts = getattr(linear, "lora_dropout", {})
+    dropout = dropouts[name] if name in dropouts else None
+    if dropout is not None and not isinstance(dropout, torch.nn.Identity) and float(getattr(dropout, "p", 0.0)) != 0.0:
+        raise SkipPatch
+    scaling = getattr(linear, "scaling", {})
+    return base.weight, linear.lora_A[name].weight, linear.lora_B[name].weight, float(scaling.get(name, 1.0)), bias
+
+
+def make_lora_mlp_forward(module) -> Callable:
+    for proj in (module.gate_proj, module.up_proj, module.down_proj):
+        _lora_parts(proj, allow_bias=True)
+    act = _activation_name(module)
+    if act == "silu":
+        return make_swiglu_forward(module)
+    if act in GELU_EXACT + GELU_TANH:
+        return make_geglu_forward(module)
+    raise SkipPatch
+
+
+def make_lora_mlp_fused_forward(module) -> Callable:
+    if _activation_name(module) != "silu":
+        raise SkipPatch
+    for proj in (module.gate_proj, module.up_proj, module.down_proj):
+        w, a, b, _, _ = _lora_parts(proj)
+        # LoRAMLP differentiates the adapters and the input only: the base weights must be frozen
+        if not (w.dtype == a.dtype == b.dtype == torch.bfloat16) or w.requires_grad:
+            raise SkipPatch
+    from .lora_mlp import LoRAMLP
+
+    def forward(x):
+        # tensors are looked up at call time: optimiser steps, .to() moves and adapter switches are seen
+        wg, ag, bg, sg, _ = _lora_parts(module.gate_proj)
+        wu, au, bu, su, _ = _lora_parts(module.up_proj)
+        wd, ad, bd, sd, _ = _lora_parts(module.down_proj)
+        return LoRAMLP.apply(x, wg, ag, bg, sg, wu, au, bu, su, wd, ad, bd, sd)
+
+    return forward
+
+
 FORWARD_MAKERS: Dict[str, Callable] = {
     "swiglu": make_swiglu_forward,
     "geglu": make_geglu_forward,
     "fused_gate_up": make_fused_gate_up_forward,
+    "lora_mlp": make_lora_mlp_forward,
+    "lora_mlp_fused": make_lora_mlp_fused_forward,
 }
 
 
@@ -129,7 +207,8 @@ def patch(model, kernels: Optional[List[str]] = None):
     """Rebinds the MLP forwards of ``model`` in place and returns it.
 
     ``kernels``: ordered list of kernel names to try per MLP; the first whose factory accepts the module
-    wins.  ``None`` means ``["swiglu"]`` for Qwen2 / Qwen3 and ``["geglu"]`` for Gemma / Gemma 2.
+    wins.  ``None`` means the reference's mapping: ``["lora_mlp", "swiglu"]`` for Qwen2 / Qwen3 (qwen3.py:49-50) and
+    ``["lora_mlp", "geglu"]`` for Gemma / Gemma 2 (gemma.py:31-32).
     """
     if getattr(model, "_forge_patched", False):
         raise RuntimeError("Model already patched. Call unpatch(model) first.")

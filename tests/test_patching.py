@@ -32,6 +32,63 @@ def tiny_gemma2(dtype=torch.float32, device="cpu", layers=2, act="gelu_pytorch_t
     return transformers.Gemma2ForCausalLM(cfg).to(device=device, dtype=dtype)
 
 
+class FakeLoraLinear(torch.nn.Module):
+    """A linear layer wrapped the way PEFT's LoRA wraps it, as far as patch() looks: ``base_layer`` (frozen),
+    ``lora_A`` / ``lora_B`` module dicts keyed by adapter name, ``scaling`` and ``lora_dropout`` dicts, the
+    ``merged`` / ``disable_adapters`` flags and ``active_adapters``."""
+
+    def __init__(self, base: torch.nn.Linear, r: int = 8, alpha: float = 16.0, dropout: float = 0.0, name="default"):
+        super().__init__()
+        self.base_layer = base
+        base.weight.requires_grad_(False)
+        self.lora_A = torch.nn.ModuleDict({name: torch.nn.Linear(base.in_features, r, bias=False)})
+        self.lora_B = torch.nn.ModuleDict({name: torch.nn.Linear(r, base.out_features, bias=False)})
+        torch.nn.init.normal_(self.lora_B[name].weight, std=0.05)  # non-zero, so that the adapters matter
+        self.scaling = {name: alpha / r}
+        self.lora_dropout = torch.nn.ModuleDict(
+            {name: torch.nn.Dropout(dropout) if dropout else torch.nn.Identity()})
+        self.active_adapters = [name]
+        self.merged = False
+        self.disable_adapters = False
+
+    def forward(self, x):
+        a = self.active_adapters[0]
+        return self.base_layer(x) + self.scaling[a] * self.lora_B[a](self.lora_A[a](self.lora_dropout[a](x)))
+
+
+def wrap_mlps(model, **kw):
+    torch.manual_seed(1)
+    for m in model.modules():
+        if type(m).__name__.endswith("MLP"):
+            for proj in ("gate_proj", "up_proj", "down_proj"):
+                setattr(m, proj, FakeLoraLinear(getattr(m, proj), **kw))
+    return model
+
+
+def test_lora_wrapped_mlps_take_the_lora_kernel():
+    model = wrap_mlps(tiny_qwen3())
+    patching.patch(model)
+    assert model._forge_patched_counts == {"lora_mlp": 2}
+    patching.unpatch(model)
+    # adapters that a fused path could not apply exactly (dropout, merged) leave the module to the next kernel
+    model = wrap_mlps(tiny_qwen3(), dropout=0.1)
+    patching.patch(model)
+    assert model._forge_patched_counts == {"swiglu": 2}
+    patching.unpatch(model)
+    model = wrap_mlps(tiny_qwen3())
+    next(m for m in model.modules() if type(m).__name__ == "Qwen3MLP").up_proj.merged = True
+    patching.patch(model)
+    assert model._forge_patched_counts == {"lora_mlp": 1, "swiglu": 1}
+    patching.unpatch(model)
+    # the one-launch kernel takes bf16 only: fp32 wrappers fall through
+    model = wrap_mlps(tiny_qwen3())
+    patching.patch(model, kernels=["lora_mlp_fused", "lora_mlp", "swiglu"])
+    assert model._forge_patched_counts == {"lora_mlp": 2}
+    gemma = wrap_mlps(tiny_gemma2())
+    patching.patch(gemma)
+    assert gemma._forge_patched_counts == {"lora_mlp": 2}
+
+
 def test_gemma_mlps_get_the_geglu_forward():
     model = tiny_gemma2()
     mlps = [m for m in model.modules() if type(m).__name__ == "Gemma2MLP"]
@@ -90,6 +147,10 @@ def test_patch_validates_before_mutating():
     (tiny_qwen3, None, "swiglu"), (tiny_qwen3, ["fused_gate_up", "swiglu"], "fused_gate_up"),
     (tiny_gemma2, None, "geglu"), (tiny_gemma2, ["fused_gate_up", "geglu"], "fused_gate_up"),
     (lambda *a, **k: tiny_gemma2(*a, act="gelu", **k), ["fused_gate_up", "geglu"], "fused_gate_up"),
+    (lambda dtype, device, layers: wrap_mlps(tiny_qwen3(layers=layers)).to(device=device, dtype=dtype), None, "lora_mlp"),
+    (lambda dtype, device, layers: wrap_mlps(tiny_qwen3(layers=layers)).to(device=device, dtype=dtype),
+     ["lora_mlp_fused", "swiglu"], "lora_mlp_fused"),
+    (lambda dtype, device, layers: wrap_mlps(tiny_gemma2(layers=layers)).to(device=device, dtype=dtype), None, "lora_mlp"),
 ])
 def test_patched_logits_and_gradients_match(make, kernels, expected):
     model = make(torch.bfloat16, "cuda", layers=3)
@@ -99,7 +160,7 @@ def test_patched_logits_and_gradients_match(make, kernels, expected):
         model.zero_grad(set_to_none=True)
         out = model(ids, labels=ids)
         out.loss.backward()
-        grads = torch.cat([p.grad.float().flatten() for p in model.parameters()])
+        grads = torch.cat([p.grad.float().flatten() for p in model.parameters() if p.grad is not None])
         return out.logits.detach().clone(), out.loss.detach().clone(), grads
 
     base_logits, base_loss, base_grads = run()
