@@ -104,6 +104,14 @@ SWIGLU_B200_API int swiglu_b200_bwd(void* dgate, void* dup, const void* dout, co
 SWIGLU_B200_API int swiglu_b200_bwd_recompute(void* h, void* dgate, void* dup, const void* dout, const void* gate,
                               const void* up, int64_t n, int dtype, float gm, float dm, int device, void* stream);
 
+/* swiglu_b200_bwd_recompute for the GeGLU sibling: h = gelu(gate) * up with its backward, no multipliers; results
+ * bit-identical to swiglu_b200_geglu_fwd / swiglu_b200_geglu_bwd.  No counterpart in the reference (its LoRA MLP is
+ * SiLU only, kernels/lora_mlp/experiments/v3/lora_mlp_kernel_v3.py:133); this is what a LoRA MLP with a GELU gate
+ * needs in its backward. */
+SWIGLU_B200_API int swiglu_b200_geglu_bwd_recompute(void* h, void* dgate, void* dup, const void* dout, const void* gate,
+                                    const void* up, int64_t n, int dtype, int approximate_tanh, int device,
+                                    void* stream);
+
 /* Dry run of the access planning of swiglu_b200_fwd / swiglu_b200_bwd (and their GeGLU twins): which
  * access width and addressing a call with these pointers and strides would use.  No CUDA call is made and
  * no memory is touched, so the host-side planning can be tested without a device.  No counterpart in the
@@ -218,6 +226,15 @@ SWIGLU_B200_API int swiglu_b200_lora_gemm_fwd(void* h, void* e_out, void* g_out,
                               const void* w_up, const void* xa_scaled, const void* b_gate, const void* b_up, int64_t m,
                               int64_t n, int64_t k, int64_t r, float gm, float dm, void* status, int device,
                               void* stream);
+
+/* swiglu_b200_lora_gemm_fwd with the GELU of the GeGLU sibling in the epilogue (tanh approximation when
+ * approximate_tanh != 0, else the erf form): the gate/up stage of a LoRA MLP of the Gemma family in one launch.
+ * The reference has no fused kernel for this case and routes it through its projection modules and geglu
+ * (forge/forge/patching/kernels/lora.py:166-188). */
+SWIGLU_B200_API int swiglu_b200_lora_geglu_gemm_fwd(void* h, void* e_out, void* g_out, const void* x, const void* w_gate,
+                                    const void* w_up, const void* xa_scaled, const void* b_gate, const void* b_up,
+                                    int64_t m, int64_t n, int64_t k, int64_t r, int approximate_tanh, void* status,
+                                    int device, void* stream);
 
 /* Backward GEMMs of the fused projection, from dgate/dup (the outputs of swiglu_b200_bwd on the
  * saved pre-activations):

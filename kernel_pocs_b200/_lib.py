@@ -67,6 +67,14 @@ SIGNATURES = {
         ctypes.c_int,
         [_c_ptr] * 6 + [_c_i64] * 3 + [ctypes.c_int, _c_ptr, ctypes.c_int, _c_ptr],
     ),
+    "swiglu_b200_lora_geglu_gemm_fwd": (
+        ctypes.c_int,
+        [_c_ptr] * 9 + [_c_i64] * 4 + [ctypes.c_int, _c_ptr, ctypes.c_int, _c_ptr],
+    ),
+    "swiglu_b200_geglu_bwd_recompute": (
+        ctypes.c_int,
+        [_c_ptr] * 6 + [_c_i64, ctypes.c_int, ctypes.c_int, ctypes.c_int, _c_ptr],
+    ),
     "swiglu_b200_lora_gemm_fwd": (
         ctypes.c_int,
         [_c_ptr] * 9 + [_c_i64] * 4 + [ctypes.c_float, ctypes.c_float, _c_ptr, ctypes.c_int, _c_ptr],

@@ -232,14 +232,14 @@ int bwd_typed(const Plan& p, bool inplace, void* dgate, void* dup, const void* d
 
 // ------------------------------------------------------------------ backward with h recomputed
 
-template <class T, int BYTES, bool ALIASED>
+template <class T, int ACT, int BYTES, bool ALIASED>
 int launch_recompute(void* h, void* dgate, void* dup, const void* dout, const void* gate, const void* up, long long n,
                      float gm, float dm, cudaStream_t st) {
   constexpr bool FAST = (sizeof(T) == 2);
   constexpr int LDM = ALIASED ? SWIGLU_LD_ALIASED : SWIGLU_LD_RO;
   constexpr int EPV = BYTES / (int)sizeof(T);
   const long long n_vec = n / EPV;
-  auto kernel = swiglu_bwd_recompute_kernel<T, BYTES, FAST, SWIGLU_THREADS, SWIGLU_BWD_UNROLL, LDM, SWIGLU_ST>;
+  auto kernel = swiglu_bwd_recompute_kernel<T, BYTES, FAST, SWIGLU_THREADS, SWIGLU_BWD_UNROLL, LDM, SWIGLU_ST, ACT>;
   const unsigned grid = grid_for(n_vec, SWIGLU_THREADS, SWIGLU_BWD_UNROLL);
   kernel<<<grid, SWIGLU_THREADS, 0, st>>>(h, dgate, dup, dout, gate, up, n_vec, (int)(n - n_vec * EPV), gm, dm);
   cudaError_t err = cudaGetLastError();
@@ -248,12 +248,12 @@ int launch_recompute(void* h, void* dgate, void* dup, const void* dout, const vo
   return SWIGLU_B200_OK;
 }
 
-template <class T>
+template <class T, int ACT>
 int recompute_by_width(int bytes, bool aliased, void* h, void* dgate, void* dup, const void* dout, const void* gate,
                        const void* up, long long n, float gm, float dm, cudaStream_t st) {
 #define SWIGLU_RECOMPUTE_CASE(B)                                                                          \
-  return aliased ? launch_recompute<T, B, true>(h, dgate, dup, dout, gate, up, n, gm, dm, st)             \
-                 : launch_recompute<T, B, false>(h, dgate, dup, dout, gate, up, n, gm, dm, st)
+  return aliased ? launch_recompute<T, ACT, B, true>(h, dgate, dup, dout, gate, up, n, gm, dm, st)        \
+                 : launch_recompute<T, ACT, B, false>(h, dgate, dup, dout, gate, up, n, gm, dm, st)
   switch (bytes) {
     case 16: SWIGLU_RECOMPUTE_CASE(16);
     case 8: SWIGLU_RECOMPUTE_CASE(8);
@@ -411,6 +411,44 @@ int bwd_entry(void* dgate, void* dup, const void* dout, const void* gate, const 
   }
 }
 
+// Backward that also returns h (see swiglu_bwd_recompute_kernel): six flat tensors of n elements.
+template <int ACT>
+int recompute_entry(void* h, void* dgate, void* dup, const void* dout, const void* gate, const void* up, int64_t n,
+                    int dtype, float gm, float dm, int device, void* stream) {
+  if (dtype != SWIGLU_B200_F32 && dtype != SWIGLU_B200_F16 && dtype != SWIGLU_B200_BF16) return SWIGLU_B200_ERR_DTYPE;
+  if (n < 0) return SWIGLU_B200_ERR_SHAPE;
+  if (n == 0) return SWIGLU_B200_OK;
+  if (!h || !dgate || !dup || !dout || !gate || !up) return SWIGLU_B200_ERR_NULL;
+  const int es = elem_size(dtype);
+  void* outs[3] = {h, dgate, dup};
+  const void* ins[3] = {dout, gate, up};
+  int width = 16;
+  for (int k = 0; k < 3; ++k) {
+    if (addr_of(outs[k]) % es || addr_of(ins[k]) % es) return SWIGLU_B200_ERR_ALIGN;
+    width = pow2_divisor(addr_of(outs[k]), width);
+    width = pow2_divisor(addr_of(ins[k]), width);
+  }
+  // An output may overwrite one input exactly; any other overlap (outputs with each other included) is an error.
+  bool aliased = false;
+  for (int a = 0; a < 3; ++a) {
+    const Extent ea = extent(outs[a], 1, n, n, es);
+    for (int b = a + 1; b < 3; ++b)
+      if (overlaps(ea, extent(outs[b], 1, n, n, es))) return SWIGLU_B200_ERR_ALIAS;
+    for (int b = 0; b < 3; ++b) {
+      if (outs[a] == ins[b]) aliased = true;
+      else if (overlaps(ea, extent(ins[b], 1, n, n, es))) return SWIGLU_B200_ERR_ALIAS;
+    }
+  }
+  DeviceScope scope(device);
+  if (scope.err != cudaSuccess) return fail_cuda(SWIGLU_B200_ERR_DEVICE, scope.err);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case SWIGLU_B200_F32: return recompute_by_width<float, ACT>(width, aliased, h, dgate, dup, dout, gate, up, n, gm, dm, st);
+    case SWIGLU_B200_F16: return recompute_by_width<__half, ACT>(width, aliased, h, dgate, dup, dout, gate, up, n, gm, dm, st);
+    default: return recompute_by_width<__nv_bfloat16, ACT>(width, aliased, h, dgate, dup, dout, gate, up, n, gm, dm, st);
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -447,41 +485,17 @@ int swiglu_b200_geglu_bwd(void* dgate, void* dup, const void* dout, const void* 
                                        dout_row_stride, dtype, 1.0f, 1.0f, device, stream);
 }
 
-// Backward that also returns h (see swiglu_bwd_recompute_kernel): six flat tensors of n elements.
 int swiglu_b200_bwd_recompute(void* h, void* dgate, void* dup, const void* dout, const void* gate, const void* up,
                               int64_t n, int dtype, float gm, float dm, int device, void* stream) {
-  if (dtype != SWIGLU_B200_F32 && dtype != SWIGLU_B200_F16 && dtype != SWIGLU_B200_BF16) return SWIGLU_B200_ERR_DTYPE;
-  if (n < 0) return SWIGLU_B200_ERR_SHAPE;
-  if (n == 0) return SWIGLU_B200_OK;
-  if (!h || !dgate || !dup || !dout || !gate || !up) return SWIGLU_B200_ERR_NULL;
-  const int es = elem_size(dtype);
-  void* outs[3] = {h, dgate, dup};
-  const void* ins[3] = {dout, gate, up};
-  int width = 16;
-  for (int k = 0; k < 3; ++k) {
-    if (addr_of(outs[k]) % es || addr_of(ins[k]) % es) return SWIGLU_B200_ERR_ALIGN;
-    width = pow2_divisor(addr_of(outs[k]), width);
-    width = pow2_divisor(addr_of(ins[k]), width);
-  }
-  // An output may overwrite one input exactly; any other overlap (outputs with each other included) is an error.
-  bool aliased = false;
-  for (int a = 0; a < 3; ++a) {
-    const Extent ea = extent(outs[a], 1, n, n, es);
-    for (int b = a + 1; b < 3; ++b)
-      if (overlaps(ea, extent(outs[b], 1, n, n, es))) return SWIGLU_B200_ERR_ALIAS;
-    for (int b = 0; b < 3; ++b) {
-      if (outs[a] == ins[b]) aliased = true;
-      else if (overlaps(ea, extent(ins[b], 1, n, n, es))) return SWIGLU_B200_ERR_ALIAS;
-    }
-  }
-  DeviceScope scope(device);
-  if (scope.err != cudaSuccess) return fail_cuda(SWIGLU_B200_ERR_DEVICE, scope.err);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  switch (dtype) {
-    case SWIGLU_B200_F32: return recompute_by_width<float>(width, aliased, h, dgate, dup, dout, gate, up, n, gm, dm, st);
-    case SWIGLU_B200_F16: return recompute_by_width<__half>(width, aliased, h, dgate, dup, dout, gate, up, n, gm, dm, st);
-    default: return recompute_by_width<__nv_bfloat16>(width, aliased, h, dgate, dup, dout, gate, up, n, gm, dm, st);
-  }
+  return recompute_entry<ACT_SILU>(h, dgate, dup, dout, gate, up, n, dtype, gm, dm, device, stream);
+}
+
+int swiglu_b200_geglu_bwd_recompute(void* h, void* dgate, void* dup, const void* dout, const void* gate,
+                                    const void* up, int64_t n, int dtype, int approximate_tanh, int device,
+                                    void* stream) {
+  return approximate_tanh
+             ? recompute_entry<ACT_GELU_TANH>(h, dgate, dup, dout, gate, up, n, dtype, 1.0f, 1.0f, device, stream)
+             : recompute_entry<ACT_GELU_ERF>(h, dgate, dup, dout, gate, up, n, dtype, 1.0f, 1.0f, device, stream);
 }
 
 // Reports, without launching anything, how a forward / backward call with these addresses and strides

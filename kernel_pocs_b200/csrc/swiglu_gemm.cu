@@ -588,18 +588,37 @@ int swiglu_b200_geglu_gemm_fwd(void* h, void* gate_out, void* up_out, const void
                        device, stream, approximate_tanh ? ACT_GELU_TANH : ACT_GELU_ERF);
 }
 
-int swiglu_b200_lora_gemm_fwd(void* h, void* e_out, void* g_out, const void* x, const void* w_gate, const void* w_up,
-                              const void* xa_scaled, const void* b_gate, const void* b_up, int64_t m, int64_t n,
-                              int64_t k, int64_t r, float gm, float dm, void* status, int device, void* stream) {
+namespace {
+
+int lora_gemm_checked(void* h, void* e_out, void* g_out, const void* x, const void* w_gate, const void* w_up,
+                      const void* xa_scaled, const void* b_gate, const void* b_up, int64_t m, int64_t n, int64_t k,
+                      int64_t r, float gm, float dm, void* status, int device, void* stream, int act) {
   if (r < 0) return SWIGLU_B200_ERR_SHAPE;
   if (r == 0)
     return gemm_fwd_impl(h, e_out, g_out, x, w_gate, w_up, nullptr, nullptr, nullptr, m, n, k, 0, gm, dm, status,
-                         device, stream);
+                         device, stream, act);
   if (r > 64 || r % 8 != 0) return SWIGLU_B200_ERR_SHAPE;
   if (m > 0 && n > 0 && (!xa_scaled || !b_gate || !b_up)) return SWIGLU_B200_ERR_NULL;
   if (((uintptr_t)xa_scaled | (uintptr_t)b_gate | (uintptr_t)b_up) % 16) return SWIGLU_B200_ERR_ALIGN;
   return gemm_fwd_impl(h, e_out, g_out, x, w_gate, w_up, xa_scaled, b_gate, b_up, m, n, k, (int)r, gm, dm, status,
-                       device, stream);
+                       device, stream, act);
+}
+
+}  // namespace
+
+int swiglu_b200_lora_gemm_fwd(void* h, void* e_out, void* g_out, const void* x, const void* w_gate, const void* w_up,
+                              const void* xa_scaled, const void* b_gate, const void* b_up, int64_t m, int64_t n,
+                              int64_t k, int64_t r, float gm, float dm, void* status, int device, void* stream) {
+  return lora_gemm_checked(h, e_out, g_out, x, w_gate, w_up, xa_scaled, b_gate, b_up, m, n, k, r, gm, dm, status, device,
+                           stream, ACT_SILU);
+}
+
+int swiglu_b200_lora_geglu_gemm_fwd(void* h, void* e_out, void* g_out, const void* x, const void* w_gate,
+                                    const void* w_up, const void* xa_scaled, const void* b_gate, const void* b_up,
+                                    int64_t m, int64_t n, int64_t k, int64_t r, int approximate_tanh, void* status,
+                                    int device, void* stream) {
+  return lora_gemm_checked(h, e_out, g_out, x, w_gate, w_up, xa_scaled, b_gate, b_up, m, n, k, r, 1.0f, 1.0f, status,
+                           device, stream, approximate_tanh ? ACT_GELU_TANH : ACT_GELU_ERF);
 }
 
 

@@ -360,6 +360,17 @@ template <> struct Math<true, ACT_GELU_TANH> {
     const float dq = fmaf(x2, 3.0f * GeluConst::kQ3, GeluConst::kQ1);
     dgate = (dh * u) * (sig * fmaf(g * (1.0f - sig), dq, 1.0f));
   }
+  // fwd and bwd of one element off one exponential; each result is the expression above, bit for bit
+  static __device__ __forceinline__ void bwd_h(float dh, float g, float u, const Consts&, float& h, float& dgate,
+                                               float& dup) {
+    const float x2 = g * g;
+    const float qr = quarter_recip(g, x2);
+    const float sig = qr * 0.25f;
+    h = ((g * 0.25f) * qr) * u;
+    dup = dh * (g * sig);
+    const float dq = fmaf(x2, 3.0f * GeluConst::kQ3, GeluConst::kQ1);
+    dgate = (dh * u) * (sig * fmaf(g * (1.0f - sig), dq, 1.0f));
+  }
 };
 
 template <> struct Math<false, ACT_GELU_TANH> {
@@ -381,6 +392,11 @@ template <> struct Math<false, ACT_GELU_TANH> {
     const float dq = fmaf(x2, 3.0f * GeluConst::kQ3, GeluConst::kQ1);
     dgate = (dh * u) * (sig * fmaf(g * one_minus_sig, dq, 1.0f));
   }
+  static __device__ __forceinline__ void bwd_h(float dh, float g, float u, const Consts& c, float& h, float& dgate,
+                                               float& dup) {
+    h = fwd(g, u, c);  // same q, exp and quotient as bwd: the compiler shares them
+    bwd(dh, g, u, c, dgate, dup);
+  }
 };
 
 // Exact form, fp32 I/O: the accurate erfcf and expf.
@@ -390,6 +406,14 @@ template <> struct Math<false, ACT_GELU_ERF> {
   }
   static __device__ __forceinline__ void bwd(float dh, float g, float u, const Consts&, float& dgate, float& dup) {
     const float cdf = 0.5f * erfcf(-g * GeluConst::kInvSqrt2);
+    dup = dh * (g * cdf);
+    const float pdf = GeluConst::kInvSqrt2Pi * expf(-0.5f * g * g);
+    dgate = (dh * u) * fmaf(g, pdf, cdf);
+  }
+  static __device__ __forceinline__ void bwd_h(float dh, float g, float u, const Consts&, float& h, float& dgate,
+                                               float& dup) {
+    const float cdf = 0.5f * erfcf(-g * GeluConst::kInvSqrt2);
+    h = (g * cdf) * u;
     dup = dh * (g * cdf);
     const float pdf = GeluConst::kInvSqrt2Pi * expf(-0.5f * g * g);
     dgate = (dh * u) * fmaf(g, pdf, cdf);
@@ -428,6 +452,14 @@ template <> struct Math<true, ACT_GELU_ERF> {
   static __device__ __forceinline__ void bwd(float dh, float g, float u, const Consts&, float& dgate, float& dup) {
     float cdf, pdf;
     cdf_pdf(g, cdf, pdf);
+    dup = dh * (g * cdf);
+    dgate = (dh * u) * fmaf(g, pdf, cdf);
+  }
+  static __device__ __forceinline__ void bwd_h(float dh, float g, float u, const Consts&, float& h, float& dgate,
+                                               float& dup) {
+    float cdf, pdf;
+    cdf_pdf(g, cdf, pdf);
+    h = (g * cdf) * u;
     dup = dh * (g * cdf);
     dgate = (dh * u) * fmaf(g, pdf, cdf);
   }
@@ -728,7 +760,7 @@ swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const v
 // bytes, then `tail` scalar elements handled by the last CTA.
 // ---------------------------------------------------------------------------------------
 
-template <class T, int BYTES, bool FAST, int THREADS, int UNROLL, int LDM, int STM>
+template <class T, int BYTES, bool FAST, int THREADS, int UNROLL, int LDM, int STM, int ACT = ACT_SILU>
 __global__ void __launch_bounds__(THREADS)
 swiglu_bwd_recompute_kernel(void* h, void* dgate, void* dup, const void* dout, const void* gate, const void* up,
                             long long n_vec, int tail, float gm, float dm) {
@@ -759,7 +791,7 @@ swiglu_bwd_recompute_kernel(void* h, void* dgate, void* dup, const void* dout, c
         Codec<T>::template unpack<BYTES>(g[k], fg);
         Codec<T>::template unpack<BYTES>(u[k], fu);
 #pragma unroll
-        for (int e = 0; e < EPV; ++e) Math<FAST, ACT_SILU>::bwd_h(fd[e], fg[e], fu[e], c, fh[e], fdg[e], fdu[e]);
+        for (int e = 0; e < EPV; ++e) Math<FAST, ACT>::bwd_h(fd[e], fg[e], fu[e], c, fh[e], fdg[e], fdu[e]);
         Vec<BYTES> vh, vdg, vdu;
         Codec<T>::template pack<BYTES>(fh, vh);
         Codec<T>::template pack<BYTES>(fdg, vdg);
@@ -781,7 +813,7 @@ swiglu_bwd_recompute_kernel(void* h, void* dgate, void* dup, const void* dout, c
     Codec<T>::template unpack<ES>(vd, fd);
     Codec<T>::template unpack<ES>(vg, fg);
     Codec<T>::template unpack<ES>(vu, fu);
-    Math<FAST, ACT_SILU>::bwd_h(fd[0], fg[0], fu[0], c, fh[0], fdg[0], fdu[0]);
+    Math<FAST, ACT>::bwd_h(fd[0], fg[0], fu[0], c, fh[0], fdg[0], fdu[0]);
     Vec<ES> vh, vdg, vdu;
     Codec<T>::template pack<ES>(fh, vh);
     Codec<T>::template pack<ES>(fdg, vdg);

@@ -79,8 +79,9 @@ def gate_up_swiglu_forward(x, w_gate, w_up, gate_multiplier=1.0, down_multiplier
     return h
 
 
-def lora_gate_up_swiglu_forward(x, w_gate, w_up, A_gate, B_gate, s_gate, A_up, B_up, s_up, save_eg=False):
-    """``h = silu(e) * g`` with ``e = x W_g^T + s_g (x A_g^T) B_g^T`` and ``g`` likewise, in ONE tcgen05 launch
+def lora_gate_up_swiglu_forward(x, w_gate, w_up, A_gate, B_gate, s_gate, A_up, B_up, s_up, save_eg=False,
+                                activation: str = "silu"):
+    """``h = act(e) * g`` (``activation``: ``"silu"``, ``"gelu_tanh"`` or ``"gelu_exact"``) with ``e = x W_g^T + s_g (x A_g^T) B_g^T`` and ``g`` likewise, in ONE tcgen05 launch
     (``swiglu_b200_lora_gemm_fwd``): the adapter terms ride along as extra steps of the projections' contraction.
     The counterpart of the reference's ``fused_gate_up_swiglu`` (kernels/lora_mlp/experiments/v2/
     lora_mlp_kernel_v2.py:141-209).  W ``[n, k]``, A ``[r, k]``, B ``[n, r]``, all bf16; r a multiple of 8 up to 64.
@@ -106,14 +107,16 @@ def lora_gate_up_swiglu_forward(x, w_gate, w_up, A_gate, B_gate, s_gate, A_up, B
     h = torch.empty((m, n), dtype=x.dtype, device=x.device)
     e = torch.empty_like(h) if save_eg else None
     g = torch.empty_like(h) if save_eg else None
-    _lib.check(
-        "lora_gate_up_swiglu_forward",
-        _lib.lib.swiglu_b200_lora_gemm_fwd(
-            h.data_ptr(), e.data_ptr() if save_eg else None, g.data_ptr() if save_eg else None, x2.data_ptr(),
-            wg.data_ptr(), wu.data_ptr(), xa.data_ptr(), bg.data_ptr(), bu.data_ptr(), m, n, k, r, 1.0, 1.0,
-            _status(x.device).data_ptr(), x.device.index, torch.cuda.current_stream(x.device).cuda_stream,
-        ),
-    )
+    if activation not in ("silu", "gelu_tanh", "gelu_exact"):
+        raise ValueError(f"activation must be 'silu', 'gelu_tanh' or 'gelu_exact', got {activation!r}")
+    common = (h.data_ptr(), e.data_ptr() if save_eg else None, g.data_ptr() if save_eg else None, x2.data_ptr(),
+              wg.data_ptr(), wu.data_ptr(), xa.data_ptr(), bg.data_ptr(), bu.data_ptr(), m, n, k, r)
+    tail = (_status(x.device).data_ptr(), x.device.index, torch.cuda.current_stream(x.device).cuda_stream)
+    if activation == "silu":
+        rc = _lib.lib.swiglu_b200_lora_gemm_fwd(*common, 1.0, 1.0, *tail)
+    else:
+        rc = _lib.lib.swiglu_b200_lora_geglu_gemm_fwd(*common, int(activation == "gelu_tanh"), *tail)
+    _lib.check("lora_gate_up_swiglu_forward", rc)
     return h.view(*x.shape[:-1], n), e, g
 
 

@@ -94,6 +94,33 @@ def geglu_backward(dout: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, app
     return dgate.view(dout.shape), dup.view(dout.shape)
 
 
+def geglu_backward_recompute(dout: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, approximate: str = "tanh",
+                             preserve_inputs: bool = False):
+    """``(h, dgate, dup)`` from one pass over ``(dout, gate, up)``: ``geglu_backward`` together with the forward
+    output, for training steps that kept ``gate`` and ``up`` but not ``h``.  Unless ``preserve_inputs`` is set, ``h``
+    is written over ``dout``, ``dgate`` over ``gate`` and ``dup`` over ``up``.  No counterpart in the reference."""
+    _check_same_shape_inputs(gate, up)
+    _check_cuda_dtype(gate)
+    tanh = _check_approximate(approximate)
+    _require_cuda(gate, "gate")
+    if dout.dtype != gate.dtype or dout.device != gate.device or dout.shape != gate.shape:
+        raise ValueError("dout must have the shape, dtype and device of gate and up")
+    if preserve_inputs:
+        dout, gate, up = dout.contiguous(), gate.contiguous(), up.contiguous()
+        h, dgate, dup = torch.empty_like(dout), torch.empty_like(gate), torch.empty_like(up)
+    else:
+        if not (dout.is_contiguous() and gate.is_contiguous() and up.is_contiguous()):
+            raise ValueError("the in-place form needs contiguous dout, gate and up; pass preserve_inputs=True")
+        h, dgate, dup = dout, gate, up
+    _lib.check(
+        "geglu_backward_recompute",
+        _lib.lib.swiglu_b200_geglu_bwd_recompute(
+            h.data_ptr(), dgate.data_ptr(), dup.data_ptr(), dout.data_ptr(), gate.data_ptr(), up.data_ptr(),
+            gate.numel(), _DTYPE_CODE[gate.dtype], int(tanh), gate.device.index, _stream(gate.device)),
+    )
+    return h, dgate, dup
+
+
 def geglu_packed_forward(gate_up: torch.Tensor, approximate: str = "tanh"):
     _check_packed_input(gate_up)
     _check_cuda_dtype(gate_up)

@@ -134,51 +134,74 @@ def _one_launch_ok(X, W_gate, A_gate) -> bool:
     return r % 8 == 0 and 8 <= r <= 64 and k % 8 == 0 and n % 16 == 0
 
 
+ACTIVATIONS = ("silu", "gelu_tanh", "gelu_exact")
+
+
+def _approximate(activation: str) -> str:
+    return "tanh" if activation == "gelu_tanh" else "none"
+
+
 def _lora_mlp_forward(X, W_gate, A_gate, B_gate, s_gate, W_up, A_up, B_up, s_up, W_down, A_down, B_down, s_down,
-                      save_eg):
+                      save_eg, activation="silu"):
+    if activation not in ACTIVATIONS:
+        raise ValueError(f"activation must be one of {ACTIVATIONS}, got {activation!r}")
     x2 = X.reshape(-1, X.shape[-1])
     if _one_launch_ok(X, W_gate, A_gate):
-        # gate and up projections, both adapters and SwiGLU in one tcgen05 launch; e and g leave the chip only
-        # when a backward pass needs them
+        # gate and up projections, both adapters and the gated activation in one tcgen05 launch; e and g leave
+        # the chip only when a backward pass needs them
         from .fused_mlp import lora_gate_up_swiglu_forward
 
-        h, e, g = lora_gate_up_swiglu_forward(x2, W_gate, W_up, A_gate, B_gate, s_gate, A_up, B_up, s_up, save_eg)
+        h, e, g = lora_gate_up_swiglu_forward(x2, W_gate, W_up, A_gate, B_gate, s_gate, A_up, B_up, s_up, save_eg,
+                                              activation)
     else:
         e = x2 @ W_gate.t()
         g = x2 @ W_up.t()
-        if A_gate is not None:
+        if A_gate is not None and activation == "silu":
             h, e, g = fused_lora_swiglu_inplace(e, g, x2 @ A_gate.t(), x2 @ A_up.t(), B_gate, B_up, s_gate, s_up,
                                                 save_eg=save_eg)
         else:
-            h = swiglu_forward(e, g)[0]
+            if A_gate is not None:
+                e.addmm_(x2 @ A_gate.t(), B_gate.t(), alpha=s_gate)
+                g.addmm_(x2 @ A_up.t(), B_up.t(), alpha=s_up)
+            if activation == "silu":
+                h = swiglu_forward(e, g)[0]
+            else:
+                from .geglu import geglu_forward
+
+                h = geglu_forward(e, g, _approximate(activation))[0]
     out = h @ W_down.t()
     if A_down is not None:
         out.addmm_(h @ A_down.t(), B_down.t(), alpha=s_down)
     return out.view(*X.shape[:-1], out.shape[-1]), e, g
 
 
-def lora_mlp(X, W_gate, A_gate, B_gate, s_gate, W_up, A_up, B_up, s_up, W_down, A_down, B_down, s_down):
-    """LoRA MLP forward without autograd: ``down(silu(gate(X)) * up(X))``, every projection ``X W^T + s (X A^T) B^T``
+def lora_mlp(X, W_gate, A_gate, B_gate, s_gate, W_up, A_up, B_up, s_up, W_down, A_down, B_down, s_down,
+             activation: str = "silu"):
+    """LoRA MLP forward without autograd: ``down(act(gate(X)) * up(X))``, every projection ``X W^T + s (X A^T) B^T``
     with W ``[out, in]``, A ``[r, in]``, B ``[out, r]``.  Argument order of the reference's ``lora_mlp_v3``
-    (kernels/lora_mlp/experiments/v3/lora_mlp_kernel_v3.py:244-256); adapters may be ``None``."""
+    (kernels/lora_mlp/experiments/v3/lora_mlp_kernel_v3.py:244-256); adapters may be ``None``.  ``activation`` (not in
+    the reference, whose block is SiLU only): ``"silu"``, ``"gelu_tanh"`` or ``"gelu_exact"``."""
     with torch.no_grad():
         return _lora_mlp_forward(X, W_gate, A_gate, B_gate, s_gate, W_up, A_up, B_up, s_up, W_down, A_down, B_down,
-                                 s_down, save_eg=False)[0]
+                                 s_down, save_eg=False, activation=activation)[0]
 
 
 class LoRAMLP(torch.autograd.Function):
     """Trainable LoRA MLP: gradients for X and the six adapter matrices, base weights frozen.  Same ``apply``
-    arguments and gradient tuple as the reference's ``LoRAMLPv3`` (lora_mlp_kernel_v3.py:259-357).  The forward
+    arguments and gradient tuple as the reference's ``LoRAMLPv3`` (lora_mlp_kernel_v3.py:259-357), plus an optional
+    fourteenth argument ``activation`` (``"silu"``, ``"gelu_tanh"``, ``"gelu_exact"``) for Gemma-style blocks.  The forward
     keeps X and the adapter-corrected e, g (not h); the backward recomputes h and overwrites the saved e and g
     with their gradients, so a graph can be walked once."""
 
     @staticmethod
-    def forward(ctx, X, W_gate, A_gate, B_gate, s_gate, W_up, A_up, B_up, s_up, W_down, A_down, B_down, s_down):
+    def forward(ctx, X, W_gate, A_gate, B_gate, s_gate, W_up, A_up, B_up, s_up, W_down, A_down, B_down, s_down,
+                activation="silu"):
         out, e, g = _lora_mlp_forward(X, W_gate, A_gate, B_gate, s_gate, W_up, A_up, B_up, s_up, W_down, A_down,
-                                      B_down, s_down, save_eg=True)
+                                      B_down, s_down, save_eg=True, activation=activation)
         ctx.save_for_backward(X, e, g, A_gate, B_gate, A_up, B_up, A_down, B_down)
         ctx.base_weights = (W_gate, W_up, W_down)
         ctx.scales = (s_gate, s_up, s_down)
+        ctx.activation = activation
         return out
 
     @staticmethod
@@ -193,7 +216,12 @@ class LoRAMLP(torch.autograd.Function):
         dyB = dy @ B_down                                   # [M, r]
         dh = dy @ W_down
         dh.addmm_(dyB, A_down, alpha=s_down)
-        h, de, dg = swiglu_backward_recompute(dh, e, g)     # in place: dh <- h, e <- de, g <- dg
+        if ctx.activation == "silu":
+            h, de, dg = swiglu_backward_recompute(dh, e, g)  # in place: dh <- h, e <- de, g <- dg
+        else:
+            from .geglu import geglu_backward_recompute
+
+            h, de, dg = geglu_backward_recompute(dh, e, g, _approximate(ctx.activation))
         dA_down = s_down * (dyB.t() @ h)                    # [r, I]
         dB_down = s_down * (dy.t() @ (h @ A_down.t()))      # [H, r]
 
@@ -214,4 +242,5 @@ class LoRAMLP(torch.autograd.Function):
             dX.addmm_(dg, W_up)
         dX.addmm_(deB, A_gate, alpha=s_gate)
         dX.addmm_(dgB, A_up, alpha=s_up)
-        return (dX.view_as(X), None, dA_gate, dB_gate, None, None, dA_up, dB_up, None, None, dA_down, dB_down, None)
+        return (dX.view_as(X), None, dA_gate, dB_gate, None, None, dA_up, dB_up, None, None, dA_down, dB_down, None,
+                None)

@@ -16,7 +16,7 @@ when its three projections carry an active, unmerged LoRA adapter without dropou
 through ``swiglu`` / ``geglu`` while the wrapped projections compute their own adapter terms; any other module is left
 to the next kernel in the list.  PEFT itself is not needed: the wrappers are recognised by their attributes
 (``base_layer``, ``lora_A``, ``lora_B``, ``scaling``, ``lora_dropout``).  ``"lora_mlp_fused"`` (opt-in, not in the
-reference's final mapping) goes further for bias-free bf16 SiLU MLPs: the whole block runs through ``LoRAMLP`` of
+reference's final mapping) goes further for bias-free bf16 MLPs, SiLU or GELU: the whole block runs through ``LoRAMLP`` of
 ``lora_mlp`` (projections, adapters and SwiGLU in one tcgen05 launch; hand-written backward).
 
 One kernel is added that the reference does not have: ``"fused_gate_up"`` replaces the two projection GEMMs
@@ -175,7 +175,14 @@ def make_lora_mlp_forward(module) -> Callable:
 
 
 def make_lora_mlp_fused_forward(module) -> Callable:
-    if _activation_name(module) != "silu":
+    act = _activation_name(module)
+    if act == "silu":
+        activation = "silu"
+    elif act in GELU_TANH:
+        activation = "gelu_tanh"
+    elif act in GELU_EXACT:
+        activation = "gelu_exact"
+    else:
         raise SkipPatch
     for proj in (module.gate_proj, module.up_proj, module.down_proj):
         w, a, b, _, _ = _lora_parts(proj)
@@ -189,7 +196,7 @@ def make_lora_mlp_fused_forward(module) -> Callable:
         wg, ag, bg, sg, _ = _lora_parts(module.gate_proj)
         wu, au, bu, su, _ = _lora_parts(module.up_proj)
         wd, ad, bd, sd, _ = _lora_parts(module.down_proj)
-        return LoRAMLP.apply(x, wg, ag, bg, sg, wu, au, bu, su, wd, ad, bd, sd)
+        return LoRAMLP.apply(x, wg, ag, bg, sg, wu, au, bu, su, wd, ad, bd, sd, activation)
 
     return forward
 

@@ -303,3 +303,63 @@ def test_one_launch_projection_with_adapters(m, n, k, r, save_eg):
     h0, _, _ = lora_gate_up_swiglu_forward(x, wg, wu, ag, torch.zeros_like(bg), sg, au, torch.zeros_like(bu), su)
     check_status(x.device)
     assert torch.equal(h0, gate_up_swiglu_forward(x, wg, wu))
+
+
+# ------------------------------------------------------------------------------------------ GELU-gated blocks
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("approximate", ["tanh", "none"])
+@pytest.mark.parametrize("shape", [(7,), (3, 5, 257), (1000, 1101)])
+def test_geglu_recompute_equals_forward_and_backward(dtype, approximate, shape):
+    from kernel_pocs_b200.geglu import geglu_backward, geglu_backward_recompute, geglu_forward
+
+    dh, gate, up = rand3(shape, dtype, seed=41)
+    h_ref = geglu_forward(gate, up, approximate)[0]
+    dgate_ref, dup_ref = geglu_backward(dh, gate, up, approximate, preserve_inputs=True)
+    h, dgate, dup = geglu_backward_recompute(dh, gate, up, approximate, preserve_inputs=True)
+    for got, ref in ((h, h_ref), (dgate, dgate_ref), (dup, dup_ref)):
+        assert torch.equal(got.reshape(-1).view(torch.uint8), ref.reshape(-1).view(torch.uint8))
+    dh2, gate2, up2 = dh.clone(), gate.clone(), up.clone()
+    h2, dgate2, dup2 = geglu_backward_recompute(dh2, gate2, up2, approximate)
+    assert h2.data_ptr() == dh2.data_ptr() and dgate2.data_ptr() == gate2.data_ptr()
+    assert torch.equal(h2, h) and torch.equal(dgate2, dgate) and torch.equal(dup2, dup)
+
+
+def composite_act(X, p, activation):
+    proj = lambda x, n: x @ p[f"W_{n}"].t() + p[f"s_{n}"] * ((x @ p[f"A_{n}"].t()) @ p[f"B_{n}"].t())
+    e = proj(X, "gate")
+    act = torch.nn.functional.silu(e) if activation == "silu" else torch.nn.functional.gelu(
+        e, approximate="tanh" if activation == "gelu_tanh" else "none")
+    return proj(act * proj(X, "up"), "down")
+
+
+@pytest.mark.parametrize("activation", ["gelu_tanh", "gelu_exact"])
+@pytest.mark.parametrize("dtype,shape,rank", [(torch.float32, (2, 32, 128, 256), 8), (torch.bfloat16, (2, 256, 512, 1408), 16),
+                                              (torch.bfloat16, (1, 100, 128, 264), 12)])
+def test_mlp_with_gelu_gate_matches_composite(activation, dtype, shape, rank):
+    """LoRAMLP with the GELU gates of the Gemma family (no fused kernel for it exists in the reference) against the
+    PyTorch composite under autograd: fp32 tightly, bf16 within 3 % of each tensor's largest magnitude against the
+    fp32 composite of the same bf16 parameters."""
+    b, s, hidden, inter = shape
+    p = make_params(hidden, inter, rank, dtype)
+    g = torch.Generator(device=DEVICE).manual_seed(9)
+    X = torch.randn(b, s, hidden, generator=g, device=DEVICE).to(dtype)
+    dY = torch.randn(b, s, hidden, generator=g, device=DEVICE).to(dtype)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        p32 = {k: (v.float() if isinstance(v, torch.Tensor) else v) for k, v in p.items()}
+        out_ref, grads_ref = run_with_grads(lambda x, q: composite_act(x, q, activation), X.float(), p32, dY.float())
+        before = _lib.lib.swiglu_b200_gemm_launch_count()
+        out, grads = run_with_grads(lambda x, q: LoRAMLP.apply(*args_of(x, q), activation), X, p, dY)
+        check_status(X.device)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    one_launch = dtype == torch.bfloat16 and rank % 8 == 0 and inter % 16 == 0
+    assert _lib.lib.swiglu_b200_gemm_launch_count() == before + (1 if one_launch else 0)
+    bound = 1e-3 if dtype == torch.float32 else 3e-2
+    for name, a, r in zip(["out", "X"] + GRADS, [out] + grads, [out_ref] + grads_ref):
+        assert a.dtype == dtype and a.shape == r.shape, name
+        err = (a.float() - r).abs().max().item()
+        assert err <= bound * r.abs().max().item(), f"{name}: max err {err} against max |ref| {r.abs().max().item()}"
+    assert torch.equal(lora_mlp(*args_of(X, p), activation), out)

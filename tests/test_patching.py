@@ -151,6 +151,10 @@ def test_patch_validates_before_mutating():
     (lambda dtype, device, layers: wrap_mlps(tiny_qwen3(layers=layers)).to(device=device, dtype=dtype),
      ["lora_mlp_fused", "swiglu"], "lora_mlp_fused"),
     (lambda dtype, device, layers: wrap_mlps(tiny_gemma2(layers=layers)).to(device=device, dtype=dtype), None, "lora_mlp"),
+    (lambda dtype, device, layers: wrap_mlps(tiny_gemma2(layers=layers)).to(device=device, dtype=dtype),
+     ["lora_mlp_fused", "geglu"], "lora_mlp_fused"),
+    (lambda dtype, device, layers: wrap_mlps(tiny_gemma2(layers=layers, act="gelu")).to(device=device, dtype=dtype),
+     ["lora_mlp_fused", "geglu"], "lora_mlp_fused"),
 ])
 def test_patched_logits_and_gradients_match(make, kernels, expected):
     model = make(torch.bfloat16, "cuda", layers=3)
