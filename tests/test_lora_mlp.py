@@ -284,11 +284,11 @@ def test_one_launch_projection_with_adapters(m, n, k, r, save_eg):
     h, e, gg = lora_gate_up_swiglu_forward(x, wg, wu, ag, bg, sg, au, bu, su, save_eg=save_eg)
     check_status(x.device)
     assert _lib.lib.swiglu_b200_gemm_launch_count() == before + 1
-    # x A^T is a bf16 tensor on its way into the kernel (as it is in the reference, whose xa_gate / xa_up are
-    # bf16 matmul results), scaled in fp32 and rounded once more: the comparison starts from those values
+    # x (s A)^T is a bf16 tensor on its way into the kernel (as x A^T is in the reference, whose xa_gate / xa_up
+    # are bf16 matmul results): the comparison starts from those values
     xf = x.float()
-    xa_g = (sg * (x @ ag.t()).float()).bfloat16().float()
-    xa_u = (su * (x @ au.t()).float()).bfloat16().float()
+    xa_g = (x @ (ag * sg).t()).float()
+    xa_u = (x @ (au * su).t()).float()
     e_ref = xf @ wg.float().t() + xa_g @ bg.float().t()
     g_ref = xf @ wu.float().t() + xa_u @ bu.float().t()
     assert_close_bf16(h, torch.nn.functional.silu(e_ref) * g_ref, "h")
