@@ -174,3 +174,57 @@ def test_backward_gemms_match_fp32_reference(m, n, k, tile, monkeypatch):
     none_x, dwg2, dwu2 = F.gate_up_swiglu_backward_gemms(dgate, dup, x, wg, wu, need_dx=False)
     F.check_status(x.device)
     assert none_x is None and torch.equal(dwg2, dwg) and torch.equal(dwu2, dwu)
+
+
+def test_tensor_core_kernels_on_random_shapes():
+    """Forward projection (plain, with adapters, with a GELU gate) and both backward GEMMs on 48 seeded random
+    shapes: ragged row counts, widths that end inside a tile, contractions that end inside a K block, every rank
+    layout of the adapter steps, both backward tile widths."""
+    import os
+    import random
+
+    from kernel_pocs_b200.geglu import gate_up_geglu_forward
+
+    rng = random.Random(20240607)
+    g = torch.Generator(device=DEVICE).manual_seed(77)
+    mk = lambda *s, std=1.0: (std * torch.randn(*s, generator=g, device=DEVICE)).bfloat16()
+    saved = os.environ.get("SWIGLU_B200_GEMM_BWD_TILE")
+    try:
+        for case in range(48):
+            m = rng.choice([1, 7, 127, 128, 129, 255, 257, 300, 511, 777, 1024, 1500])
+            n = 16 * rng.randint(1, 75)
+            k = 16 * rng.randint(1, 50)
+            r = rng.choice([0, 8, 16, 24, 32, 40, 48, 56, 64])
+            what = f"case {case}: m={m} n={n} k={k} r={r}"
+            x, wg, wu = mk(m, k), mk(n, k, std=k ** -0.5), mk(n, k, std=k ** -0.5)
+            xf, wgf, wuf = x.float(), wg.float(), wu.float()
+            e_ref, u_ref = xf @ wgf.t(), xf @ wuf.t()
+            if r:
+                ag, au, bg, bu = mk(r, k, std=k ** -0.5), mk(r, k, std=k ** -0.5), mk(n, r, std=0.3), mk(n, r, std=0.3)
+                h, e, u = F.lora_gate_up_swiglu_forward(x, wg, wu, ag, bg, 2.0, au, bu, 0.5, save_eg=True)
+                e_ref = e_ref + (x @ (ag * 2.0).t()).float() @ bg.float().t()
+                u_ref = u_ref + (x @ (au * 0.5).t()).float() @ bu.float().t()
+            else:
+                h, e, u = F.gate_up_swiglu_forward(x, wg, wu, save_preactivations=True)
+            F.check_status(x.device)
+            assert_close_bf16(e, e_ref, what + " gate")
+            assert_close_bf16(u, u_ref, what + " up")
+            assert_close_bf16(h, torch.nn.functional.silu(e_ref) * u_ref, what + " h")
+            if case % 3 == 0:
+                approximate = "tanh" if case % 2 else "none"
+                hg = gate_up_geglu_forward(x, wg, wu, approximate)
+                F.check_status(x.device)
+                assert_close_bf16(hg, torch.nn.functional.gelu(xf @ wgf.t(), approximate=approximate) * (xf @ wuf.t()),
+                                  what + " geglu h")
+            dgate, dup = mk(m, n), mk(m, n)
+            os.environ["SWIGLU_B200_GEMM_BWD_TILE"] = ("256", "512")[case % 2]
+            dx, dwg, dwu = F.gate_up_swiglu_backward_gemms(dgate, dup, x, wg, wu)
+            F.check_status(x.device)
+            assert_close_bf16(dx, dgate.float() @ wgf + dup.float() @ wuf, what + " dx")
+            assert_close_bf16(dwg, dgate.float().t() @ xf, what + " dw_gate")
+            assert_close_bf16(dwu, dup.float().t() @ xf, what + " dw_up")
+    finally:
+        if saved is None:
+            os.environ.pop("SWIGLU_B200_GEMM_BWD_TILE", None)
+        else:
+            os.environ["SWIGLU_B200_GEMM_BWD_TILE"] = saved
