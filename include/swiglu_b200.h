@@ -119,6 +119,7 @@ SWIGLU_B200_API int swiglu_b200_geglu_bwd_recompute(void* h, void* dgate, void* 
  *   bits 0-7   access width of the body in bytes (16, 8, 4 or 2)
  *   bit  8     pitched-row addressing (a row stride differs from cols)
  *   bit  9     inputs skewed against the outputs: aligned loads + shuffle + funnel shift
+ *   bit  10    ... and every input is within 4 bytes of a boundary: one word from a neighbour completes a vector
  *   bits 16-23 scalar elements peeled in front of the body, bits 24-31 scalar elements in front and behind
  * and when < 0 the negated SWIGLU_B200_ERR_* code the real call would return for these arguments. */
 SWIGLU_B200_API int swiglu_b200_plan_fwd(const void* out, const void* gate, const void* up, int64_t rows, int64_t cols,

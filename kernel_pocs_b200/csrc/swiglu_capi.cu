@@ -31,6 +31,15 @@ using namespace swiglu_b200;
 #ifndef SWIGLU_SKEW_UNROLL
 #define SWIGLU_SKEW_UNROLL 2  // skewed-load kernels keep a second granule per vector in registers
 #endif
+#ifndef SWIGLU_SKEW_FWD_UNROLL
+#define SWIGLU_SKEW_FWD_UNROLL 3  // forward: two inputs, so a third tile row still fits 64 registers
+#endif
+#ifndef SWIGLU_SKEW1_FWD_UNROLL
+#define SWIGLU_SKEW1_FWD_UNROLL 4  // one-word variant (every skew within 4 bytes of a boundary)
+#endif
+#ifndef SWIGLU_SKEW1_BWD_UNROLL
+#define SWIGLU_SKEW1_BWD_UNROLL 3
+#endif
 #ifndef SWIGLU_LD_RO
 #define SWIGLU_LD_RO LD_NC_NOALLOC  // inputs that this launch never writes
 #endif
@@ -89,6 +98,8 @@ inline int pow2_divisor(unsigned long long v, int limit) {
 struct Plan {
   bool rows;   // 2-D addressing
   bool shift;  // flat, 16-byte body, some input skewed against the outputs (see ld_skewed)
+  bool one_word;  // ... and every skew is within 4 bytes of a boundary: one word of a neighbouring granule
+                  // completes a vector
   int bytes;   // access width of the body
   Shape shape;
   long long skip;  // bytes by which every base pointer is advanced (flat head)
@@ -124,9 +135,11 @@ Plan make_plan(const unsigned long long* out, int n_out, const unsigned long lon
       p.shape.head = (int)head;
       p.shape.edge = (int)(n - p.shape.n_vec * epv);
       p.skip = head * es;
+      p.one_word = true;
       for (int k = 0; k < n_in; ++k) {
         p.skew[k] = (int)((in[k] + (unsigned long long)p.skip) % kWide);
         p.shift = p.shift || p.skew[k] != 0;
+        p.one_word = p.one_word && (p.skew[k] <= 4 || p.skew[k] >= 12);
       }
     } else {
       const int epv = common / es;
@@ -150,10 +163,10 @@ Plan make_plan(const unsigned long long* out, int n_out, const unsigned long lon
 
 // ------------------------------------------------------------------ forward dispatch
 
-template <class T, int ACT, int BYTES, bool ROWS, bool SHIFT = false>
+template <class T, int ACT, int BYTES, bool ROWS, int SHIFT = 0>
 int launch_fwd(void* out, const void* gate, const void* up, const Shape& s, float gm, float dm, cudaStream_t st) {
   constexpr bool FAST = (sizeof(T) == 2);
-  constexpr int UNROLL = SHIFT ? SWIGLU_SKEW_UNROLL : SWIGLU_FWD_UNROLL;
+  constexpr int UNROLL = SHIFT == 4 ? SWIGLU_SKEW_FWD_UNROLL : SHIFT == 1 ? SWIGLU_SKEW1_FWD_UNROLL : SWIGLU_FWD_UNROLL;
   auto kernel =
       swiglu_fwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, UNROLL, SWIGLU_LD_RO, SWIGLU_ST, SHIFT, ACT>;
   const unsigned grid = grid_for(s.n_vec, SWIGLU_THREADS, UNROLL);
@@ -179,19 +192,21 @@ int fwd_by_width(int bytes, void* out, const void* gate, const void* up, const S
 
 template <class T, int ACT>
 int fwd_typed(const Plan& p, void* out, const void* gate, const void* up, float gm, float dm, cudaStream_t st) {
-  if (p.shift) return launch_fwd<T, ACT, 16, false, true>(out, gate, up, p.shape, gm, dm, st);
+  if (p.shift)
+    return p.one_word ? launch_fwd<T, ACT, 16, false, 1>(out, gate, up, p.shape, gm, dm, st)
+                      : launch_fwd<T, ACT, 16, false, 4>(out, gate, up, p.shape, gm, dm, st);
   return p.rows ? fwd_by_width<T, ACT, true>(p.bytes, out, gate, up, p.shape, gm, dm, st)
                 : fwd_by_width<T, ACT, false>(p.bytes, out, gate, up, p.shape, gm, dm, st);
 }
 
 // ------------------------------------------------------------------ backward dispatch
 
-template <class T, int ACT, int BYTES, bool ROWS, bool INPLACE, bool SHIFT = false>
+template <class T, int ACT, int BYTES, bool ROWS, bool INPLACE, int SHIFT = 0>
 int launch_bwd(void* dgate, void* dup, const void* dout, const void* gate, const void* up, const Shape& s, float gm,
                float dm, cudaStream_t st) {
   constexpr bool FAST = (sizeof(T) == 2);
   constexpr int LD_IO = INPLACE ? SWIGLU_LD_ALIASED : SWIGLU_LD_RO;
-  constexpr int UNROLL = SHIFT ? SWIGLU_SKEW_UNROLL : SWIGLU_BWD_UNROLL;
+  constexpr int UNROLL = SHIFT == 4 ? SWIGLU_SKEW_UNROLL : SHIFT == 1 ? SWIGLU_SKEW1_BWD_UNROLL : SWIGLU_BWD_UNROLL;
   auto kernel =
       swiglu_bwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, UNROLL, SWIGLU_LD_RO, LD_IO, SWIGLU_ST, SHIFT, ACT>;
   const unsigned grid = grid_for(s.n_vec, SWIGLU_THREADS, UNROLL);
@@ -219,8 +234,11 @@ template <class T, int ACT>
 int bwd_typed(const Plan& p, bool inplace, void* dgate, void* dup, const void* dout, const void* gate,
               const void* up, float gm, float dm, cudaStream_t st) {
   if (p.shift) {
-    return inplace ? launch_bwd<T, ACT, 16, false, true, true>(dgate, dup, dout, gate, up, p.shape, gm, dm, st)
-                   : launch_bwd<T, ACT, 16, false, false, true>(dgate, dup, dout, gate, up, p.shape, gm, dm, st);
+    if (p.one_word)
+      return inplace ? launch_bwd<T, ACT, 16, false, true, 1>(dgate, dup, dout, gate, up, p.shape, gm, dm, st)
+                     : launch_bwd<T, ACT, 16, false, false, 1>(dgate, dup, dout, gate, up, p.shape, gm, dm, st);
+    return inplace ? launch_bwd<T, ACT, 16, false, true, 4>(dgate, dup, dout, gate, up, p.shape, gm, dm, st)
+                   : launch_bwd<T, ACT, 16, false, false, 4>(dgate, dup, dout, gate, up, p.shape, gm, dm, st);
   }
   if (p.rows) {
     return inplace ? bwd_by_width<T, ACT, true, true>(p.bytes, dgate, dup, dout, gate, up, p.shape, gm, dm, st)
@@ -500,7 +518,8 @@ int swiglu_b200_geglu_bwd_recompute(void* h, void* dgate, void* dup, const void*
 
 // Reports, without launching anything, how a forward / backward call with these addresses and strides
 // would be executed: bits 0-7 the access width in bytes, bit 8 pitched-row addressing, bit 9 the
-// skewed-load kernel, bits 16-23 the scalar head elements, bits 24-31 head + tail scalar elements.
+// skewed-load kernel, bit 10 its one-word variant, bits 16-23 the scalar head elements, bits 24-31 head + tail
+// scalar elements.
 // Negative: the argument error the real call would return, negated.
 int swiglu_b200_plan_fwd(const void* out, const void* gate, const void* up, int64_t rows, int64_t cols,
                          int64_t in_row_stride, int64_t out_row_stride, int dtype) {
@@ -512,7 +531,7 @@ int swiglu_b200_plan_fwd(const void* out, const void* gate, const void* up, int6
   const unsigned long long ins[2] = {addr_of(gate), addr_of(up)};
   const long long pitch[2] = {in_row_stride, out_row_stride};
   const Plan p = make_plan(outs, 1, ins, 2, pitch, 2, rows, cols, es);
-  return p.bytes | (p.rows ? 1 << 8 : 0) | (p.shift ? 1 << 9 : 0) | (p.shape.head << 16) | (p.shape.edge << 24);
+  return p.bytes | (p.rows ? 1 << 8 : 0) | (p.shift ? 1 << 9 : 0) | (p.shift && p.one_word ? 1 << 10 : 0) | (p.shape.head << 16) | (p.shape.edge << 24);
 }
 
 int swiglu_b200_plan_bwd(const void* dgate, const void* dup, const void* dout, const void* gate, const void* up,
@@ -528,7 +547,7 @@ int swiglu_b200_plan_bwd(const void* dgate, const void* dup, const void* dout, c
   const unsigned long long ins[3] = {addr_of(dout), addr_of(gate), addr_of(up)};
   const long long pitch[3] = {in_row_stride, grad_row_stride, dout_row_stride};
   const Plan p = make_plan(outs, 2, ins, 3, pitch, 3, rows, cols, es);
-  return p.bytes | (p.rows ? 1 << 8 : 0) | (p.shift ? 1 << 9 : 0) | (p.shape.head << 16) | (p.shape.edge << 24);
+  return p.bytes | (p.rows ? 1 << 8 : 0) | (p.shift ? 1 << 9 : 0) | (p.shift && p.one_word ? 1 << 10 : 0) | (p.shape.head << 16) | (p.shape.edge << 24);
 }
 
 }  // extern "C"

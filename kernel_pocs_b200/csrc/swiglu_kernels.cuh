@@ -529,30 +529,55 @@ __device__ __forceinline__ Vec<16> funnel16(const Vec<16>& lo, const Vec<16>& hi
   return o;
 }
 
+// NW = how many 32-bit words of a NEIGHBOURING granule a vector needs besides its main granule: 4 in general
+// (main = the granule the vector starts in, the rest comes from the next one).  NW = 1 serves every input that
+// is at most 4 bytes off a boundary in EITHER direction (one element off, the common case): for a skew of
+// 1..4 bytes the main granule is the one the vector starts in and one word of the next completes it; for a
+// skew of 12..15 the main granule is the one the vector ends in and the last word of the previous one
+// completes it.  One word instead of four is cheaper in registers (the part a lane fetches for itself when it
+// has no neighbour), in shuffles, and leaves room for more loads in flight.
+//
 // Phase 1, with the other loads of the tile: `base` is the input's body pointer (misaligned by `skew`
-// bytes), `off` the byte offset of vector i in the outputs.  Loads the first granule of the vector
-// into `lo` and, for the lanes that cannot get it from a neighbour, the second into `own_hi`.
-template <int LDM>
+// bytes), `off` the byte offset of vector i in the outputs.  Loads the main granule into `lo` and, for the lanes
+// that cannot get the neighbouring word(s) from another lane, those into `own`.  `edge_lane`: lane 31 or the
+// last vector (it has no next lane), `first_lane`: lane 0 (it has no previous lane).
+template <int LDM, int NW>
 __device__ __forceinline__ void ld_skewed_issue(const void* base, long long off, int skew, bool active,
-                                                bool self_fetch, Vec<16>& lo, Vec<16>& own_hi) {
+                                                bool edge_lane, bool first_lane, Vec<16>& lo, Vec<4 * NW>& own) {
   lo = Vec<16>{};
-  own_hi = Vec<16>{};
-  const char* granule = cbyte(base) - skew + off;
-  if (active) {
+  own = Vec<4 * NW>{};
+  const char* granule = cbyte(base) - skew + off;  // the aligned granule the vector starts in
+  if (!active || skew == 0) {
+    if (active) lo = Ld<16, LDM>::ld(granule);
+    return;
+  }
+  if (NW == 1 && skew >= 12) {
+    lo = Ld<16, LDM>::ld(granule + 16);
+    if (first_lane) own = Ld<4 * NW, LDM>::ld(granule + 12);
+  } else {
     lo = Ld<16, LDM>::ld(granule);
-    if (skew != 0 && self_fetch) own_hi = Ld<16, LDM>::ld(granule + 16);
+    if (edge_lane) own = Ld<4 * NW, LDM>::ld(granule + 16);
   }
 }
 
 // Phase 2, after every load of the tile has been issued (a shuffle waits for its operand, so doing
 // this between the loads would serialise them).  All 32 lanes must call this together.
-__device__ __forceinline__ Vec<16> ld_skewed_finish(const Vec<16>& lo, const Vec<16>& own_hi, int skew,
-                                                    bool self_fetch) {
+template <int NW>
+__device__ __forceinline__ Vec<16> ld_skewed_finish(const Vec<16>& lo, const Vec<4 * NW>& own, int skew,
+                                                    bool edge_lane, bool first_lane) {
   if (skew == 0) return lo;  // uniform over the launch
-  Vec<16> hi;
+  if (NW == 1 && skew >= 12) {
+    Vec<16> prev{};
+    prev.w[3] = __shfl_up_sync(0xffffffffu, lo.w[3], 1);
+    if (first_lane) prev.w[3] = own.w[0];
+    return funnel16(prev, lo, skew);
+  }
+  Vec<16> hi{};
 #pragma unroll
-  for (int i = 0; i < 4; ++i) hi.w[i] = __shfl_down_sync(0xffffffffu, lo.w[i], 1);
-  if (self_fetch) hi = own_hi;
+  for (int i = 0; i < NW; ++i) {
+    hi.w[i] = __shfl_down_sync(0xffffffffu, lo.w[i], 1);
+    if (edge_lane) hi.w[i] = own.w[i];
+  }
   return funnel16(lo, hi, skew);
 }
 
@@ -585,7 +610,7 @@ struct Locator {
 // the tile, so each warp-wide access is one contiguous 512- or 1024-byte segment.
 // ---------------------------------------------------------------------------------------
 
-template <class T, int BYTES, bool FAST, bool ROWS, int THREADS, int UNROLL, int LDM, int STM, bool SHIFT = false,
+template <class T, int BYTES, bool FAST, bool ROWS, int THREADS, int UNROLL, int LDM, int STM, int SHIFT = 0,
           int ACT = ACT_SILU>
 __global__ void __launch_bounds__(THREADS)
 swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const void* __restrict__ up, Shape s,
@@ -599,18 +624,20 @@ swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const v
     const long long v0 = tile * TILE + threadIdx.x;
     const bool full = (tile + 1) * TILE <= s.n_vec;
     Vec<BYTES> g[UNROLL], u[UNROLL];
-    Vec<SHIFT ? 16 : 2> g2[SHIFT ? UNROLL : 1], u2[SHIFT ? UNROLL : 1];  // self-fetched second granules
+    constexpr int NW = SHIFT ? SHIFT : 1;  // words taken from the next granule (skewed loads only)
+    Vec<4 * NW> g2[SHIFT ? UNROLL : 1], u2[SHIFT ? UNROLL : 1];  // self-fetched starts of the second granules
     long long oo[UNROLL];
 #pragma unroll
     for (int k = 0; k < UNROLL; ++k) {
       const long long i = v0 + (long long)k * THREADS;
       if constexpr (SHIFT) {
         static_assert(!SHIFT || (BYTES == 16 && !ROWS), "skewed loads exist for flat 16-byte streams only");
+        static_assert(SHIFT == 0 || SHIFT == 1 || SHIFT == 4, "one word or the whole next granule");
         const bool active = full || i < s.n_vec;
-        const bool self_fetch = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec;
+        const bool edge_lane = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec, first_lane = (threadIdx.x & 31) == 0;
         oo[k] = i * BYTES;
-        ld_skewed_issue<LDM>(gate, oo[k], s.skew_gate, active, self_fetch, g[k], g2[k]);
-        ld_skewed_issue<LDM>(up, oo[k], s.skew_up, active, self_fetch, u[k], u2[k]);
+        ld_skewed_issue<LDM, NW>(gate, oo[k], s.skew_gate, active, edge_lane, first_lane, g[k], g2[k]);
+        ld_skewed_issue<LDM, NW>(up, oo[k], s.skew_up, active, edge_lane, first_lane, u[k], u2[k]);
       } else if (full || i < s.n_vec) {
         long long oi, og;
         Locator<ROWS, BYTES>::at(s, i, oi, oo[k], og);
@@ -622,9 +649,9 @@ swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const v
     for (int k = 0; k < UNROLL; ++k) {
       const long long i = v0 + (long long)k * THREADS;
       if constexpr (SHIFT) {
-        const bool self_fetch = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec;
-        g[k] = ld_skewed_finish(g[k], g2[k], s.skew_gate, self_fetch);
-        u[k] = ld_skewed_finish(u[k], u2[k], s.skew_up, self_fetch);
+        const bool edge_lane = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec, first_lane = (threadIdx.x & 31) == 0;
+        g[k] = ld_skewed_finish<NW>(g[k], g2[k], s.skew_gate, edge_lane, first_lane);
+        u[k] = ld_skewed_finish<NW>(u[k], u2[k], s.skew_up, edge_lane, first_lane);
       }
       if (full || i < s.n_vec) {
         float fg[EPV], fu[EPV], fh[EPV];
@@ -667,7 +694,7 @@ swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const v
 // ---------------------------------------------------------------------------------------
 
 template <class T, int BYTES, bool FAST, bool ROWS, int THREADS, int UNROLL, int LDM_DH, int LDM_IO, int STM,
-          bool SHIFT = false, int ACT = ACT_SILU>
+          int SHIFT = 0, int ACT = ACT_SILU>
 __global__ void __launch_bounds__(THREADS)
 swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const void* gate, const void* up, Shape s,
                   float gm, float dm) {
@@ -680,7 +707,8 @@ swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const v
     const long long v0 = tile * TILE + threadIdx.x;
     const bool full = (tile + 1) * TILE <= s.n_vec;
     Vec<BYTES> d[UNROLL], g[UNROLL], u[UNROLL];
-    Vec<SHIFT ? 16 : 2> d2[SHIFT ? UNROLL : 1], g2[SHIFT ? UNROLL : 1], u2[SHIFT ? UNROLL : 1];
+    constexpr int NW = SHIFT ? SHIFT : 1;
+    Vec<4 * NW> d2[SHIFT ? UNROLL : 1], g2[SHIFT ? UNROLL : 1], u2[SHIFT ? UNROLL : 1];
     long long og[UNROLL];
 #pragma unroll
     for (int k = 0; k < UNROLL; ++k) {
@@ -688,11 +716,11 @@ swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const v
       if constexpr (SHIFT) {
         static_assert(!SHIFT || (BYTES == 16 && !ROWS), "skewed loads exist for flat 16-byte streams only");
         const bool active = full || i < s.n_vec;
-        const bool self_fetch = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec;
+        const bool edge_lane = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec, first_lane = (threadIdx.x & 31) == 0;
         og[k] = i * BYTES;
-        ld_skewed_issue<LDM_DH>(dout, og[k], s.skew_dout, active, self_fetch, d[k], d2[k]);
-        ld_skewed_issue<LDM_IO>(gate, og[k], s.skew_gate, active, self_fetch, g[k], g2[k]);
-        ld_skewed_issue<LDM_IO>(up, og[k], s.skew_up, active, self_fetch, u[k], u2[k]);
+        ld_skewed_issue<LDM_DH, NW>(dout, og[k], s.skew_dout, active, edge_lane, first_lane, d[k], d2[k]);
+        ld_skewed_issue<LDM_IO, NW>(gate, og[k], s.skew_gate, active, edge_lane, first_lane, g[k], g2[k]);
+        ld_skewed_issue<LDM_IO, NW>(up, og[k], s.skew_up, active, edge_lane, first_lane, u[k], u2[k]);
       } else if (full || i < s.n_vec) {
         long long oi, oo;
         Locator<ROWS, BYTES>::at(s, i, oi, oo, og[k]);
@@ -707,10 +735,10 @@ swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const v
     for (int k = 0; k < UNROLL; ++k) {
       const long long i = v0 + (long long)k * THREADS;
       if constexpr (SHIFT) {
-        const bool self_fetch = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec;
-        d[k] = ld_skewed_finish(d[k], d2[k], s.skew_dout, self_fetch);
-        g[k] = ld_skewed_finish(g[k], g2[k], s.skew_gate, self_fetch);
-        u[k] = ld_skewed_finish(u[k], u2[k], s.skew_up, self_fetch);
+        const bool edge_lane = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec, first_lane = (threadIdx.x & 31) == 0;
+        d[k] = ld_skewed_finish<NW>(d[k], d2[k], s.skew_dout, edge_lane, first_lane);
+        g[k] = ld_skewed_finish<NW>(g[k], g2[k], s.skew_gate, edge_lane, first_lane);
+        u[k] = ld_skewed_finish<NW>(u[k], u2[k], s.skew_up, edge_lane, first_lane);
       }
       if (full || i < s.n_vec) {
         float fd[EPV], fg[EPV], fu[EPV], fdg[EPV], fdu[EPV];

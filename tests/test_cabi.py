@@ -156,6 +156,12 @@ def test_access_planning_without_a_device():
     # inputs skewed against an aligned output: skewed-load kernel, no head
     assert _plan(f(O, G + 2, U + 6, 4, 4096, 4096, 4096, BF)) == dict(bytes=16, rows=False, shift=True, head=0, edge=0)
     assert _plan(f(O, G + 4, U, 4, 4096, 4096, 4096, F32)) == dict(bytes=16, rows=False, shift=True, head=0, edge=0)
+    # ... its one-word variant (bit 10) when no input is more than 4 bytes off: one element of any dtype
+    assert f(O, G + 2, U + 6, 4, 4096, 4096, 4096, BF) & 0x400 == 0
+    assert f(O, G + 2, U + 2, 4, 4096, 4096, 4096, BF) & 0x400
+    assert f(O, G + 4, U, 4, 4096, 4096, 4096, F32) & 0x400
+    assert f(O, G, U, 4, 4096, 4096, 4096, BF) & 0x400 == 0     # aligned: no skewed loads at all
+    assert b(G, U, D + 2, G, U, 16, 512, 512, 512, 512, BF) & 0x400 and not b(G, U, D + 10, G, U, 16, 512, 512, 512, 512, BF) & 0x400
     # packed gate|up: pitched rows; even half-width keeps 16 bytes, an odd one drops to the element size
     assert _plan(f(O, G, G + 2 * 5504, 8, 5504, 11008, 5504, BF)) == dict(bytes=16, rows=True, shift=False, head=0, edge=0)
     assert _plan(f(O, G, G + 2 * 257, 3, 257, 514, 257, BF))["bytes"] == 2
