@@ -29,10 +29,10 @@ using namespace swiglu_b200;
 #define SWIGLU_BWD_UNROLL 2
 #endif
 #ifndef SWIGLU_SKEW_UNROLL
-#define SWIGLU_SKEW_UNROLL 2  // skewed-load kernels keep a second granule per vector in registers
+#define SWIGLU_SKEW_UNROLL 2  // skewed-load kernels keep words of a second granule per vector in registers
 #endif
 #ifndef SWIGLU_SKEW_FWD_UNROLL
-#define SWIGLU_SKEW_FWD_UNROLL 3  // forward: two inputs, so a third tile row still fits 64 registers
+#define SWIGLU_SKEW_FWD_UNROLL 4  // forward: two inputs, so the usual four tile rows still fit 64 registers
 #endif
 #ifndef SWIGLU_SKEW1_FWD_UNROLL
 #define SWIGLU_SKEW1_FWD_UNROLL 4  // one-word variant (every skew within 4 bytes of a boundary)
@@ -166,7 +166,7 @@ Plan make_plan(const unsigned long long* out, int n_out, const unsigned long lon
 template <class T, int ACT, int BYTES, bool ROWS, int SHIFT = 0>
 int launch_fwd(void* out, const void* gate, const void* up, const Shape& s, float gm, float dm, cudaStream_t st) {
   constexpr bool FAST = (sizeof(T) == 2);
-  constexpr int UNROLL = SHIFT == 4 ? SWIGLU_SKEW_FWD_UNROLL : SHIFT == 1 ? SWIGLU_SKEW1_FWD_UNROLL : SWIGLU_FWD_UNROLL;
+  constexpr int UNROLL = SHIFT == 2 ? SWIGLU_SKEW_FWD_UNROLL : SHIFT == 1 ? SWIGLU_SKEW1_FWD_UNROLL : SWIGLU_FWD_UNROLL;
   auto kernel =
       swiglu_fwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, UNROLL, SWIGLU_LD_RO, SWIGLU_ST, SHIFT, ACT>;
   const unsigned grid = grid_for(s.n_vec, SWIGLU_THREADS, UNROLL);
@@ -194,7 +194,7 @@ template <class T, int ACT>
 int fwd_typed(const Plan& p, void* out, const void* gate, const void* up, float gm, float dm, cudaStream_t st) {
   if (p.shift)
     return p.one_word ? launch_fwd<T, ACT, 16, false, 1>(out, gate, up, p.shape, gm, dm, st)
-                      : launch_fwd<T, ACT, 16, false, 4>(out, gate, up, p.shape, gm, dm, st);
+                      : launch_fwd<T, ACT, 16, false, 2>(out, gate, up, p.shape, gm, dm, st);
   return p.rows ? fwd_by_width<T, ACT, true>(p.bytes, out, gate, up, p.shape, gm, dm, st)
                 : fwd_by_width<T, ACT, false>(p.bytes, out, gate, up, p.shape, gm, dm, st);
 }
@@ -206,7 +206,7 @@ int launch_bwd(void* dgate, void* dup, const void* dout, const void* gate, const
                float dm, cudaStream_t st) {
   constexpr bool FAST = (sizeof(T) == 2);
   constexpr int LD_IO = INPLACE ? SWIGLU_LD_ALIASED : SWIGLU_LD_RO;
-  constexpr int UNROLL = SHIFT == 4 ? SWIGLU_SKEW_UNROLL : SHIFT == 1 ? SWIGLU_SKEW1_BWD_UNROLL : SWIGLU_BWD_UNROLL;
+  constexpr int UNROLL = SHIFT == 2 ? SWIGLU_SKEW_UNROLL : SHIFT == 1 ? SWIGLU_SKEW1_BWD_UNROLL : SWIGLU_BWD_UNROLL;
   auto kernel =
       swiglu_bwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, UNROLL, SWIGLU_LD_RO, LD_IO, SWIGLU_ST, SHIFT, ACT>;
   const unsigned grid = grid_for(s.n_vec, SWIGLU_THREADS, UNROLL);
@@ -237,8 +237,8 @@ int bwd_typed(const Plan& p, bool inplace, void* dgate, void* dup, const void* d
     if (p.one_word)
       return inplace ? launch_bwd<T, ACT, 16, false, true, 1>(dgate, dup, dout, gate, up, p.shape, gm, dm, st)
                      : launch_bwd<T, ACT, 16, false, false, 1>(dgate, dup, dout, gate, up, p.shape, gm, dm, st);
-    return inplace ? launch_bwd<T, ACT, 16, false, true, 4>(dgate, dup, dout, gate, up, p.shape, gm, dm, st)
-                   : launch_bwd<T, ACT, 16, false, false, 4>(dgate, dup, dout, gate, up, p.shape, gm, dm, st);
+    return inplace ? launch_bwd<T, ACT, 16, false, true, 2>(dgate, dup, dout, gate, up, p.shape, gm, dm, st)
+                   : launch_bwd<T, ACT, 16, false, false, 2>(dgate, dup, dout, gate, up, p.shape, gm, dm, st);
   }
   if (p.rows) {
     return inplace ? bwd_by_width<T, ACT, true, true>(p.bytes, dgate, dup, dout, gate, up, p.shape, gm, dm, st)

@@ -529,17 +529,16 @@ __device__ __forceinline__ Vec<16> funnel16(const Vec<16>& lo, const Vec<16>& hi
   return o;
 }
 
-// NW = how many 32-bit words of a NEIGHBOURING granule a vector needs besides its main granule: 4 in general
-// (main = the granule the vector starts in, the rest comes from the next one).  NW = 1 serves every input that
-// is at most 4 bytes off a boundary in EITHER direction (one element off, the common case): for a skew of
-// 1..4 bytes the main granule is the one the vector starts in and one word of the next completes it; for a
-// skew of 12..15 the main granule is the one the vector ends in and the last word of the previous one
-// completes it.  One word instead of four is cheaper in registers (the part a lane fetches for itself when it
-// has no neighbour), in shuffles, and leaves room for more loads in flight.
+// NW = how many 32-bit words of a NEIGHBOURING granule a vector takes besides its main granule.  The main
+// granule is the one the vector starts in when the skew is at most 8 bytes (the words come from the NEXT granule)
+// and the one it ends in otherwise (the words are the last ones of the PREVIOUS granule), so two words always
+// suffice (NW = 2).  NW = 1 serves launches whose inputs are all within 4 bytes of a boundary in either direction
+// (one element off, the common case).  Few words are cheap in registers (the part a lane fetches for itself
+// when it has no neighbour), in shuffles, and leave room for more loads in flight.
 //
 // Phase 1, with the other loads of the tile: `base` is the input's body pointer (misaligned by `skew`
 // bytes), `off` the byte offset of vector i in the outputs.  Loads the main granule into `lo` and, for the lanes
-// that cannot get the neighbouring word(s) from another lane, those into `own`.  `edge_lane`: lane 31 or the
+// that cannot get the neighbouring words from another lane, those into `own`.  `edge_lane`: lane 31 or the
 // last vector (it has no next lane), `first_lane`: lane 0 (it has no previous lane).
 template <int LDM, int NW>
 __device__ __forceinline__ void ld_skewed_issue(const void* base, long long off, int skew, bool active,
@@ -547,13 +546,12 @@ __device__ __forceinline__ void ld_skewed_issue(const void* base, long long off,
   lo = Vec<16>{};
   own = Vec<4 * NW>{};
   const char* granule = cbyte(base) - skew + off;  // the aligned granule the vector starts in
-  if (!active || skew == 0) {
-    if (active) lo = Ld<16, LDM>::ld(granule);
-    return;
-  }
-  if (NW == 1 && skew >= 12) {
+  if (!active) return;
+  if (skew == 0) {
+    lo = Ld<16, LDM>::ld(granule);
+  } else if (skew > 8) {
     lo = Ld<16, LDM>::ld(granule + 16);
-    if (first_lane) own = Ld<4 * NW, LDM>::ld(granule + 12);
+    if (first_lane) own = Ld<4 * NW, LDM>::ld(granule + 16 - 4 * NW);
   } else {
     lo = Ld<16, LDM>::ld(granule);
     if (edge_lane) own = Ld<4 * NW, LDM>::ld(granule + 16);
@@ -566,19 +564,21 @@ template <int NW>
 __device__ __forceinline__ Vec<16> ld_skewed_finish(const Vec<16>& lo, const Vec<4 * NW>& own, int skew,
                                                     bool edge_lane, bool first_lane) {
   if (skew == 0) return lo;  // uniform over the launch
-  if (NW == 1 && skew >= 12) {
-    Vec<16> prev{};
-    prev.w[3] = __shfl_up_sync(0xffffffffu, lo.w[3], 1);
-    if (first_lane) prev.w[3] = own.w[0];
-    return funnel16(prev, lo, skew);
+  Vec<16> other{};
+  if (skew > 8) {
+#pragma unroll
+    for (int i = 0; i < NW; ++i) {
+      other.w[4 - NW + i] = __shfl_up_sync(0xffffffffu, lo.w[4 - NW + i], 1);
+      if (first_lane) other.w[4 - NW + i] = own.w[i];
+    }
+    return funnel16(other, lo, skew);
   }
-  Vec<16> hi{};
 #pragma unroll
   for (int i = 0; i < NW; ++i) {
-    hi.w[i] = __shfl_down_sync(0xffffffffu, lo.w[i], 1);
-    if (edge_lane) hi.w[i] = own.w[i];
+    other.w[i] = __shfl_down_sync(0xffffffffu, lo.w[i], 1);
+    if (edge_lane) other.w[i] = own.w[i];
   }
-  return funnel16(lo, hi, skew);
+  return funnel16(lo, other, skew);
 }
 
 template <bool ROWS, int BYTES>
@@ -612,7 +612,7 @@ struct Locator {
 
 template <class T, int BYTES, bool FAST, bool ROWS, int THREADS, int UNROLL, int LDM, int STM, int SHIFT = 0,
           int ACT = ACT_SILU>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 2)  // two 512-thread CTAs per SM: at most 64 registers
 swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const void* __restrict__ up, Shape s,
                   float gm, float dm) {
   constexpr int EPV = BYTES / Codec<T>::kSize;
@@ -632,7 +632,7 @@ swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const v
       const long long i = v0 + (long long)k * THREADS;
       if constexpr (SHIFT) {
         static_assert(!SHIFT || (BYTES == 16 && !ROWS), "skewed loads exist for flat 16-byte streams only");
-        static_assert(SHIFT == 0 || SHIFT == 1 || SHIFT == 4, "one word or the whole next granule");
+        static_assert(SHIFT == 0 || SHIFT == 1 || SHIFT == 2, "one or two words of a neighbouring granule");
         const bool active = full || i < s.n_vec;
         const bool edge_lane = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec, first_lane = (threadIdx.x & 31) == 0;
         oo[k] = i * BYTES;
@@ -695,7 +695,7 @@ swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const v
 
 template <class T, int BYTES, bool FAST, bool ROWS, int THREADS, int UNROLL, int LDM_DH, int LDM_IO, int STM,
           int SHIFT = 0, int ACT = ACT_SILU>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 2)
 swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const void* gate, const void* up, Shape s,
                   float gm, float dm) {
   constexpr int EPV = BYTES / Codec<T>::kSize;
