@@ -16,6 +16,7 @@ Providers
     b200         this library, in-place backward (the operator's default)
     b200-safe    this library, preserve_inputs=True
     b200-packed  this library, packed gate|up layout
+    b200-perseq  this library, one call per sequence of the variable-length batch (c3 configurations only)
     torch-eager  the PyTorch composite (torch_swiglu_reference + autograd) on the same GPU
     geglu-tanh, geglu-erf   the sibling GeGLU operator of this library (in-place backward), same byte model
 
@@ -123,7 +124,7 @@ def run_case(name, args, device, rank, world):
             # before the timed kernels start
             if packed:
                 gate_up.copy_(gate_up0)
-            elif provider == "b200" or provider.startswith("geglu-"):
+            elif provider in ("b200", "b200-perseq") or provider.startswith("geglu-"):
                 gate.copy_(gate0)
                 up.copy_(up0)
             else:
@@ -168,6 +169,27 @@ def run_case(name, args, device, rank, world):
 
             def bwd():
                 swiglu_packed_backward(dh, gate_up, gate_up.shape, preserve_inputs=False)
+
+            def full():
+                fwd()
+                bwd()
+
+            setups = {m: restore for m in ("forward", "backward", "full")}
+        elif provider == "b200-perseq":
+            # one call per sequence of the variable-length batch (row slices of the packed token axis): what a
+            # caller that walks cu_seqlens does; the op is row-independent, so the results are those of one call
+            lens = W.varlen_lengths()
+            if sum(lens) != rows:
+                continue  # only the whole var-len batch (c3 and its variants, unsharded) has these boundaries
+            bounds = [(sum(lens[:i]), sum(lens[:i + 1])) for i in range(len(lens))]
+
+            def fwd():
+                for a, b in bounds:
+                    swiglu_forward(gate[a:b], up[a:b])
+
+            def bwd():
+                for a, b in bounds:
+                    swiglu_backward(dh[a:b], gate[a:b], up[a:b])
 
             def full():
                 fwd()
@@ -403,7 +425,7 @@ def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--configs", nargs="+", default=["c1", "c2", "c3", "c3-fp32", "c3+w11009", "c3+w11009-off1"])
     ap.add_argument("--providers", nargs="+", default=["b200", "b200-safe", "torch-eager"],
-                    choices=["b200", "b200-safe", "b200-packed", "torch-eager", "geglu-tanh", "geglu-erf"])
+                    choices=["b200", "b200-safe", "b200-packed", "b200-perseq", "torch-eager", "geglu-tanh", "geglu-erf"])
     ap.add_argument("--modes", nargs="+", default=["forward", "backward", "full"],
                     choices=["forward", "backward", "full"])
     ap.add_argument("--warmup", type=int, default=20)
