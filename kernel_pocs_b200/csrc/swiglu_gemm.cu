@@ -231,6 +231,8 @@ constexpr int STAGE_BYTES = 2 * TILE_BYTES;              // X tile + one weight 
 constexpr int ACC_BUFS = 2;
 constexpr int TMEM_COLS = 512;
 constexpr int BAND = 8;                                  // row-tiles (of 256 rows) per band
+constexpr int EPI_COLS = 16;  // accumulator columns an epilogue thread takes per TMEM wait (32: no faster, the
+                              // epilogue hides behind the next tile's MMAs either way)
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
 
@@ -368,35 +370,44 @@ swiglu_gemm_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __g
       const int row = m0 + (int)rank * BM + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)b * 256u;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        uint32_t g[16], u[16];
-        tmem_ld16(t_row + c, g);
-        tmem_ld16(t_row + BN + c, u);
+      for (int c = 0; c < BN; c += EPI_COLS) {
+        uint32_t g[EPI_COLS], u[EPI_COLS];
+        if constexpr (EPI_COLS == 32) {
+          tmem_ld32(t_row + c, g);
+          tmem_ld32(t_row + BN + c, u);
+        } else {
+          tmem_ld16(t_row + c, g);
+          tmem_ld16(t_row + BN + c, u);
+        }
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < p.m && n0 + c < p.n) {
-          uint32_t hv[8], gv[8], uv[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
-            const float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
-            __nv_bfloat162 hb = __floats2bfloat162_rn(Math<true, ACT>::fwd(g0, u0, cst), Math<true, ACT>::fwd(g1, u1, cst));
-            __nv_bfloat162 gb = __floats2bfloat162_rn(g0, g1);
-            __nv_bfloat162 ub = __floats2bfloat162_rn(u0, u1);
-            hv[j] = *reinterpret_cast<uint32_t*>(&hb);
-            gv[j] = *reinterpret_cast<uint32_t*>(&gb);
-            uv[j] = *reinterpret_cast<uint32_t*>(&ub);
-          }
-          const long long off = (long long)row * p.n + n0 + c;
-          uint4* dst = reinterpret_cast<uint4*>(p.h + off);
-          dst[0] = make_uint4(hv[0], hv[1], hv[2], hv[3]);
-          dst[1] = make_uint4(hv[4], hv[5], hv[6], hv[7]);
-          if (p.gate_out) {
-            uint4* dg = reinterpret_cast<uint4*>(p.gate_out + off);
-            dg[0] = make_uint4(gv[0], gv[1], gv[2], gv[3]);
-            dg[1] = make_uint4(gv[4], gv[5], gv[6], gv[7]);
-            uint4* du = reinterpret_cast<uint4*>(p.up_out + off);
-            du[0] = make_uint4(uv[0], uv[1], uv[2], uv[3]);
-            du[1] = make_uint4(uv[4], uv[5], uv[6], uv[7]);
+        for (int q = 0; q < EPI_COLS / 16; ++q) {
+          if (row < p.m && n0 + c + 16 * q < p.n) {  // n is a multiple of 16: a group of 16 columns is in or out
+            uint32_t hv[8], gv[8], uv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float g0 = __uint_as_float(g[16 * q + 2 * j]), g1 = __uint_as_float(g[16 * q + 2 * j + 1]);
+              const float u0 = __uint_as_float(u[16 * q + 2 * j]), u1 = __uint_as_float(u[16 * q + 2 * j + 1]);
+              __nv_bfloat162 hb =
+                  __floats2bfloat162_rn(Math<true, ACT>::fwd(g0, u0, cst), Math<true, ACT>::fwd(g1, u1, cst));
+              __nv_bfloat162 gb = __floats2bfloat162_rn(g0, g1);
+              __nv_bfloat162 ub = __floats2bfloat162_rn(u0, u1);
+              hv[j] = *reinterpret_cast<uint32_t*>(&hb);
+              gv[j] = *reinterpret_cast<uint32_t*>(&gb);
+              uv[j] = *reinterpret_cast<uint32_t*>(&ub);
+            }
+            const long long off = (long long)row * p.n + n0 + c + 16 * q;
+            uint4* dst = reinterpret_cast<uint4*>(p.h + off);
+            dst[0] = make_uint4(hv[0], hv[1], hv[2], hv[3]);
+            dst[1] = make_uint4(hv[4], hv[5], hv[6], hv[7]);
+            if (p.gate_out) {
+              uint4* dg = reinterpret_cast<uint4*>(p.gate_out + off);
+              dg[0] = make_uint4(gv[0], gv[1], gv[2], gv[3]);
+              dg[1] = make_uint4(gv[4], gv[5], gv[6], gv[7]);
+              uint4* du = reinterpret_cast<uint4*>(p.up_out + off);
+              du[0] = make_uint4(uv[0], uv[1], uv[2], uv[3]);
+              du[1] = make_uint4(uv[4], uv[5], uv[6], uv[7]);
+            }
           }
         }
       }
