@@ -15,28 +15,92 @@ import torch
 from . import _lib
 from .swiglu import _as_float, swiglu_backward
 
-_status_words: dict[int, torch.Tensor] = {}
+class _StatusRing:
+    """Status words of the tensor-core kernels of one device, checked without stalling the stream.
+
+    Every launch gets its own word out of a small ring (so launches that overlap on different streams do not
+    share one).  A kernel whose bounded waits gave up leaves a code there.  Each time the ring wraps around, all
+    of it is copied to pinned host memory, asynchronously on the stream current then, and a copy that has
+    completed is inspected at the next launch: a failure surfaces as a ``RuntimeError`` within two turns of
+    the ring, at the cost of one small copy per ``SLOTS`` launches and no synchronisation.  ``check_status``
+    synchronises and looks at once."""
+
+    SLOTS = 16
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.dev = torch.zeros(self.SLOTS, dtype=torch.int32, device=device)
+        self.words = [self.dev[i:i + 1] for i in range(self.SLOTS)]
+        self.host = torch.zeros(self.SLOTS, dtype=torch.int32).pin_memory()
+        self.pending = None  # event of the ring copy in flight
+        self.next = 0
+        self.used = False
+
+    @staticmethod
+    def _raise(code: int):
+        raise RuntimeError(f"a tensor-core kernel of swiglu_b200 reported a timed-out wait (code {code}); "
+                           "its output is incomplete")
+
+    def _collect(self, wait: bool):
+        ev = self.pending
+        if ev is None:
+            return
+        if wait:
+            ev.synchronize()
+        elif not ev.query():
+            return
+        self.pending = None
+        codes = [c for c in self.host.tolist() if c]
+        if codes:
+            self.dev.zero_()  # reported once
+            self._raise(codes[0])
+
+    def acquire(self) -> torch.Tensor:
+        """The word for the launch that is about to be made (a one-element view; the C entry zeroes it)."""
+        i = self.next
+        if i == 0 and self.used:
+            # the ring has gone round: look at the previous copy, then send the words of the last turn
+            self._collect(wait=True)
+            self.host.copy_(self.dev, non_blocking=True)
+            self.pending = torch.cuda.Event()
+            self.pending.record(torch.cuda.current_stream(self.device))
+        elif self.pending is not None:
+            self._collect(wait=False)
+        self.used = True
+        self.next = (i + 1) % self.SLOTS
+        return self.words[i]
+
+    def check(self):
+        torch.cuda.synchronize(self.device)
+        codes = [c for c in self.dev.tolist() if c]
+        self.dev.zero_()
+        self.pending = None
+        if codes:
+            self._raise(codes[0])
+
+
+_status_rings: dict[int, _StatusRing] = {}
 
 
 def _status(device: torch.device) -> torch.Tensor:
-    t = _status_words.get(device.index)
-    if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=device)
-        _status_words[device.index] = t
-    return t
+    ring = _status_rings.get(device.index)
+    if ring is None:
+        ring = _status_rings[device.index] = _StatusRing(device)
+    return ring.acquire()
 
 
 def check_status(device: torch.device | int | None = None) -> None:
-    """Synchronises ``device`` and raises if the last fused-GEMM launch on it gave up on an
-    internal wait (the kernel bounds every wait and reports instead of hanging)."""
-    dev = torch.device("cuda", torch.cuda.current_device() if device is None else torch.device(device).index or 0) \
-        if not isinstance(device, torch.device) else device
-    word = _status_words.get(dev.index)
-    if word is None:
-        return
-    code = int(word.item())  # synchronises
-    if code != 0:
-        raise RuntimeError(f"swiglu_b200_gemm_fwd reported a timed-out wait (code {code}); its output is incomplete")
+    """Synchronises ``device`` and raises if a tensor-core launch on it since the last check gave up on an
+    internal wait (the kernels bound every wait and report instead of hanging)."""
+    if isinstance(device, torch.device):
+        index = device.index if device.index is not None else torch.cuda.current_device()
+    elif device is None:
+        index = torch.cuda.current_device()
+    else:
+        index = torch.device(device).index or 0
+    ring = _status_rings.get(index)
+    if ring is not None:
+        ring.check()
 
 
 def _check_operands(x, w_gate, w_up):

@@ -228,3 +228,27 @@ def test_tensor_core_kernels_on_random_shapes():
             os.environ.pop("SWIGLU_B200_GEMM_BWD_TILE", None)
         else:
             os.environ["SWIGLU_B200_GEMM_BWD_TILE"] = saved
+
+
+def test_status_ring_reports_a_failed_launch_without_synchronising():
+    """A kernel that gives up on a wait leaves a code in its status word.  Made on the host here (the word is
+    filled by hand after a good launch; no kernel is made to fail): the code must surface as a RuntimeError at
+    one of the next launches, once, and an explicit check afterwards must be clean."""
+    x, wg, wu = make(256, 128, 64)
+    F.gate_up_swiglu_forward(x, wg, wu)
+    F.check_status(x.device)
+    word = F._status(x.device)           # the word the next launch would get
+    word.fill_(321)
+    with pytest.raises(RuntimeError, match="code 321"):
+        for _ in range(2 * F._StatusRing.SLOTS):
+            F.gate_up_swiglu_forward(x, wg, wu)
+            torch.cuda.synchronize()
+    F.check_status(x.device)
+    h = F.gate_up_swiglu_forward(x, wg, wu)
+    F.check_status(x.device)
+    assert bool(torch.isfinite(h).all())
+    # the explicit check sees a code at once
+    F._status(x.device).fill_(77)
+    with pytest.raises(RuntimeError, match="code 77"):
+        F.check_status(x.device)
+    F.check_status(x.device)
