@@ -10,6 +10,8 @@ dw_up (``SWIGLU_B200_GEMM_BWD=cublas`` selects PyTorch matmuls instead, for comp
 """
 from __future__ import annotations
 
+import threading
+
 import torch
 
 from . import _lib
@@ -35,6 +37,7 @@ class _StatusRing:
         self.pending = None  # event of the ring copy in flight
         self.next = 0
         self.used = False
+        self.lock = threading.Lock()  # forward (caller's thread) and backward (autograd's thread) both launch
 
     @staticmethod
     def _raise(code: int):
@@ -57,6 +60,10 @@ class _StatusRing:
 
     def acquire(self) -> torch.Tensor:
         """The word for the launch that is about to be made (a one-element view; the C entry zeroes it)."""
+        with self.lock:
+            return self._acquire_locked()
+
+    def _acquire_locked(self) -> torch.Tensor:
         i = self.next
         if i == 0 and self.used:
             # the ring has gone round: look at the previous copy, then send the words of the last turn
@@ -71,10 +78,11 @@ class _StatusRing:
         return self.words[i]
 
     def check(self):
-        torch.cuda.synchronize(self.device)
-        codes = [c for c in self.dev.tolist() if c]
-        self.dev.zero_()
-        self.pending = None
+        with self.lock:
+            torch.cuda.synchronize(self.device)
+            codes = [c for c in self.dev.tolist() if c]
+            self.dev.zero_()
+            self.pending = None
         if codes:
             self._raise(codes[0])
 
