@@ -38,12 +38,19 @@ DTYPE_NAME = {torch.float32: "fp32", torch.float16: "fp16", torch.bfloat16: "bf1
 METRIC = "swiglu_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this GPU pool, used when MEASURED_PEAKS.json is absent
-# dram__bytes_read.sum + dram__bytes_write.sum of one backward launch on the c2 workload: the ncu
-# capture of the first 8192 of its 32768 token rows (profiles/swiglu_fwd_bwd_c2_8192rows_ncu_full.md:
-# 704.66 MB read + 413.66 MB written) scaled by 4; the traffic of this pure stream grows in proportion
-# to the rows.  Reads equal the algorithmic reads exactly; writes are short by what L2 still holds
-# when the kernel ends.
-BWD_DRAM_TRAFFIC_BYTES_C2 = 4 * (704_655_872 + 413_662_464)
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE in-place bf16 backward launch over 8192 token
+# rows of width 14336 (an ncu capture of the first quarter of the c2 workload: 704.66 MB read,
+# 413.66 MB written).  The kernel is a pure stream, so its traffic grows in proportion to the
+# elements it processes: `roofline.traffic` is this figure scaled by elements and element size.
+# Reads equal the algorithmic reads exactly; writes are short by what L2 still holds when the
+# kernel ends.
+BWD_DRAM_TRAFFIC_CAPTURE = {"bytes": 704_655_872 + 413_662_464, "elements": 8192 * 14336, "itemsize": 2}
+
+
+def scaled_bwd_traffic(w, tokens: int) -> int:
+    c = BWD_DRAM_TRAFFIC_CAPTURE
+    itemsize = torch.empty((), dtype=w.dtype).element_size()
+    return round(c["bytes"] * (tokens * w.width / c["elements"]) * (itemsize / c["itemsize"]))
 
 
 def parse_args():
@@ -58,6 +65,8 @@ def parse_args():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="time limit of the cpu_baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-strong-c5", action="store_true", help="skip the strong-scaling sub-record")
+    ap.add_argument("--c5-steps", type=int, default=10)
     return ap.parse_args()
 
 
@@ -171,20 +180,54 @@ def cpu_sample_rows(w) -> int:
     return min(w.tokens, rows)
 
 
+def host_threads() -> int:
+    """Host cores this process may use.  torch.distributed.run exports OMP_NUM_THREADS=1 to its
+    workers; the CPU arm undoes that for itself, since it is the only work on the host."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_step_fn():
+    """(kind, step) for the CPU arm.  ``step(gate, up, dh)`` runs one forward + backward on host
+    tensors: through the reference's own ``swiglu()`` when the unmodified copy of its module is
+    present under baseline/_ref ("reference"), else through the restatement of that same CPU
+    path in oracle/ ("port").  Both evaluate the ATen composite and its autograd backward."""
+    try:
+        from benchmarks import fetch_reference
+
+        ref = fetch_reference.load()
+
+        def step(gate, up, dh):
+            g = gate.detach().clone().requires_grad_(True)
+            u = up.detach().clone().requires_grad_(True)
+            h = ref.swiglu(g, u)  # host tensors: kernels/swiglu/swiglu.py:396-397 -> torch_swiglu_reference
+            dgate, dup = torch.autograd.grad(h, (g, u), dh)
+            return h.detach(), dgate, dup
+
+        return "reference", step
+    except Exception:
+        from oracle import oracle as O
+
+        return "port", O.aten_fwd_bwd
+
+
 def time_cpu_path(w, limit_s: float, min_steps: int = 3, fixed_steps: int | None = None, warmup: int = 1):
     """tokens/s of fwd+bwd on the host for a row sample of workload ``w``."""
     from kernel_pocs_b200 import workloads as W
-    from oracle import oracle as O
 
+    torch.set_num_threads(host_threads())
+    kind, step = cpu_step_fn()
     rows = cpu_sample_rows(w)
     gate, up, dh = W.generate_rows(w, 0, rows, "cpu")
     for _ in range(warmup):
-        O.aten_fwd_bwd(gate, up, dh)
+        step(gate, up, dh)
     times = []
     t_begin = time.perf_counter()
     while True:
         t0 = time.perf_counter()
-        O.aten_fwd_bwd(gate, up, dh)
+        step(gate, up, dh)
         times.append(time.perf_counter() - t0)
         if fixed_steps is not None:
             if len(times) >= fixed_steps:
@@ -192,14 +235,17 @@ def time_cpu_path(w, limit_s: float, min_steps: int = 3, fixed_steps: int | None
         elif len(times) >= min_steps and time.perf_counter() - t_begin > limit_s:
             break
     sec = sum(times) / len(times)
+    how = ("the reference's own swiglu() on host tensors + autograd" if kind == "reference"
+           else "the ATen composite + autograd as the reference's swiglu() evaluates them for host tensors")
     return {
         "value": rows / sec,
         "unit": UNIT,
         "cores": torch.get_num_threads(),
         "host_cpus": os.cpu_count(),
-        "kind": "port",
+        "kind": kind,
         "sample": f"first {rows} of {w.tokens} token rows of {w.name} ({w.width} wide, {DTYPE_NAME[w.dtype]}), "
-                  f"{len(times)} steps of fwd+bwd by the ATen composite + autograd, mean {sec * 1e3:.1f} ms/step",
+                  f"{len(times)} steps of fwd+bwd by {how}, mean {sec * 1e3:.1f} ms/step",
+        "sample_rows": rows,
         "ms_per_step_sample": sec * 1e3,
         "steps": len(times),
     }
@@ -209,20 +255,23 @@ def run_reference_arm(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    world = max(1, int(os.environ.get("WORLD_SIZE", "1")), args.gpus)
     res = time_cpu_path(w, 0.0, fixed_steps=args.steps, warmup=max(args.warmup, 1))
-    rows = cpu_sample_rows(w)
+    rows = res["sample_rows"]
     line = {
         "impl": "reference",
         "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": res["ms_per_step_sample"] * (w.tokens / rows),
+        "warmup": args.warmup, "ms_per_step": res["ms_per_step_sample"],
+        "ms_per_step_full_workload_extrapolated": res["ms_per_step_sample"] * (w.tokens * world / rows),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": DTYPE_NAME[w.dtype], "data": "synthetic",
-        "config": config_of(w, args, 1),
+        "config": config_of(w, args, world),
         "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-        "note": "CPU path of the reference (its PyTorch composite + autograd) on this host; ms_per_step is the "
-                "sample time scaled to the full workload",
+        "note": "CPU path of the reference (its PyTorch composite + autograd) on this host, all host threads, "
+                f"rank 0 only; one step = fwd+bwd over a {rows}-row sample of the workload and ms_per_step is the "
+                "measured time of that step; tokens/s = sample rows / that time",
     }
     print(json.dumps(line), flush=True)
 
@@ -237,6 +286,188 @@ def config_of(w, args, world):
         "l2": "inputs >> L2 (2.8 GB forward, 4.7 GB backward per step vs 126 MB); between timed steps, untimed: gate/up "
               "restored from pristine copies, then one read-only pass over dh evicts the copies' dirty lines"
               if w.name != "c1" else "fits L2 (parity case, launch-bound)",
+    }
+
+
+# ---------------------------------------------------------------------------------------------
+# host placement and the copy ceiling of the end-to-end leg
+# ---------------------------------------------------------------------------------------------
+
+def gpu_pci_address(index: int) -> str | None:
+    """PCI address "dddd:bb:dd.f" of the visible device ``index`` (NVML first, torch's device
+    properties otherwise)."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(ClockSampler._physical_index(index))
+        bus_id = pynvml.nvmlDeviceGetPciInfo(h).busId
+        bus_id = bus_id.decode() if isinstance(bus_id, bytes) else bus_id
+        return bus_id.lower()[-12:]  # NVML pads the domain to eight digits
+    except Exception:
+        pass
+    try:
+        p_ = torch.cuda.get_device_properties(index)
+        return f"{p_.pci_domain_id:04x}:{p_.pci_bus_id:02x}:{p_.pci_device_id:02x}.0"
+    except Exception:
+        return None
+
+
+def bind_host_near_gpu(index: int) -> dict:
+    """Pins this process to the CPUs of the NUMA node its GPU hangs off, BEFORE any pinned buffer
+    is allocated, so that the staging memory of the end-to-end leg is local to the GPU's PCIe
+    root.  Host side only (scheduler affinity of this process); nothing on the GPU changes.
+    Returns what it found for the JSON line."""
+    info = {"pci": gpu_pci_address(index), "numa_node": None, "cpus_bound": None}
+    if info["pci"] is None:
+        return info
+    try:
+        node = int((Path("/sys/bus/pci/devices") / info["pci"] / "numa_node").read_text().strip())
+    except Exception:
+        return info
+    info["numa_node"] = node
+    if node < 0:  # the platform reports no affinity (one node, or a virtual machine)
+        return info
+    try:
+        cpus = set()
+        for part in Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            info["cpus_bound"] = len(allowed)
+    except Exception:
+        pass
+    return info
+
+
+def copy_ceiling_ms(pinned_in, pinned_out, device, chunk_bytes: int, steps: int, barrier):
+    """What the host link allows for one end-to-end step with no kernel at all: the step's input
+    bytes host-to-device on one stream and its output bytes device-to-host on another, at the same
+    time, one plain asynchronous copy per chunk, every rank at once.  Returns ms per step."""
+    staging_in = torch.empty(chunk_bytes, dtype=torch.uint8, device=device)
+    staging_out = torch.empty(chunk_bytes, dtype=torch.uint8, device=device)
+    s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    flat_in = [t.view(-1).view(torch.uint8) for t in pinned_in]
+    flat_out = [t.view(-1).view(torch.uint8) for t in pinned_out]
+
+    def one_step():
+        with torch.cuda.stream(s_in):
+            for t in flat_in:
+                for off in range(0, t.numel(), chunk_bytes):
+                    n = min(chunk_bytes, t.numel() - off)
+                    staging_in[:n].copy_(t[off:off + n], non_blocking=True)
+        with torch.cuda.stream(s_out):
+            for t in flat_out:
+                for off in range(0, t.numel(), chunk_bytes):
+                    n = min(chunk_bytes, t.numel() - off)
+                    t[off:off + n].copy_(staging_out[:n], non_blocking=True)
+
+    one_step()
+    barrier()
+    cur = torch.cuda.current_stream(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(cur)
+    s_in.wait_stream(cur)
+    s_out.wait_stream(cur)
+    for _ in range(steps):
+        one_step()
+    cur.wait_stream(s_in)
+    cur.wait_stream(s_out)
+    e1.record(cur)
+    barrier()
+    return e0.elapsed_time(e1) / steps
+
+
+# ---------------------------------------------------------------------------------------------
+# strong scaling of the Llama-3-70B activation shape (rows split over the ranks, no collective)
+# ---------------------------------------------------------------------------------------------
+
+def weighted_hash(t: torch.Tensor) -> int:
+    """Order-sensitive integer hash of a tensor's bit patterns (exact: integer arithmetic)."""
+    bits = t.contiguous().view(torch.int16 if t.element_size() == 2 else torch.int32).reshape(-1).to(torch.int64)
+    weights = torch.arange(bits.numel(), device=t.device, dtype=torch.int64) % 65521 + 1
+    return int((bits * weights).sum().item())
+
+
+def run_strong_c5(W, swiglu_forward, swiglu_backward, launch_count, device, rank, world, dist, barrier, steps):
+    """[65536, 28672] bf16, seed 4, split by contiguous token rows over the ranks.  Aggregate
+    tokens/s = all tokens / max over ranks of the mean step time; per-GPU GB/s from each rank's
+    own time; a checksum of every output bit over all ranks (identical at every rank count exactly
+    when the results are); and a cross-check that the first rows of the next rank's block,
+    generated and computed here, hash like that rank's own."""
+    w = W.workloads()["c5"]
+    lo, hi = W.row_shard(w.tokens, world, rank)
+    gate0, up0, dh = W.generate_rows(w, lo, hi, device)
+    gate, up = gate0.clone(), up0.clone()
+
+    def restore():
+        gate.copy_(gate0)
+        up.copy_(up0)
+        dh.sum()
+
+    def step():
+        h, g2, u2 = swiglu_forward(gate, up)
+        dgate, dup = swiglu_backward(dh, g2, u2)  # in place over gate/up, the operator's default
+        return h, dgate, dup
+
+    for _ in range(3):
+        restore()
+        step()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    barrier()
+    launches0 = launch_count()
+    for a, b in evs:
+        restore()
+        a.record()
+        h, dgate, dup = step()
+        b.record()
+    barrier()
+    launches = launch_count() - launches0
+    mine_ms = sum(a.elapsed_time(b) for a, b in evs) / steps
+    probe = min(64, hi - lo)
+    own_hash = [weighted_hash(t[:probe]) for t in (h, dgate, dup)]
+    checksum = [int(t.view(torch.int16).sum(dtype=torch.int64).item()) for t in (h, dgate, dup)]
+    del h, dgate, dup, gate, up, gate0, up0, dh
+    torch.cuda.empty_cache()
+
+    # the first rows of the NEXT rank's block, generated and computed on this device
+    nlo, nhi = W.row_shard(w.tokens, world, (rank + 1) % world)
+    nprobe = min(64, nhi - nlo)
+    ng, nu, nd = W.generate_rows(w, nlo, nlo + nprobe, device)
+    nh, ng2, nu2 = swiglu_forward(ng, nu)
+    ndg, ndu = swiglu_backward(nd, ng2, nu2)
+    neighbour_hash = [weighted_hash(t) for t in (nh, ndg, ndu)]
+
+    # hashes do not fit a double exactly: gather them as int64 beside the timings
+    ints = torch.tensor([*own_hash, *neighbour_hash, *checksum], dtype=torch.int64, device=device)
+    if world > 1:
+        all_ms = [torch.zeros(1, dtype=torch.float64, device=device) for _ in range(world)]
+        dist.all_gather(all_ms, torch.tensor([mine_ms], dtype=torch.float64, device=device))
+        all_ints = [torch.zeros_like(ints) for _ in range(world)]
+        dist.all_gather(all_ints, ints)
+        all_ms = [float(t.item()) for t in all_ms]
+        all_ints = [t.tolist() for t in all_ints]
+    else:
+        all_ms, all_ints = [mine_ms], [ints.tolist()]
+    if rank != 0:
+        return None
+    shards = [W.row_shard(w.tokens, world, r) for r in range(world)]
+    bytes_per_row = 8 * w.width * 2
+    cross_ok = all(all_ints[r][3:6] == all_ints[(r + 1) % world][0:3] for r in range(world))
+    total = [sum(all_ints[r][6 + i] for r in range(world)) for i in range(3)]
+    worst = max(all_ms)
+    return {
+        "workload": f"c5: {w.note}; gate/up/dh bf16 [{w.tokens}, {w.width}] in total, N(0,1), seed {w.seed}, "
+                    f"contiguous token rows split over {world} GPU(s), no collective",
+        "scaling": "strong", "n_gpus": world, "steps": steps, "tokens_total": w.tokens,
+        "ms_per_step": worst, "value": w.tokens / (worst * 1e-3), "unit": UNIT,
+        "ms_per_step_by_rank": all_ms,
+        "hbm_gbs_per_gpu": [(b - a) * bytes_per_row / (ms * 1e-3) / 1e9 for (a, b), ms in zip(shards, all_ms)],
+        "gpu_launches_rank0": launches,
+        "output_checksum_h_dgate_dup": total,
+        "next_rank_block_reproduced_bit_exactly": cross_ok,
     }
 
 
@@ -271,6 +502,8 @@ def main():
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    affinity0 = os.sched_getaffinity(0)
+    placement = bind_host_near_gpu(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
         dist.barrier()
@@ -379,16 +612,43 @@ def main():
         for got, want in zip(outs, (h_dev, dgate_dev, dup_dev)):
             if not torch.equal(got[:64], want[:64].cpu()) or not torch.equal(got[-64:], want[-64:].cpu()):
                 raise SystemExit("e2e: the bytes copied back to the host differ from the device result")
+        # the ceiling: the same bytes over the same link with no kernel in between, every rank at once
+        ceil_ms = copy_ceiling_ms((hg, hu, hd), outs, device, 32 << 20, args.e2e_steps, barrier)
+        tc = torch.tensor([ceil_ms], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(tc, op=dist.ReduceOp.MAX)
+        ceil_ms = tc.item()
+        step_bytes = 3 * gate0.numel() * es
         e2e = {"value": tokens_total / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": 3 * gate0.numel() * es * world, "d2h_bytes_per_step": 3 * gate0.numel() * es * world,
+               "h2d_bytes_per_step": step_bytes * world, "d2h_bytes_per_step": step_bytes * world,
                "steps": args.e2e_steps, "gpu_launches": e2e_launches,
+               "copy_ceiling": {"value": tokens_total / (ceil_ms * 1e-3), "unit": UNIT, "ms_per_step": ceil_ms,
+                                "gbs_per_direction_per_gpu": step_bytes / (ceil_ms * 1e-3) / 1e9,
+                                "what": "the step's input bytes host-to-device and its output bytes device-to-host at "
+                                        "the same time on two streams, plain 32 MiB asynchronous copies from/to the "
+                                        "same pinned buffers, no kernel, all ranks at once (max over ranks)"},
+               "frac_of_copy_ceiling": ceil_ms / e2e_ms,
+               "gbs_per_direction_per_gpu": step_bytes / (e2e_ms * 1e-3) / 1e9,
+               "host_placement": placement,
                "path": "swiglu_b200_host_fwd_bwd: pinned host gate/up/dh -> device workspace in row chunks, forward + "
                        "in-place backward per chunk, h/dgate/dup -> pinned host; copies of neighbouring chunks overlap "
                        "the kernels"}
-        del ws
+        del ws, hg, hu, hd, outs
+    os.sched_setaffinity(0, affinity0)
 
     if sampler:
         sampler.stop()
+
+    # ---- strong scaling of c5 over the same ranks ------------------------------------------------
+    strong = None
+    if not args.no_strong_c5:
+        from kernels.swiglu import swiglu_backward, swiglu_forward
+
+        h_dev = dgate_dev = dup_dev = None
+        del gate, up, gate0, up0, dh
+        torch.cuda.empty_cache()
+        strong = run_strong_c5(W, swiglu_forward, swiglu_backward, _lib.launch_count, device, rank, world,
+                               dist if world > 1 else None, barrier, args.c5_steps)
 
     if rank == 0:
         peak, peak_kind = measured_hbm_peak()
@@ -410,10 +670,13 @@ def main():
                                                    f"{'out-of-place' if preserve else 'in-place'}>",
                          "achieved": bwd_gbs, "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak,
                          "peak_source": f"{peak_kind} copy bandwidth (burst)",
-                         "traffic": BWD_DRAM_TRAFFIC_BYTES_C2 if w.name == "c2" else None,
+                         "traffic": scaled_bwd_traffic(w, w.tokens),
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch over 8192 "
+                                           "rows x 14336 bf16, scaled by elements x element size",
                          "algorithmic_bytes": w.bytes_bwd()},
             "clocks": sampler.summary(mark0, mark1) if sampler else None,
             "e2e": e2e,
+            "strong_c5": strong,
             "gpu_launches": launches,
             "wall_s_timed_loop_incl_restores": wall,
         }

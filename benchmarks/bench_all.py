@@ -10,7 +10,10 @@ providers x modes x shapes, CUDA-event timing with the two fastest and two slowe
 dropped, :97-120) and of the empty benchmarks/bench_all.py the reference ships.  What it adds: every
 row carries the algorithmic byte count (forward 3*N*s, backward 5*N*s, full 8*N*s bytes), the
 achieved GB/s, its fraction of the measured HBM copy bandwidth of this pool and of the nominal
-8 TB/s, and tokens/s.
+8 TB/s, and tokens/s.  Like the reference's sweep (:123-131) every row also carries the peak device
+memory of one call (torch.cuda.max_memory_allocated after an untimed setup), and what the call
+allocated on top of its inputs: the in-place backward is the reason the operator's default mode
+needs less.
 
 Providers
     b200         this library, in-place backward (the operator's default)
@@ -18,6 +21,12 @@ Providers
     b200-packed  this library, packed gate|up layout
     b200-perseq  this library, one call per sequence of the variable-length batch (c3 configurations only)
     torch-eager  the PyTorch composite (torch_swiglu_reference + autograd) on the same GPU
+    ref-triton-fast, ref-triton-safe, ref-triton-packed
+                 the reference's own Triton kernels (its swiglu_forward / swiglu_backward and the packed
+                 twins, in-place and preserve_inputs), from the unmodified copy that
+                 benchmarks/fetch_reference.py places under baseline/_ref; reported as unavailable when
+                 the copy is absent or its JIT fails.  Same launch wrappers, same timing, same GPU.
+    liger        Liger's LigerSiLUMulFunction (context only, as in the reference's sweep)
     geglu-tanh, geglu-erf   the sibling GeGLU operator of this library (in-place backward), same byte model
 
 Configurations are the synthetic workloads of kernel_pocs_b200/workloads.py plus ragged variants
@@ -75,6 +84,20 @@ def time_cuda(fn, setup, warmup: int, rep: int):
     return sum(trimmed) / len(trimmed), times[len(times) // 2], times[0]
 
 
+def peak_memory(fn, setup):
+    """(peak bytes allocated during one call, bytes the call allocated beyond what was live before it)."""
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    setup()
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated()
+    torch.cuda.reset_peak_memory_stats()
+    fn()
+    torch.cuda.synchronize()
+    peak = torch.cuda.max_memory_allocated()
+    return peak, peak - before
+
+
 def make_case(name: str, device, rank: int, world: int, strong: bool, max_rows: int = 0):
     """Returns (workload, gate, up, dh) for this rank."""
     base = name.split("+")[0]
@@ -101,8 +124,22 @@ def clone_like(t: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def reference_ops():
+    """The reference's launch wrappers (Triton kernels underneath) from the copy under baseline/_ref."""
+    try:
+        import fetch_reference
+    except ImportError:
+        from benchmarks import fetch_reference
+    return fetch_reference.load()
+
+
+def unavailable_row(name, provider, exc):
+    text = (str(exc).strip().splitlines() or [type(exc).__name__])[-1]
+    return {"config": name, "provider": provider, "unavailable": f"{type(exc).__name__}: {text}"[:300]}
+
+
 def run_case(name, args, device, rank, world):
-    from kernels.swiglu import swiglu_backward, swiglu_forward, swiglu_packed_backward, swiglu_packed_forward
+    import kernels.swiglu as own_ops
     from kernels.swiglu import torch_swiglu_reference
 
     w, gate0, up0, dh = make_case(name, device, rank, world, args.strong, args.max_rows)
@@ -112,8 +149,15 @@ def run_case(name, args, device, rank, world):
     byte_model = {"forward": 3 * n * es, "backward": 5 * n * es, "full": 8 * n * es}
     out_rows = []
     for provider in args.providers:
-        packed = provider == "b200-packed"
-        preserve = provider == "b200-safe"
+        ops = own_ops
+        if provider.startswith("ref-triton-"):
+            try:
+                ops = reference_ops()
+            except Exception as exc:  # copy absent, or triton not importable
+                out_rows.append(unavailable_row(name, provider, exc))
+                continue
+        packed = provider in ("b200-packed", "ref-triton-packed")
+        preserve = provider in ("b200-safe", "ref-triton-safe")
         gate, up = clone_like(gate0), clone_like(up0)
         gate_up0 = torch.cat([gate0, up0], dim=-1) if packed else None
         gate_up = gate_up0.clone() if packed else None
@@ -124,7 +168,7 @@ def run_case(name, args, device, rank, world):
             # before the timed kernels start
             if packed:
                 gate_up.copy_(gate_up0)
-            elif provider in ("b200", "b200-perseq") or provider.startswith("geglu-"):
+            elif provider in ("b200", "b200-perseq", "ref-triton-fast", "liger") or provider.startswith("geglu-"):
                 gate.copy_(gate0)
                 up.copy_(up0)
             else:
@@ -145,8 +189,40 @@ def run_case(name, args, device, rank, world):
             def full():
                 fwd()
                 bwd()
+                state.clear()
 
-            setups = {"forward": lambda: None, "backward": fwd, "full": lambda: None}
+            setups = {"forward": state.clear, "backward": fwd, "full": state.clear}
+        elif provider == "liger":
+            try:
+                from liger_kernel.ops.swiglu import LigerSiLUMulFunction
+            except Exception as exc:
+                out_rows.append(unavailable_row(name, provider, exc))
+                continue
+            state = {}
+            g = gate.requires_grad_(True)
+            u = up.requires_grad_(True)
+
+            def fwd():
+                state["h"] = LigerSiLUMulFunction.apply(g, u)
+
+            def bwd():
+                torch.autograd.grad(state["h"], (g, u), dh)
+
+            def full():
+                fwd()
+                bwd()
+                state.clear()
+
+            def liger_restore():
+                state.clear()
+                with torch.no_grad():
+                    restore()
+
+            def liger_bwd_setup():
+                liger_restore()
+                fwd()
+
+            setups = {"forward": liger_restore, "backward": liger_bwd_setup, "full": liger_restore}
         elif provider.startswith("geglu-"):
             from kernels.geglu import geglu_backward, geglu_forward
 
@@ -165,10 +241,10 @@ def run_case(name, args, device, rank, world):
             setups = {m: restore for m in ("forward", "backward", "full")}
         elif packed:
             def fwd():
-                swiglu_packed_forward(gate_up)
+                ops.swiglu_packed_forward(gate_up)
 
             def bwd():
-                swiglu_packed_backward(dh, gate_up, gate_up.shape, preserve_inputs=False)
+                ops.swiglu_packed_backward(dh, gate_up, gate_up.shape, preserve_inputs=False)
 
             def full():
                 fwd()
@@ -185,11 +261,11 @@ def run_case(name, args, device, rank, world):
 
             def fwd():
                 for a, b in bounds:
-                    swiglu_forward(gate[a:b], up[a:b])
+                    ops.swiglu_forward(gate[a:b], up[a:b])
 
             def bwd():
                 for a, b in bounds:
-                    swiglu_backward(dh[a:b], gate[a:b], up[a:b])
+                    ops.swiglu_backward(dh[a:b], gate[a:b], up[a:b])
 
             def full():
                 fwd()
@@ -198,10 +274,10 @@ def run_case(name, args, device, rank, world):
             setups = {m: restore for m in ("forward", "backward", "full")}
         else:
             def fwd():
-                swiglu_forward(gate, up)
+                ops.swiglu_forward(gate, up)
 
             def bwd():
-                swiglu_backward(dh, gate, up, preserve_inputs=preserve)
+                ops.swiglu_backward(dh, gate, up, preserve_inputs=preserve)
 
             def full():
                 fwd()
@@ -211,7 +287,14 @@ def run_case(name, args, device, rank, world):
 
         fns = {"forward": fwd, "backward": bwd, "full": full}
         for mode in args.modes:
-            mean, med, best = time_cuda(fns[mode], setups[mode], args.warmup, args.rep)
+            try:
+                mean, med, best = time_cuda(fns[mode], setups[mode], args.warmup, args.rep)
+                peak_bytes, extra_bytes = peak_memory(fns[mode], setups[mode])
+            except Exception as exc:
+                if ops is own_ops and provider != "liger":
+                    raise  # this library's own providers never fail quietly
+                out_rows.append(unavailable_row(name, provider, exc))
+                break
             t = torch.tensor([mean, med, best], dtype=torch.float64, device=device)
             if world > 1:
                 import torch.distributed as dist
@@ -225,6 +308,7 @@ def run_case(name, args, device, rank, world):
                 "algorithmic_bytes_per_gpu": byte_model[mode],
                 "gbs_per_gpu": byte_model[mode] / (mean * 1e-3) / 1e9,
                 "tokens_per_s": (w.tokens if args.strong else rows * world) / (mean * 1e-3),
+                "peak_mib": peak_bytes / 2**20, "call_allocates_mib": extra_bytes / 2**20,
             })
         del gate, up, gate_up, gate_up0
         torch.cuda.empty_cache()
@@ -425,7 +509,8 @@ def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--configs", nargs="+", default=["c1", "c2", "c3", "c3-fp32", "c3+w11009", "c3+w11009-off1"])
     ap.add_argument("--providers", nargs="+", default=["b200", "b200-safe", "torch-eager"],
-                    choices=["b200", "b200-safe", "b200-packed", "b200-perseq", "torch-eager", "geglu-tanh", "geglu-erf"])
+                    choices=["b200", "b200-safe", "b200-packed", "b200-perseq", "torch-eager", "geglu-tanh", "geglu-erf",
+                             "ref-triton-fast", "ref-triton-safe", "ref-triton-packed", "liger"])
     ap.add_argument("--modes", nargs="+", default=["forward", "backward", "full"],
                     choices=["forward", "backward", "full"])
     ap.add_argument("--warmup", type=int, default=20)
@@ -460,15 +545,20 @@ def main():
                 rows.extend(run_lora(args, device))
             continue
         for r in run_case(name, args, device, rank, world):
+            if "unavailable" in r:
+                rows.append(r)
+                if rank == 0:
+                    print(f"{r['config']:>16} {r['provider']:>17} unavailable: {r['unavailable']}", flush=True)
+                continue
             r["frac_of_measured_copy"] = r["gbs_per_gpu"] / peak
             r["frac_of_nominal_8TBs"] = r["gbs_per_gpu"] / NOMINAL_HBM_GBS
             rows.append(r)
             if rank == 0:
-                print(f"{r['config']:>16} {r['provider']:>11} {r['mode']:>8} {r['dtype']:>8} "
+                print(f"{r['config']:>16} {r['provider']:>17} {r['mode']:>8} {r['dtype']:>8} "
                       f"{r['ms_mean_trimmed']:9.4f} ms  {r['gbs_per_gpu']:8.1f} GB/s/GPU  "
                       f"{100 * r['frac_of_measured_copy']:6.1f}% of {kind} {peak:.0f}  "
                       f"{100 * r['frac_of_nominal_8TBs']:5.1f}% of 8000  {r['tokens_per_s'] / 1e6:9.3f} Mtok/s "
-                      f"x{world}", flush=True)
+                      f"x{world}  peak {r['peak_mib']:8.0f} MiB (+{r['call_allocates_mib']:.0f})", flush=True)
     if rank == 0 and args.save:
         Path(args.save).parent.mkdir(parents=True, exist_ok=True)
         Path(args.save).write_text(json.dumps({"hbm_peak_gbs": peak, "hbm_peak_kind": kind, "rows": rows}, indent=1))

@@ -9,10 +9,15 @@
  *   swiglu_b200_bwd   <- kernels/swiglu/swiglu.py:250-261 (_swiglu_backward_kernel launch in
  *                        swiglu_backward) and :312-322 (_swiglu_packed_backward_kernel launch)
  *
- * All pointers are device pointers owned by the caller.  The library allocates nothing, keeps
- * no per-call state, never synchronises the stream and never aborts: every failure is a
- * non-zero return code.  Calls are asynchronous on `stream` and may be made concurrently
- * from several host threads (for example one per device).
+ * All pointers are device pointers owned by the caller.  The library allocates no device memory,
+ * never synchronises the stream and never aborts: every failure is a non-zero return code.  Calls
+ * are asynchronous on `stream` and may be made concurrently from several host threads (for example
+ * one per device).  State the library keeps between calls, all of it per process: the launch
+ * counters; per device, the SM count and the shared-memory opt-in of the tensor-core kernels,
+ * queried or set on their first launch there; per device, once swiglu_b200_host_fwd_bwd has been
+ * called for it, two copy streams and ten events that every later call of that entry point on the
+ * device reuses (never destroyed; calls for one device are serialised on the host while they
+ * enqueue); and the status array of swiglu_b200_gemm_fwd_noalloc described at its declaration.
  *
  * Layouts.  A tensor is `rows` x `cols` elements with a row stride given in ELEMENTS.
  *   separate gate/up  : in_row_stride == out_row_stride == cols
@@ -150,7 +155,8 @@ SWIGLU_B200_API int swiglu_b200_geglu_bwd(void* dgate, void* dup, const void* do
  * `workspace` (256-byte aligned, any size that holds at least 12 token rows; see
  * swiglu_b200_host_workspace_bytes for a size that makes the chunks about 32 MiB) and three
  * chunks are kept in flight: while one is copied in, the kernels run on the previous one and
- * the one before is copied out, on two internal copy streams and the caller's `stream`.
+ * the one before is copied out, on two internal copy streams (created on the first call for the
+ * device and kept) and the caller's `stream`.
  * The call only enqueues work; when `stream` is synchronised every output is on the host.
  * The workspace must not be used by other work until then. */
 SWIGLU_B200_API int swiglu_b200_host_fwd_bwd(void* h, void* dgate, void* dup, const void* gate, const void* up, const void* dout,
@@ -189,8 +195,11 @@ SWIGLU_B200_API int swiglu_b200_gemm_fwd(void* h, void* gate_out, void* up_out, 
  * kernel's status word lives in a 256-byte array inside the library image, so the caller passes
  * inputs and outputs only.  The call performs no cudaMalloc/cudaFree and uses no allocating
  * library routine.
- *   status_host    NULL, or where to copy the status word after the kernel (asynchronously on
- *                  `stream`; use pinned memory): 0 once the stream is synchronised means success.
+ *   status_host    NULL, or where to copy the status word after the kernel, asynchronously on
+ *                  `stream`: 0 once the stream is synchronised means success.  It must be pinned
+ *                  (page-locked) host memory: a copy to pageable memory blocks the host until it
+ *                  is done and cannot be issued while a stream is being captured.  For an empty
+ *                  problem (m or n zero) nothing is launched and 0 is stored there directly.
  * Limit: the scratch array is 256 bytes per device and is held by every GPU that loads the
  * library until the process exits; a call needs 4 of them for any problem size, and a call whose
  * need exceeded the array would be refused with SWIGLU_B200_ERR_WORKSPACE.
@@ -252,6 +261,18 @@ SWIGLU_B200_API int swiglu_b200_gemm_bwd(void* dx, void* dw_gate, void* dw_up, c
 
 /* Number of backward-GEMM kernels launched by this process. */
 SWIGLU_B200_API uint64_t swiglu_b200_gemm_bwd_launch_count(void);
+
+/* TEST-ONLY: makes a bounded wait run out.  No counterpart in the reference.  Every mbarrier wait of
+ * the tensor-core kernels above gives up after a limit, stores a code in the launch's status word
+ * and lets the kernel return; this entry launches one CTA of one warp that initialises a barrier
+ * nothing ever arrives at and waits on it with the same wait function and a limit of
+ * `limit_cycles` SM clock cycles (at most 40 000 000, about 20 ms).  No bulk copy, tensor memory or
+ * MMA is involved, and the real kernels are not altered for it.  After the stream is synchronised
+ * `status` (device int, zeroed by the launch, as for swiglu_b200_gemm_fwd) holds `code` (non-zero).
+ *   mode   0: the CTA-scope wait of the one-CTA kernels; 1: the CTA-scope wait of the CTA-pair
+ *          kernels; 2: the same with its 200 ns pause between polls; 3: their cluster-scope wait. */
+SWIGLU_B200_API int swiglu_b200_selftest_wait_timeout(void* status, int mode, int64_t limit_cycles, int code, int device,
+                                      void* stream);
 
 /* LoRA + SwiGLU epilogue (bf16):
  *     e = e_base + s_gate * (xa_gate . b_gate^T),  g = g_base + s_up * (xa_up . b_up^T),  h = silu(e) * g

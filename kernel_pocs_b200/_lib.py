@@ -1,8 +1,10 @@
 """ctypes binding of libswiglu_b200.so (the C ABI declared in include/swiglu_b200.h).
 
-There is no fallback.  If the shared library is missing or was built from other sources than
-the ones in the tree, it is rebuilt with nvcc on import; if that is impossible, or the library
-does not export a declared symbol, importing this module raises.
+There is no fallback.  The library is bound on first use (``lib.<entry point>`` or ``load()``):
+if it is missing or was built from other sources than the ones in the tree, it is rebuilt with
+nvcc then; if that is impossible, or the library does not export a declared symbol, that first use
+raises ImportError.  Importing the package alone does not map the library, so host-only helpers
+(the synthetic workloads, the row partition) can be used by processes that never touch a GPU.
 """
 from __future__ import annotations
 
@@ -97,6 +99,8 @@ SIGNATURES = {
          ctypes.c_int, _c_ptr],
     ),
     "swiglu_b200_gemm_bwd_launch_count": (ctypes.c_uint64, []),
+    "swiglu_b200_selftest_wait_timeout": (
+        ctypes.c_int, [_c_ptr, ctypes.c_int, _c_i64, ctypes.c_int, ctypes.c_int, _c_ptr]),
 }
 
 
@@ -122,7 +126,33 @@ def _load() -> ctypes.CDLL:
     return lib
 
 
-lib = _load()
+class _LazyLibrary:
+    """Stands for the bound library; binds it the first time an entry point is looked up."""
+
+    __slots__ = ("_cdll",)
+
+    def __init__(self):
+        self._cdll = None
+
+    def _bound(self) -> ctypes.CDLL:
+        if self._cdll is None:
+            self._cdll = _load()
+        return self._cdll
+
+    def __getattr__(self, name: str):
+        return getattr(self._bound(), name)
+
+
+lib = _LazyLibrary()
+
+
+def load() -> ctypes.CDLL:
+    """Binds the library now (building it first when stale) and returns the ctypes handle."""
+    return lib._bound()
+
+
+def is_loaded() -> bool:
+    return lib._cdll is not None
 
 
 class SwigluB200Error(RuntimeError):

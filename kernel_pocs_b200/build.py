@@ -22,7 +22,8 @@ INCLUDE = ROOT / "include"
 LIB_PATH = PKG / "libswiglu_b200.so"
 STAMP_PATH = PKG / "libswiglu_b200.so.stamp"  # digest of the sources the library was built from
 
-SOURCES = [CSRC / "swiglu_capi.cu", CSRC / "swiglu_host.cu", CSRC / "swiglu_gemm.cu", CSRC / "swiglu_gemm_bwd.cu", CSRC / "swiglu_lora.cu"]
+SOURCES = [CSRC / "swiglu_capi.cu", CSRC / "swiglu_host.cu", CSRC / "swiglu_gemm.cu", CSRC / "swiglu_gemm_bwd.cu", CSRC / "swiglu_lora.cu",
+           CSRC / "swiglu_selftest.cu"]
 HEADERS = [CSRC / "swiglu_kernels.cuh", CSRC / "tcgen05_common.cuh", INCLUDE / "swiglu_b200.h"]
 
 NVCC_FLAGS = [

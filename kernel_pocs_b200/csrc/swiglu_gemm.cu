@@ -190,13 +190,7 @@ swiglu_gemm_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   // Teardown.  After a failed wait, give copies that are still in flight time to land in this
   // CTA's shared memory before it is handed to another CTA.
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (*reinterpret_cast<volatile int*>(p.status) != 0) {
-    const long long t0 = clock64();
-    while (clock64() - t0 < 2000000LL) {
-    }
-    __syncthreads();
-  }
+  settle_before_teardown(p.status);
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -419,13 +413,7 @@ swiglu_gemm_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __g
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (*reinterpret_cast<volatile int*>(p.status) != 0) {
-    const long long t0 = clock64();
-    while (clock64() - t0 < 2000000LL) {
-    }
-    __syncthreads();
-  }
+  settle_before_teardown(p.status);
   cluster_sync();  // the peer's shared memory and TMEM stay alive until the leader's MMAs are done
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -694,10 +682,14 @@ int swiglu_b200_gemm_fwd_noalloc(void* h, const void* x, const void* w_gate, con
     // The existing entry point zeroes the status word on the stream before the kernel starts
     // (the array still holds whatever the previous call left) and allocates nothing itself.
     rc = swiglu_b200_gemm_fwd(h, nullptr, nullptr, x, w_gate, w_up, m, n, k, gm, dm, status_dev, -1, stream);
-    if (rc == SWIGLU_B200_OK && status_host != nullptr && m > 0 && n > 0) {
-      if (cudaMemcpyAsync(status_host, status_dev, sizeof(int), cudaMemcpyDeviceToHost,
-                          static_cast<cudaStream_t>(stream)) != cudaSuccess)
-        rc = SWIGLU_B200_ERR_COPY;
+    if (rc == SWIGLU_B200_OK && status_host != nullptr) {
+      if (m > 0 && n > 0) {
+        if (cudaMemcpyAsync(status_host, status_dev, sizeof(int), cudaMemcpyDeviceToHost,
+                            static_cast<cudaStream_t>(stream)) != cudaSuccess)
+          rc = SWIGLU_B200_ERR_COPY;
+      } else {
+        *status_host = 0;  // empty problem: nothing was launched, so nothing can have failed
+      }
     }
   }
   if (switched) cudaSetDevice(prev);

@@ -314,13 +314,7 @@ swiglu_gemm_bwd_kernel(const __grid_constant__ CUtensorMap map0, const __grid_co
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (*reinterpret_cast<volatile int*>(p.status) != 0) {
-    const long long t0 = clock64();
-    while (clock64() - t0 < 2000000LL) {
-    }
-    __syncthreads();
-  }
+  settle_before_teardown(p.status);
   cluster_sync();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

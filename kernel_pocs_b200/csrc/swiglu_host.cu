@@ -6,6 +6,8 @@
 
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 namespace {
 
 constexpr int kSlots = 3;            // chunks in flight: one copying in, one computing, one copying out
@@ -13,18 +15,49 @@ constexpr uint64_t kAlign = 256;     // alignment of every staging buffer inside
 
 inline uint64_t round_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 
-struct Cleanup {
-  // Streams and events are destroyed when the call returns; the runtime defers the release of
-  // each until the work already queued on it has finished.
+constexpr int kEvents = 3 * kSlots + 1;
+constexpr int kMaxDevices = 64;
+
+// The two copy streams and the events of the pipeline are made once per device, on the first call
+// for that device, and kept until the process exits: creating and destroying them on every call
+// cost more host time than enqueueing the pipeline itself.  One call at a time per device holds
+// the lock while it enqueues; a later call may reuse the events at once, because a stream wait
+// refers to the record that was current when the wait was issued.
+struct DevicePipeline {
+  std::mutex lock;
+  bool ready = false;
   cudaStream_t in = nullptr, out = nullptr;
-  cudaEvent_t ev[3 * kSlots + 1] = {};
-  int n_ev = 0;
-  int prev_device = -1;
-  bool switched = false;
-  ~Cleanup() {
-    for (int i = 0; i < n_ev; ++i) cudaEventDestroy(ev[i]);
+  cudaEvent_t ev[kEvents] = {};
+};
+
+DevicePipeline g_pipeline[kMaxDevices];
+
+// Must be called with p.lock held and the device current.
+bool ensure_pipeline(DevicePipeline& p) {
+  if (p.ready) return true;
+  cudaStream_t in = nullptr, out = nullptr;
+  cudaEvent_t ev[kEvents] = {};
+  int made = 0;
+  bool ok = cudaStreamCreateWithFlags(&in, cudaStreamNonBlocking) == cudaSuccess &&
+            cudaStreamCreateWithFlags(&out, cudaStreamNonBlocking) == cudaSuccess;
+  for (; ok && made < kEvents; ++made) ok = cudaEventCreateWithFlags(&ev[made], cudaEventDisableTiming) == cudaSuccess;
+  if (!ok) {
+    for (int i = 0; i < made; ++i) if (ev[i]) cudaEventDestroy(ev[i]);
     if (in) cudaStreamDestroy(in);
     if (out) cudaStreamDestroy(out);
+    return false;
+  }
+  p.in = in;
+  p.out = out;
+  for (int i = 0; i < kEvents; ++i) p.ev[i] = ev[i];
+  p.ready = true;
+  return true;
+}
+
+struct DeviceScope {
+  int prev_device = -1;
+  bool switched = false;
+  ~DeviceScope() {
     if (switched) cudaSetDevice(prev_device);
   }
 };
@@ -62,21 +95,21 @@ int swiglu_b200_host_fwd_bwd(void* h, void* dgate, void* dup, const void* gate, 
   if (chunk_rows > rows) chunk_rows = rows;
   per_buffer = round_up((uint64_t)chunk_rows * row_bytes, kAlign);
 
-  Cleanup c;
-  if (device >= 0) {
-    if (cudaGetDevice(&c.prev_device) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
-    if (c.prev_device != device) {
-      if (cudaSetDevice(device) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
-      c.switched = true;
-    }
+  DeviceScope scope;
+  int current = -1;
+  if (cudaGetDevice(&current) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
+  if (device >= 0 && current != device) {
+    scope.prev_device = current;
+    if (cudaSetDevice(device) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
+    scope.switched = true;
+    current = device;
   }
+  if (current < 0 || current >= kMaxDevices) return SWIGLU_B200_ERR_DEVICE;
+  DevicePipeline& pipe = g_pipeline[current];
+  std::lock_guard<std::mutex> guard(pipe.lock);
+  if (!ensure_pipeline(pipe)) return SWIGLU_B200_ERR_DEVICE;
+  struct { cudaStream_t in, out; cudaEvent_t* ev; } c = {pipe.in, pipe.out, pipe.ev};
   cudaStream_t compute = static_cast<cudaStream_t>(stream);
-  if (cudaStreamCreateWithFlags(&c.in, cudaStreamNonBlocking) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
-  if (cudaStreamCreateWithFlags(&c.out, cudaStreamNonBlocking) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
-  for (int i = 0; i < 3 * kSlots + 1; ++i) {
-    if (cudaEventCreateWithFlags(&c.ev[i], cudaEventDisableTiming) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
-    c.n_ev = i + 1;
-  }
   cudaEvent_t* loaded = &c.ev[0];            // [slot] inputs of the slot are on the device
   cudaEvent_t* computed = &c.ev[kSlots];     // [slot] both kernels of the slot are done
   cudaEvent_t* drained = &c.ev[2 * kSlots];  // [slot] outputs of the slot are back on the host

@@ -327,13 +327,7 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (*reinterpret_cast<volatile int*>(p.status) != 0) {
-    const long long t0 = clock64();
-    while (clock64() - t0 < 2000000LL) {
-    }
-    __syncthreads();
-  }
+  settle_before_teardown(p.status);
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");

@@ -30,20 +30,37 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Returns false when the barrier did not flip within WAIT_CYCLES or when another
-// thread has already reported a failure; the first failure stores `code` in *status.
-__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int* status, int code) {
+// Bounded wait.  Returns false when the barrier did not flip within `limit` cycles of the SM clock
+// or when another thread has already reported a failure; the first failure stores `code` in *status.
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int* status, int code,
+                                          long long limit = WAIT_CYCLES) {
   if (mbar_try_wait(b, parity)) return true;
   const long long t0 = clock64();
   for (int spin = 0;; ++spin) {
     if (mbar_try_wait(b, parity)) return true;
     if ((spin & 63) == 63) {
       if (*reinterpret_cast<volatile int*>(status) != 0) return false;
-      if (clock64() - t0 > WAIT_CYCLES) {
+      if (clock64() - t0 > limit) {
         atomicCAS(status, 0, code);
         return false;
       }
     }
+  }
+}
+
+// The barrier in front of every kernel's teardown.  All threads of the CTA take part in ONE barrier
+// that also tells each of them whether any thread saw a failure code in the status word, so the
+// whole CTA takes the same branch: reading the word thread by thread could split the CTA between a
+// barrier inside the branch and the next barrier after it when another CTA reports at that moment.
+// After a failure the CTA lets copies that are still in flight land in its shared memory before the
+// memory is handed to another CTA.  (The two CTAs of a pair may decide differently; both reach the
+// cluster barrier that follows either way.)
+__device__ __forceinline__ void settle_before_teardown(const int* status) {
+  if (__syncthreads_or(*reinterpret_cast<const volatile int*>(status) != 0)) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {
+    }
+    __syncthreads();
   }
 }
 
@@ -143,7 +160,8 @@ __device__ __forceinline__ bool try_wait_cluster(uint64_t* b, uint32_t parity) {
 // an accumulator): every poll is a shared-memory access, and several warps polling flat out take bandwidth from
 // the operand traffic of the MMAs they are waiting for.
 template <bool CLUSTER_SCOPE, int SLEEP_NS = 0>
-__device__ __forceinline__ bool wait(uint64_t* b, uint32_t parity, int* status, int code) {
+__device__ __forceinline__ bool wait(uint64_t* b, uint32_t parity, int* status, int code,
+                                     long long limit = WAIT_CYCLES) {
   auto poll = [&] { return CLUSTER_SCOPE ? try_wait_cluster(b, parity) : mbar_try_wait(b, parity); };
   if (poll()) return true;
   const long long t0 = clock64();
@@ -152,7 +170,7 @@ __device__ __forceinline__ bool wait(uint64_t* b, uint32_t parity, int* status, 
     if (poll()) return true;
     if ((spin & 63) == 63) {
       if (*reinterpret_cast<volatile int*>(status) != 0) return false;
-      if (clock64() - t0 > WAIT_CYCLES) {
+      if (clock64() - t0 > limit) {
         atomicCAS(status, 0, code);
         return false;
       }

@@ -18,83 +18,148 @@ from . import _lib
 from .swiglu import _as_float, swiglu_backward
 
 class _StatusRing:
-    """Status words of the tensor-core kernels of one device, checked without stalling the stream.
+    """Status words of the tensor-core kernels of one device.
 
-    Every launch gets its own word out of a small ring (so launches that overlap on different streams do not
-    share one).  A kernel whose bounded waits gave up leaves a code there.  Each time the ring wraps around, all
-    of it is copied to pinned host memory, asynchronously on the stream current then, and a copy that has
-    completed is inspected at the next launch: a failure surfaces as a ``RuntimeError`` within two turns of
-    the ring, at the cost of one small copy per ``SLOTS`` launches and no synchronisation.  ``check_status``
-    synchronises and looks at once."""
+    Every launch gets its own word (launches that overlap on different streams never share one).  A kernel whose
+    bounded waits gave up leaves a code there.  The words form a ring of two halves.  When the launches move on
+    from one half to the other, the half just left is copied to pinned host memory, asynchronously, after the
+    streams that launched into it (the stream current at that moment waits for the others first), and the half
+    being entered is inspected: its copy, enqueued one turn ago, must have arrived before its words are handed
+    out (and zeroed) again.  If that copy is still in flight the host waits for it, which bounds how far the host
+    runs ahead of the device to one turn of the ring (``2 * HALF`` launches); otherwise nothing blocks.  A
+    failure surfaces as a ``RuntimeError`` within one turn.  ``check_status`` synchronises and looks at once.
 
-    SLOTS = 16
+    Taking a word and launching the kernel that uses it happen under one lock (``launch()``), so the copy of a
+    half is never enqueued between the two; the forward (caller's thread) and the backward (autograd's thread)
+    both launch."""
+
+    HALF = 16
+    SLOTS = 2 * HALF
 
     def __init__(self, device: torch.device):
         self.device = device
         self.dev = torch.zeros(self.SLOTS, dtype=torch.int32, device=device)
         self.words = [self.dev[i:i + 1] for i in range(self.SLOTS)]
-        self.host = torch.zeros(self.SLOTS, dtype=torch.int32).pin_memory()
-        self.pending = None  # event of the ring copy in flight
+        self.host = [torch.zeros(self.HALF, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.pending = [None, None]  # per half: event of its copy in flight
+        self.streams = [{}, {}]      # per half: streams that launched into it since its last copy
         self.next = 0
-        self.used = False
-        self.lock = threading.Lock()  # forward (caller's thread) and backward (autograd's thread) both launch
+        self.lock = threading.RLock()
 
     @staticmethod
     def _raise(code: int):
         raise RuntimeError(f"a tensor-core kernel of swiglu_b200 reported a timed-out wait (code {code}); "
                            "its output is incomplete")
 
-    def _collect(self, wait: bool):
-        ev = self.pending
+    def _inspect(self, half: int):
+        """Waits for the copy of ``half`` if one is in flight and raises if it holds a code."""
+        ev = self.pending[half]
         if ev is None:
             return
-        if wait:
-            ev.synchronize()
-        elif not ev.query():
-            return
-        self.pending = None
-        codes = [c for c in self.host.tolist() if c]
+        ev.synchronize()  # returns at once unless the host is a whole turn ahead of the device
+        self.pending[half] = None
+        codes = [c for c in self.host[half].tolist() if c]
         if codes:
-            self.dev.zero_()  # reported once
+            # reported once: every launch into this half has finished (its copy came after them), so the
+            # words can be cleared here; the launches that reuse them zero their own again anyway
+            self.host[half].zero_()
+            lo = half * self.HALF
+            self.dev[lo:lo + self.HALF].zero_()
             self._raise(codes[0])
 
-    def acquire(self) -> torch.Tensor:
-        """The word for the launch that is about to be made (a one-element view; the C entry zeroes it)."""
-        with self.lock:
-            return self._acquire_locked()
+    def _send(self, half: int):
+        """Enqueues the copy of ``half`` to the host behind every stream that launched into it."""
+        current = torch.cuda.current_stream(self.device)
+        for stream in self.streams[half].values():
+            if stream != current:
+                current.wait_stream(stream)
+        self.streams[half] = {}
+        lo = half * self.HALF
+        self.host[half].copy_(self.dev[lo:lo + self.HALF], non_blocking=True)
+        self.pending[half] = torch.cuda.Event()
+        self.pending[half].record(current)
 
     def _acquire_locked(self) -> torch.Tensor:
         i = self.next
-        if i == 0 and self.used:
-            # the ring has gone round: look at the previous copy, then send the words of the last turn
-            self._collect(wait=True)
-            self.host.copy_(self.dev, non_blocking=True)
-            self.pending = torch.cuda.Event()
-            self.pending.record(torch.cuda.current_stream(self.device))
-        elif self.pending is not None:
-            self._collect(wait=False)
-        self.used = True
+        half, first = divmod(i, self.HALF)
+        if first == 0:
+            other = 1 - half
+            if self.streams[other]:
+                self._send(other)
+            self._inspect(half)  # may raise: the launch that asked is not made, the next one finds the ring clean
+        stream = torch.cuda.current_stream(self.device)
+        self.streams[half][stream.cuda_stream] = stream
         self.next = (i + 1) % self.SLOTS
         return self.words[i]
+
+    def acquire(self) -> torch.Tensor:
+        """The word for a launch that is about to be made (a one-element view; the C entry zeroes it).  Callers
+        that launch should use ``launch()``; this is for tests that fill a word by hand."""
+        with self.lock:
+            return self._acquire_locked()
+
+    def launch(self):
+        """``with ring.launch() as word:`` hands out the next word and holds the ring's lock until the block,
+        which enqueues the kernel, is left."""
+        return _Launch(self)
 
     def check(self):
         with self.lock:
             torch.cuda.synchronize(self.device)
             codes = [c for c in self.dev.tolist() if c]
+            for half in (0, 1):
+                if self.pending[half] is not None:
+                    codes += [c for c in self.host[half].tolist() if c]
+                    self.host[half].zero_()
+                    self.pending[half] = None
+                self.streams[half] = {}
             self.dev.zero_()
-            self.pending = None
         if codes:
             self._raise(codes[0])
 
 
+class _Launch:
+    __slots__ = ("ring",)
+
+    def __init__(self, ring: _StatusRing):
+        self.ring = ring
+
+    def __enter__(self) -> torch.Tensor:
+        self.ring.lock.acquire()
+        try:
+            return self.ring._acquire_locked()
+        except BaseException:
+            self.ring.lock.release()
+            raise
+
+    def __exit__(self, *exc):
+        self.ring.lock.release()
+        return False
+
+
 _status_rings: dict[int, _StatusRing] = {}
+_status_rings_lock = threading.Lock()
+
+
+def _ring(device: torch.device) -> _StatusRing:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    ring = _status_rings.get(index)
+    if ring is None:
+        with _status_rings_lock:
+            ring = _status_rings.get(index)
+            if ring is None:
+                ring = _status_rings[index] = _StatusRing(torch.device("cuda", index))
+    return ring
 
 
 def _status(device: torch.device) -> torch.Tensor:
-    ring = _status_rings.get(device.index)
-    if ring is None:
-        ring = _status_rings[device.index] = _StatusRing(device)
-    return ring.acquire()
+    """The next status word of ``device`` without a launch (tests fill it by hand)."""
+    return _ring(device).acquire()
+
+
+def _launching(device: torch.device):
+    """``with _launching(device) as word:`` around the C call that enqueues a tensor-core kernel."""
+    return _ring(device).launch()
 
 
 def check_status(device: torch.device | int | None = None) -> None:
@@ -109,6 +174,28 @@ def check_status(device: torch.device | int | None = None) -> None:
     ring = _status_rings.get(index)
     if ring is not None:
         ring.check()
+
+
+def selftest_wait_timeout(device: torch.device | int | None = None, mode: int = 0, limit_cycles: int = 2_000_000,
+                          code: int = 901) -> torch.Tensor:
+    """Test-only: launches the library's one-warp self-test kernel (``swiglu_b200_selftest_wait_timeout``), whose
+    single wait is on a barrier that nothing ever arrives at and is limited to ``limit_cycles`` of the SM clock
+    (about a millisecond by default).  The kernel gives up, leaves ``code`` in its status word, taken from the
+    same ring as every tensor-core launch, and returns; so a later launch or ``check_status`` raises, exactly
+    as it would for a real kernel whose wait ran out.  Returns the status word (a one-element view).
+    ``mode`` selects the wait under test: 0 CTA-scope, 1 the pair kernels' CTA-scope wait, 2 the same with
+    the 200 ns pause between polls, 3 their cluster-scope wait."""
+    if device is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    else:
+        dev = torch.device(device) if not isinstance(device, int) else torch.device("cuda", device)
+        if dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+    with _launching(dev) as status:
+        rc = _lib.lib.swiglu_b200_selftest_wait_timeout(status.data_ptr(), int(mode), int(limit_cycles), int(code),
+                                                        dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check("selftest_wait_timeout", rc)
+    return status
 
 
 def _check_operands(x, w_gate, w_up):
@@ -136,15 +223,14 @@ def gate_up_swiglu_forward(x, w_gate, w_up, gate_multiplier=1.0, down_multiplier
     h = torch.empty((m, n), dtype=x.dtype, device=x.device)
     gate = torch.empty_like(h) if save_preactivations else None
     up = torch.empty_like(h) if save_preactivations else None
-    _lib.check(
-        "gate_up_swiglu_forward",
-        _lib.lib.swiglu_b200_gemm_fwd(
+    with _launching(x.device) as status:
+        rc = _lib.lib.swiglu_b200_gemm_fwd(
             h.data_ptr(), gate.data_ptr() if save_preactivations else None,
             up.data_ptr() if save_preactivations else None, x2.data_ptr(), wg.data_ptr(), wu.data_ptr(),
-            m, n, k, gm, dm, _status(x.device).data_ptr(), x.device.index,
+            m, n, k, gm, dm, status.data_ptr(), x.device.index,
             torch.cuda.current_stream(x.device).cuda_stream,
-        ),
-    )
+        )
+    _lib.check("gate_up_swiglu_forward", rc)
     h = h.view(*x.shape[:-1], n)
     if save_preactivations:
         return h, gate, up
@@ -181,11 +267,12 @@ def lora_gate_up_swiglu_forward(x, w_gate, w_up, A_gate, B_gate, s_gate, A_up, B
         raise ValueError(f"activation must be 'silu', 'gelu_tanh' or 'gelu_exact', got {activation!r}")
     common = (h.data_ptr(), e.data_ptr() if save_eg else None, g.data_ptr() if save_eg else None, x2.data_ptr(),
               wg.data_ptr(), wu.data_ptr(), xa.data_ptr(), bg.data_ptr(), bu.data_ptr(), m, n, k, r)
-    tail = (_status(x.device).data_ptr(), x.device.index, torch.cuda.current_stream(x.device).cuda_stream)
-    if activation == "silu":
-        rc = _lib.lib.swiglu_b200_lora_gemm_fwd(*common, 1.0, 1.0, *tail)
-    else:
-        rc = _lib.lib.swiglu_b200_lora_geglu_gemm_fwd(*common, int(activation == "gelu_tanh"), *tail)
+    with _launching(x.device) as status:
+        tail = (status.data_ptr(), x.device.index, torch.cuda.current_stream(x.device).cuda_stream)
+        if activation == "silu":
+            rc = _lib.lib.swiglu_b200_lora_gemm_fwd(*common, 1.0, 1.0, *tail)
+        else:
+            rc = _lib.lib.swiglu_b200_lora_geglu_gemm_fwd(*common, int(activation == "gelu_tanh"), *tail)
     _lib.check("lora_gate_up_swiglu_forward", rc)
     return h.view(*x.shape[:-1], n), e, g
 
@@ -203,15 +290,14 @@ def gate_up_swiglu_backward_gemms(dgate, dup, x, w_gate, w_up, need_dx=True, nee
     dwu = torch.empty_like(wu) if need_dw else None
     if not (need_dx or need_dw):
         return None, None, None
-    _lib.check(
-        "gate_up_swiglu_backward_gemms",
-        _lib.lib.swiglu_b200_gemm_bwd(
+    with _launching(x.device) as status:
+        rc = _lib.lib.swiglu_b200_gemm_bwd(
             dx.data_ptr() if need_dx else None, dwg.data_ptr() if need_dw else None,
             dwu.data_ptr() if need_dw else None, dgate.data_ptr(), dup.data_ptr(), x2.data_ptr(), wg.data_ptr(),
-            wu.data_ptr(), m, n, k, _status(x.device).data_ptr(), x.device.index,
+            wu.data_ptr(), m, n, k, status.data_ptr(), x.device.index,
             torch.cuda.current_stream(x.device).cuda_stream,
-        ),
-    )
+        )
+    _lib.check("gate_up_swiglu_backward_gemms", rc)
     return (dx.view(x.shape) if need_dx else None), dwg, dwu
 
 

@@ -269,7 +269,7 @@ def torch_geglu_mlp_reference(x, gate_weight, up_weight, down_weight, gate_bias=
 def gate_up_geglu_forward(x, w_gate, w_up, approximate: str = "tanh", save_preactivations: bool = False):
     """``gelu(x @ w_gate.T) * (x @ w_up.T)`` in one launch; with ``save_preactivations`` also the two projections
     (rounded to bf16).  bf16 operands, ``k % 8 == 0``, ``n % 16 == 0``."""
-    from .fused_mlp import _check_operands, _status
+    from .fused_mlp import _check_operands, _launching
 
     tanh = _check_approximate(approximate)
     _check_operands(x, w_gate, w_up)
@@ -281,14 +281,13 @@ def gate_up_geglu_forward(x, w_gate, w_up, approximate: str = "tanh", save_preac
     h = torch.empty((m, n), dtype=x.dtype, device=x.device)
     gate = torch.empty_like(h) if save_preactivations else None
     up = torch.empty_like(h) if save_preactivations else None
-    _lib.check(
-        "gate_up_geglu_forward",
-        _lib.lib.swiglu_b200_geglu_gemm_fwd(
+    with _launching(x.device) as status:
+        rc = _lib.lib.swiglu_b200_geglu_gemm_fwd(
             h.data_ptr(), gate.data_ptr() if save_preactivations else None,
             up.data_ptr() if save_preactivations else None, x2.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(),
-            m, n, k, int(tanh), _status(x.device).data_ptr(), x.device.index, _stream(x.device),
-        ),
-    )
+            m, n, k, int(tanh), status.data_ptr(), x.device.index, _stream(x.device),
+        )
+    _lib.check("gate_up_geglu_forward", rc)
     h = h.view(*x.shape[:-1], n)
     return (h, gate, up) if save_preactivations else h
 

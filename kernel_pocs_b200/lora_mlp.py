@@ -21,7 +21,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from .fused_mlp import _status
+from .fused_mlp import _launching
 from .swiglu import _as_float, swiglu_backward_recompute, swiglu_forward
 
 
@@ -89,15 +89,14 @@ def fused_lora_swiglu(
     h = torch.empty_like(e_base)
     e_out = (e_base if _inplace else torch.empty_like(e_base)) if save_eg else None
     g_out = (g_base if _inplace else torch.empty_like(e_base)) if save_eg else None
-    _lib.check(
-        "fused_lora_swiglu",
-        _lib.lib.swiglu_b200_lora_swiglu_fwd(
+    with _launching(e_base.device) as status:
+        rc = _lib.lib.swiglu_b200_lora_swiglu_fwd(
             h.data_ptr(), e_out.data_ptr() if save_eg else None, g_out.data_ptr() if save_eg else None,
             e_base.data_ptr(), g_base.data_ptr(), xa_gate.data_ptr(), xa_up.data_ptr(), B_gate.data_ptr(),
-            B_up.data_ptr(), m, n, r, sg, su, _status(e_base.device).data_ptr(), e_base.device.index,
+            B_up.data_ptr(), m, n, r, sg, su, status.data_ptr(), e_base.device.index,
             torch.cuda.current_stream(e_base.device).cuda_stream,
-        ),
-    )
+        )
+    _lib.check("fused_lora_swiglu", rc)
     return h, e_out, g_out
 
 

@@ -176,6 +176,57 @@ def test_backward_gemms_match_fp32_reference(m, n, k, tile, monkeypatch):
     assert none_x is None and torch.equal(dwg2, dwg) and torch.equal(dwu2, dwu)
 
 
+def test_full_size_projection_workload():
+    """Benchmark configuration c4 at its FULL size: X bf16 [16384, 4096] ~ N(0,1), W_gate and W_up bf16
+    [14336, 4096] ~ N(0, 0.02^2) (seed 3), dh ~ N(0,1).  Sixty-four sampled token rows (first, last and tile
+    edges among them) of h, of both pre-activations and of dX over ALL their columns, and sixty-four sampled
+    rows of dW_gate and dW_up over all theirs, against fp32 matmuls of the same bf16 operands; then the
+    autograd wrapper must reproduce the step-by-step results bit for bit."""
+    from kernels.swiglu import swiglu_backward
+
+    m, n, k = 16384, 14336, 4096
+    g = torch.Generator(device=DEVICE).manual_seed(3)
+    x = torch.randn(m, k, generator=g, device=DEVICE).bfloat16()
+    wg = (0.02 * torch.randn(n, k, generator=g, device=DEVICE)).bfloat16()
+    wu = (0.02 * torch.randn(n, k, generator=g, device=DEVICE)).bfloat16()
+    dh = torch.randn(m, n, generator=g, device=DEVICE).bfloat16()
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        pick = torch.Generator().manual_seed(33)
+        rows = torch.cat([torch.tensor([0, 1, 127, 128, 255, 256, m - 257, m - 256, m - 2, m - 1]),
+                          torch.randint(0, m, (54,), generator=pick)]).to(DEVICE)
+        cols = torch.cat([torch.tensor([0, 1, 127, 128, 255, 256, n - 257, n - 256, n - 2, n - 1]),
+                          torch.randint(0, n, (54,), generator=pick)]).to(DEVICE)
+        h, gate, up = F.gate_up_swiglu_forward(x, wg, wu, save_preactivations=True)
+        F.check_status(x.device)
+        xr = x[rows].float()
+        g_ref, u_ref = xr @ wg.float().t(), xr @ wu.float().t()
+        assert_close_bf16(gate[rows], g_ref, "gate pre-activation rows")
+        assert_close_bf16(up[rows], u_ref, "up pre-activation rows")
+        assert_close_bf16(h[rows], torch.nn.functional.silu(g_ref) * u_ref, "h rows")
+        del g_ref, u_ref
+        h_keep = h[rows].clone()
+        # the activation backward on the saved pre-activations (in place: they become dgate, dup), then the GEMMs
+        dgate, dup = swiglu_backward(dh, gate, up)
+        dx, dwg, dwu = F.gate_up_swiglu_backward_gemms(dgate, dup, x, wg, wu)
+        F.check_status(x.device)
+        assert_close_bf16(dx[rows], dgate[rows].float() @ wg.float() + dup[rows].float() @ wu.float(), "dx rows")
+        xf = x.float()
+        assert_close_bf16(dwg[cols], dgate[:, cols].float().t() @ xf, "dw_gate rows")
+        assert_close_bf16(dwu[cols], dup[:, cols].float().t() @ xf, "dw_up rows")
+        del xf, dgate, dup, gate, up, h
+        # the same through autograd
+        leaves = [t.clone().requires_grad_(True) for t in (x, wg, wu)]
+        h2 = F.fused_gate_up_swiglu(*leaves)
+        dx2, dwg2, dwu2 = torch.autograd.grad(h2, leaves, dh)
+        F.check_status(x.device)
+        assert torch.equal(h2[rows], h_keep)
+        assert torch.equal(dx2, dx) and torch.equal(dwg2, dwg) and torch.equal(dwu2, dwu)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
 def test_tensor_core_kernels_on_random_shapes():
     """Forward projection (plain, with adapters, with a GELU gate) and both backward GEMMs on 48 seeded random
     shapes: ragged row counts, widths that end inside a tile, contractions that end inside a K block, every rank
@@ -230,21 +281,21 @@ def test_tensor_core_kernels_on_random_shapes():
             os.environ["SWIGLU_B200_GEMM_BWD_TILE"] = saved
 
 
-def test_status_ring_reports_a_failed_launch_without_synchronising():
+def test_status_ring_reports_a_failed_launch():
     """A kernel that gives up on a wait leaves a code in its status word.  Made on the host here (the word is
-    filled by hand after a good launch; no kernel is made to fail): the code must surface as a RuntimeError at
-    one of the next launches, once, and an explicit check afterwards must be clean."""
+    filled by hand after a good launch; no kernel is made to fail): the code must surface as a RuntimeError
+    within one turn of the ring, once, and an explicit check afterwards must be clean."""
     x, wg, wu = make(256, 128, 64)
     F.gate_up_swiglu_forward(x, wg, wu)
     F.check_status(x.device)
-    word = F._status(x.device)           # the word the next launch would get
+    word = F._status(x.device)           # a word of the ring, as a launch would get it
     word.fill_(321)
     with pytest.raises(RuntimeError, match="code 321"):
-        for _ in range(2 * F._StatusRing.SLOTS):
+        for _ in range(F._StatusRing.SLOTS + 1):
             F.gate_up_swiglu_forward(x, wg, wu)
-            torch.cuda.synchronize()
-    F.check_status(x.device)
-    h = F.gate_up_swiglu_forward(x, wg, wu)
+    F.check_status(x.device)              # reported once: nothing is left behind
+    for _ in range(2 * F._StatusRing.SLOTS):
+        h = F.gate_up_swiglu_forward(x, wg, wu)
     F.check_status(x.device)
     assert bool(torch.isfinite(h).all())
     # the explicit check sees a code at once
@@ -252,3 +303,74 @@ def test_status_ring_reports_a_failed_launch_without_synchronising():
     with pytest.raises(RuntimeError, match="code 77"):
         F.check_status(x.device)
     F.check_status(x.device)
+
+
+def test_status_ring_keeps_a_code_whose_half_was_already_copied():
+    """The window between the copy of a half of the ring and the reuse of its words: a code that sits in a
+    half when that half is sent to the host must still be found by an explicit check made before the ring
+    comes back to it, and by the ring itself when it does; a reused word must not hide it."""
+    x, wg, wu = make(256, 128, 64)
+    F.check_status(x.device)
+    ring = F._ring(x.device)
+    half = F._StatusRing.HALF
+    # walk to the start of a half so that the scenario below is the same wherever the ring stood
+    while ring.next % half:
+        F.gate_up_swiglu_forward(x, wg, wu)
+    F._status(x.device).fill_(555)                     # first word of this half
+    for _ in range(half):                              # the rest of this half and the first launch of the other:
+        F.gate_up_swiglu_forward(x, wg, wu)            # the half with the code is now on its way to the host
+    first = ring.next // half
+    assert ring.pending[1 - first] is not None
+    with pytest.raises(RuntimeError, match="code 555"):
+        F.check_status(x.device)
+    F.check_status(x.device)
+    # same again, but let the ring find it: launches on a side stream, so the copy has to wait for that stream
+    side = torch.cuda.Stream()
+    while ring.next % half:
+        F.gate_up_swiglu_forward(x, wg, wu)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        F.selftest_wait_timeout(x.device, 0, 200_000, 556)   # a real kernel leaves the code, on the side stream
+    with pytest.raises(RuntimeError, match="code 556"):
+        for _ in range(F._StatusRing.SLOTS):
+            F.gate_up_swiglu_forward(x, wg, wu)
+    F.check_status(x.device)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2, 3])
+def test_bounded_wait_runs_out_and_reports(mode):
+    """The failure path of the tensor-core kernels on a real GPU, in the one form that harms nothing: a
+    one-warp kernel waits, with the kernels' own wait functions and a limit of about a millisecond, on a
+    barrier nothing arrives at.  The wait must give up (the call returns, the device stays usable), the
+    status word must hold the code, the status ring must raise once, and an ordinary fused GEMM right after
+    must be correct."""
+    x, wg, wu = make(512, 256, 128, seed=21)
+    want = F.gate_up_swiglu_forward(x, wg, wu)
+    F.check_status(x.device)
+    code = 900 + mode
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    word = F.selftest_wait_timeout(x.device, mode, 2_000_000, code)
+    t1.record()
+    torch.cuda.synchronize()
+    assert int(word.item()) == code
+    assert t0.elapsed_time(t1) < 100.0, "the wait is limited to about a millisecond"
+    with pytest.raises(RuntimeError, match=f"code {code}"):
+        F.check_status(x.device)
+    F.check_status(x.device)  # reported once
+    got = F.gate_up_swiglu_forward(x, wg, wu)
+    F.check_status(x.device)
+    assert torch.equal(got, want)
+    # straight through the C ABI with a word of the caller's own
+    st = torch.zeros(1, dtype=torch.int32, device=DEVICE)
+    lib = _lib.lib
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.swiglu_b200_selftest_wait_timeout(st.data_ptr(), mode, 2_000_000, 7, 0, stream) == 0
+    torch.cuda.synchronize()
+    assert int(st.item()) == 7
+    # argument checks: limit beyond the cap, zero code, unknown mode, null word
+    assert lib.swiglu_b200_selftest_wait_timeout(st.data_ptr(), mode, 10**9, 7, 0, stream) == 3
+    assert lib.swiglu_b200_selftest_wait_timeout(st.data_ptr(), mode, 1000, 0, 0, stream) == 3
+    assert lib.swiglu_b200_selftest_wait_timeout(st.data_ptr(), 9, 1000, 7, 0, stream) == 3
+    assert lib.swiglu_b200_selftest_wait_timeout(None, mode, 1000, 7, 0, stream) == 2

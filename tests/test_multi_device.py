@@ -36,6 +36,8 @@ def test_threads_on_different_devices_do_not_interfere():
             g, u, d = W.generate_rows(w, lo, hi, dev)
             h = torch.empty_like(g)
             stream = torch.cuda.Stream(device=dev)
+            # the generator wrote g, u, d on the device's default stream: order the side stream after it
+            stream.wait_stream(torch.cuda.current_stream(dev))
             rows, cols = g.shape
             for _ in range(20):  # the calling thread's current device stays 0: the call switches and restores
                 rc = _lib.lib.swiglu_b200_fwd(h.data_ptr(), g.data_ptr(), u.data_ptr(), rows, cols, cols, cols,

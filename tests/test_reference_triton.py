@@ -1,0 +1,123 @@
+"""This library against the reference's own Triton kernels on the same GPU, same seeded inputs.
+
+The comparator is the unmodified copy of the reference's ``kernels/swiglu/swiglu.py`` that
+``benchmarks/fetch_reference.py`` places under ``baseline/_ref`` (git-ignored).  When the copy is
+absent, or Triton cannot compile for this GPU, the tests skip: the parity of record is the one
+against the CPU oracle, which is pinned to vectors produced by the reference itself.
+
+Shapes, seeds, draw order and multipliers are those of the reference's tests/test_swiglu.py:28-99.
+With unit multipliers the two implementations differ only in how often they round (once here;
+twice or three times through 16-bit intermediates in the Triton kernels, swiglu.py:75-82 and
+:102-116), so they are held to 2 ulp in fp16/bf16 (a third ulp, where an intermediate of the
+reference is an fp16 subnormal, in at most one element in ten thousand) and to the reference's
+1e-5 in fp32.  With multipliers (0.7, 1.3) the Triton in this image also rounds the multiplier
+itself to the tile's 16-bit type, so only the reference test file's own tolerances (2e-2 fp16,
+3e-2 bf16) apply.
+"""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from benchmarks import fetch_reference
+from oracle import oracle as O
+from tests._util import assert_ulp
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(2, 8, 128), (1, 3, 257), (4, 5, 1024), (1, 2, 11008)]
+PACKED_SHAPES = [(2, 8, 256), (1, 3, 514)]
+DTYPE_TOL = [(torch.float32, 1e-5), (torch.float16, 2e-2), (torch.bfloat16, 3e-2)]
+
+
+@pytest.fixture(scope="module")
+def ref():
+    if not fetch_reference.available():
+        pytest.skip("baseline/_ref is absent (benchmarks/fetch_reference.py --reference <checkout> creates it)")
+    try:
+        module = fetch_reference.load()
+        x = torch.randn(4, 64, device="cuda")
+        module.swiglu(x, x.clone())  # first JIT: proves that Triton can compile for this GPU
+        torch.cuda.synchronize()
+    except Exception as exc:  # no Triton for this architecture, no host compiler, ...
+        pytest.skip(f"the reference's Triton kernels do not run here: {type(exc).__name__}: {exc}")
+    return module
+
+
+def assert_two_ulp(got, want, what):
+    assert_ulp(got, want, 3, what)
+    beyond = int((O.ulp_distance(got, want) > 2).sum())
+    assert beyond <= max(1, got.numel() // 10000), f"{what}: {beyond} elements more than 2 ulp apart"
+
+
+def _run(op, inputs, dout, *args):
+    leaves = [t.detach().clone().requires_grad_(True) for t in inputs]
+    out = op(*leaves, *args)
+    grads = torch.autograd.grad(out, leaves, dout)
+    return (out.detach(), *grads)
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("preserve_inputs", [False, True])
+@pytest.mark.parametrize("dtype,tol", DTYPE_TOL)
+def test_unit_multipliers_within_two_ulp_of_the_triton_kernels(ref, shape, preserve_inputs, dtype, tol):
+    from kernels.swiglu import swiglu
+
+    torch.manual_seed(0)
+    gate = torch.randn(*shape, device="cuda", dtype=dtype)
+    up = torch.randn(*shape, device="cuda", dtype=dtype)
+    dout = torch.randn(*shape, device="cuda", dtype=dtype)
+    want = _run(ref.swiglu, (gate, up), dout, 1.0, 1.0, preserve_inputs)
+    got = _run(swiglu, (gate, up), dout, 1.0, 1.0, preserve_inputs)
+    for name, g, w in zip(("h", "dgate", "dup"), got, want):
+        if dtype == torch.float32:
+            torch.testing.assert_close(g, w, rtol=tol, atol=tol, msg=lambda m: f"{name}: {m}")
+        else:
+            assert_two_ulp(g, w, f"{name} vs the reference's Triton kernel")
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("dtype,tol", DTYPE_TOL)
+def test_scaled_multipliers_within_the_reference_tolerances(ref, shape, dtype, tol):
+    from kernels.swiglu import swiglu
+
+    torch.manual_seed(0)
+    gate = torch.randn(*shape, device="cuda", dtype=dtype)
+    up = torch.randn(*shape, device="cuda", dtype=dtype)
+    dout = torch.randn(*shape, device="cuda", dtype=dtype)
+    want = _run(ref.swiglu, (gate, up), dout, 0.7, 1.3, True)
+    got = _run(swiglu, (gate, up), dout, 0.7, 1.3, True)
+    for name, g, w in zip(("h", "dgate", "dup"), got, want):
+        torch.testing.assert_close(g, w, rtol=tol, atol=tol, msg=lambda m: f"{name}: {m}")
+
+
+@pytest.mark.parametrize("shape", PACKED_SHAPES)
+@pytest.mark.parametrize("multipliers", [(1.0, 1.0), (1.5, 0.5)])
+@pytest.mark.parametrize("dtype,tol", DTYPE_TOL)
+def test_packed_layout_against_the_triton_kernels(ref, shape, multipliers, dtype, tol):
+    from kernels.swiglu import swiglu_packed
+
+    torch.manual_seed(1)
+    gate_up = torch.randn(*shape, device="cuda", dtype=dtype)
+    dout = torch.randn(*shape[:-1], shape[-1] // 2, device="cuda", dtype=dtype)
+    want = _run(ref.swiglu_packed, (gate_up,), dout, *multipliers, True)
+    got = _run(swiglu_packed, (gate_up,), dout, *multipliers, True)
+    for name, g, w in zip(("h", "dgate_up"), got, want):
+        if multipliers == (1.0, 1.0) and dtype != torch.float32:
+            assert_two_ulp(g, w, f"packed {name} vs the reference's Triton kernel")
+        else:
+            torch.testing.assert_close(g, w, rtol=tol, atol=tol, msg=lambda m: f"{name}: {m}")
+
+
+def test_large_bf16_block_against_the_triton_kernels(ref):
+    """4096 token rows of the Llama-3-8B width, N(0,1): every element within 2 ulp, in-place mode."""
+    from kernels.swiglu import swiglu_backward, swiglu_forward
+
+    g = torch.Generator(device="cuda").manual_seed(11)
+    gate, up, dout = (torch.randn(4096, 14336, generator=g, device="cuda").bfloat16() for _ in range(3))
+    h_ref, gate_r, up_r = ref.swiglu_forward(gate.clone(), up.clone())
+    dgate_ref, dup_ref = ref.swiglu_backward(dout, gate_r, up_r)
+    h, gate_o, up_o = swiglu_forward(gate.clone(), up.clone())
+    dgate, dup = swiglu_backward(dout, gate_o, up_o)
+    for name, got, want in (("h", h, h_ref), ("dgate", dgate, dgate_ref), ("dup", dup, dup_ref)):
+        assert_two_ulp(got, want, f"{name} vs the reference's Triton kernel")

@@ -518,23 +518,32 @@ def test_inputs_skewed_against_each_other(dname, offsets, n):
         assert torch.equal(dg2, dgate) and torch.equal(du2, dup)
 
 
-@pytest.mark.parametrize("name", ["c2", "c5"])
+@pytest.mark.parametrize("name", ["c2", "c3", "c3-fp32", "c5"])
 def test_full_size_workloads(name):
-    """The benchmark configurations at their FULL sizes (c2: bf16 [32768, 14336]; c5: bf16 [65536, 28672],
+    """The benchmark configurations at their FULL sizes (c2: bf16 [32768, 14336]; c3: the 16 packed
+    variable-length sequences, [68298, 11008], N(0, 2^2), in bf16 and in fp32; c5: bf16 [65536, 28672],
     3.76 GB per tensor, so byte offsets pass 2^32): sampled token rows from the start, the middle and the very
-    end against the oracle, and size-independent properties -- in place == out of place, a row range computed
-    on its own == the same rows of the whole (the multi-GPU partition), dup linear in dh."""
+    end (for c3 also the first and last token of several sequences) against the oracle, and size-independent
+    properties -- in place == out of place, a row range computed on its own == the same rows of the whole
+    (the multi-GPU partition), dup linear in dh."""
     from kernel_pocs_b200 import workloads as W
 
     w = W.workloads()[name]
-    need = 7 * w.tokens * w.width * 2
+    need = 7 * w.tokens * w.width * torch.empty((), dtype=w.dtype).element_size()
     free, _total = torch.cuda.mem_get_info()
     if free < need + (4 << 30):
         pytest.skip(f"needs {need / 2**30:.0f} GiB of device memory")
     gate, up, dh = W.generate_rows(w, 0, w.tokens, DEVICE)
     h = swiglu_forward(gate, up)[0]
     dgate, dup = swiglu_backward(dh, gate, up, preserve_inputs=True)
-    rows = torch.tensor([0, 1, w.tokens // 2 - 1, w.tokens // 2, w.tokens - 2, w.tokens - 1], device=DEVICE)
+    picks = [0, 1, w.tokens // 2 - 1, w.tokens // 2, w.tokens - 2, w.tokens - 1]
+    if name.startswith("c3"):
+        lens = W.varlen_lengths()
+        assert sum(lens) == w.tokens
+        starts = [sum(lens[:i]) for i in range(len(lens))]
+        for i in (0, 3, 7, 11, 12, 15):  # sequence 11 is the shortest (434 tokens)
+            picks += [starts[i], starts[i] + lens[i] - 1]
+    rows = torch.tensor(sorted(set(picks)), device=DEVICE)
     check_against_oracle(h[rows], dgate[rows], dup[rows], gate[rows].cpu(), up[rows].cpu(), dh[rows].cpu(), 1.0, 1.0,
                          f"{name} sampled rows")
     # a shard of rows that starts beyond the 4 GiB mark (for c5) computed on its own

@@ -75,4 +75,9 @@ def test_no_alloc_entry_matches_the_regular_entry_twice_in_a_row():
                                             None, 0, stream) == 2
     assert lib.swiglu_b200_gemm_fwd_noalloc(got.data_ptr(), x.data_ptr(), wg.data_ptr(), wu.data_ptr(), 0, n, k, gm, dm,
                                             None, 0, stream) == 0
+    # with a status word given, an empty problem reports success there (nothing ran, nothing failed)
+    status_host.fill_(-1)
+    assert lib.swiglu_b200_gemm_fwd_noalloc(got.data_ptr(), x.data_ptr(), wg.data_ptr(), wu.data_ptr(), 0, n, k, gm, dm,
+                                            status_host.data_ptr(), 0, stream) == 0
     torch.cuda.synchronize()
+    assert int(status_host.item()) == 0
