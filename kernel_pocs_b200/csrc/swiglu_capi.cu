@@ -41,7 +41,29 @@ using namespace swiglu_b200;
 #define SWIGLU_SKEW1_BWD_UNROLL 3
 #endif
 #ifndef SWIGLU_LD_RO
-#define SWIGLU_LD_RO LD_NC_NOALLOC  // inputs that this launch never writes
+#define SWIGLU_LD_RO LD_NC_NOALLOC  // backward: inputs that this launch never writes
+#endif
+#ifndef SWIGLU_LD_RO_FWD
+#define SWIGLU_LD_RO_FWD LD_PLAIN   // forward: plain loads measured 1.6 % faster than the no-allocate hint
+#endif                              // (bf16 [32768, 14336]: 7.15 against 7.04 TB/s; fp32 alike)
+// Ragged-row kernels: most warps of one CTA, and the resident CTAs per SM the register budget is set for.  Measured
+// on B200 (bf16, packed gate|up, half-widths 5503 and 11009): the forward is latency-bound and gains from 1536
+// resident threads at 40 registers (6.68 TB/s against 5.6 with 1024 threads at 64 registers); the backward, three
+// windows wide, needs its 64 registers (6.2 / 5.6 TB/s; 5.3 / 5.2 at 40 registers) -- small CTAs in both.
+#ifndef SWIGLU_RAGGED_FWD_WARPS
+#define SWIGLU_RAGGED_FWD_WARPS 4
+#endif
+#ifndef SWIGLU_RAGGED_FWD_CTAS
+#define SWIGLU_RAGGED_FWD_CTAS 12
+#endif
+#ifndef SWIGLU_RAGGED_BWD_WARPS
+#define SWIGLU_RAGGED_BWD_WARPS 4
+#endif
+#ifndef SWIGLU_RAGGED_BWD_CTAS
+#define SWIGLU_RAGGED_BWD_CTAS 8
+#endif
+#ifndef SWIGLU_LD_RAGGED
+#define SWIGLU_LD_RAGGED LD_PLAIN  // ragged-row kernels: neighbouring lanes read overlapping lines, so let L1 keep them
 #endif
 #ifndef SWIGLU_LD_ALIASED
 #define SWIGLU_LD_ALIASED LD_PLAIN  // gate/up when dgate/dup overwrite them
@@ -96,6 +118,9 @@ inline int pow2_divisor(unsigned long long v, int limit) {
 }
 
 struct Plan {
+  bool ragged;  // per-row alignment: 16-byte accesses with skewed loads and a skewed second store (see
+                // swiglu_*_ragged_kernel); chosen when neither the flat nor the pitched 16-byte path applies
+  RaggedShape rshape;
   bool rows;   // 2-D addressing
   bool shift;  // flat, 16-byte body, some input skewed against the outputs (see ld_skewed)
   bool one_word;  // ... and every skew is within 4 bytes of a boundary: one word of a neighbouring granule
@@ -142,23 +167,56 @@ Plan make_plan(const unsigned long long* out, int n_out, const unsigned long lon
         p.one_word = p.one_word && (p.skew[k] <= 4 || p.skew[k] >= 12);
       }
     } else {
-      const int epv = common / es;
-      p.bytes = common;
-      p.shape.n_vec = n / epv;
-      p.shape.head = 0;
-      p.shape.edge = (int)(n - p.shape.n_vec * epv);
-      p.skip = 0;
+      // two outputs skewed against each other: one long ragged row
+      p.ragged = true;
+      p.bytes = kWide;
+      p.rshape.rows = 1;
+      p.rshape.cols = n;
     }
   } else {
     int b = common;
     b = pow2_divisor((unsigned long long)cols * es, b);
     for (int k = 0; k < n_pitch; ++k) b = pow2_divisor((unsigned long long)pitch[k] * es, b);
-    p.bytes = b;
-    p.shape.vecs_per_row = cols * es / b;
-    p.shape.n_vec = rows * p.shape.vecs_per_row;
+    if (b == kWide) {
+      // every row of every tensor starts on a 16-byte boundary and is a whole number of vectors
+      p.bytes = b;
+      p.shape.vecs_per_row = cols * es / b;
+      p.shape.n_vec = rows * p.shape.vecs_per_row;
+    } else {
+      p.ragged = true;
+      p.bytes = kWide;
+      p.rshape.rows = rows;
+      p.rshape.cols = cols;
+    }
     p.skip = 0;
   }
+  if (p.ragged) p.rshape.tasks_per_row = 0;  // set by the launcher
   return p;
+}
+
+// Ragged-row launches: a warp task is 32 frames of 32 bytes of one row; a CTA is up to `max_warps` consecutive
+// tasks of one row, the row's tasks spread evenly over its CTAs so that no warp idles; grid.x walks the row,
+// grid.y and grid.z the rows.
+struct RaggedLaunch {
+  dim3 grid;
+  unsigned block;
+};
+template <class T>
+RaggedLaunch ragged_launch(RaggedShape& s, long long max_warps) {
+  const long long epv = 32 / (long long)sizeof(T);
+  long long tasks = (s.cols / epv + 31) / 32;
+  if (tasks < 1) tasks = 1;  // the row's scalar elements still need a task
+  s.tasks_per_row = (int)tasks;
+  const long long ctas = (tasks + max_warps - 1) / max_warps;
+  const long long warps = (tasks + ctas - 1) / ctas;
+  RaggedLaunch l;
+  l.block = (unsigned)(32 * warps);
+  // rows = y * z as evenly as the 65535 limit of grid.y allows: surplus CTAs (row >= rows) return at once but
+  // still cost a launch slot each
+  const long long z = (s.rows + 65534) / 65535;
+  const long long y = (s.rows + z - 1) / z;
+  l.grid = dim3((unsigned)ctas, (unsigned)y, (unsigned)z);
+  return l;
 }
 
 // ------------------------------------------------------------------ forward dispatch
@@ -168,7 +226,7 @@ int launch_fwd(void* out, const void* gate, const void* up, const Shape& s, floa
   constexpr bool FAST = (sizeof(T) == 2);
   constexpr int UNROLL = SHIFT == 2 ? SWIGLU_SKEW_FWD_UNROLL : SHIFT == 1 ? SWIGLU_SKEW1_FWD_UNROLL : SWIGLU_FWD_UNROLL;
   auto kernel =
-      swiglu_fwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, UNROLL, SWIGLU_LD_RO, SWIGLU_ST, SHIFT, ACT>;
+      swiglu_fwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, UNROLL, SWIGLU_LD_RO_FWD, SWIGLU_ST, SHIFT, ACT>;
   const unsigned grid = grid_for(s.n_vec, SWIGLU_THREADS, UNROLL);
   kernel<<<grid, SWIGLU_THREADS, 0, st>>>(out, gate, up, s, gm, dm);
   cudaError_t err = cudaGetLastError();
@@ -191,7 +249,23 @@ int fwd_by_width(int bytes, void* out, const void* gate, const void* up, const S
 }
 
 template <class T, int ACT>
+int launch_fwd_ragged(void* out, const void* gate, const void* up, const RaggedShape& s, float gm, float dm,
+                      cudaStream_t st) {
+  constexpr bool FAST = (sizeof(T) == 2);
+  auto kernel = swiglu_fwd_ragged_kernel<T, FAST, 32 * SWIGLU_RAGGED_FWD_WARPS, SWIGLU_RAGGED_FWD_CTAS, SWIGLU_LD_RAGGED,
+                                         SWIGLU_ST, ACT>;
+  RaggedShape rs = s;
+  const RaggedLaunch l = ragged_launch<T>(rs, SWIGLU_RAGGED_FWD_WARPS);
+  kernel<<<l.grid, l.block, 0, st>>>(out, gate, up, rs, gm, dm);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda(SWIGLU_B200_ERR_LAUNCH, err);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return SWIGLU_B200_OK;
+}
+
+template <class T, int ACT>
 int fwd_typed(const Plan& p, void* out, const void* gate, const void* up, float gm, float dm, cudaStream_t st) {
+  if (p.ragged) return launch_fwd_ragged<T, ACT>(out, gate, up, p.rshape, gm, dm, st);
   if (p.shift)
     return p.one_word ? launch_fwd<T, ACT, 16, false, 1>(out, gate, up, p.shape, gm, dm, st)
                       : launch_fwd<T, ACT, 16, false, 2>(out, gate, up, p.shape, gm, dm, st);
@@ -230,9 +304,28 @@ int bwd_by_width(int bytes, void* dgate, void* dup, const void* dout, const void
   return SWIGLU_B200_ERR_ALIGN;
 }
 
+template <class T, int ACT, bool INPLACE>
+int launch_bwd_ragged(void* dgate, void* dup, const void* dout, const void* gate, const void* up,
+                      const RaggedShape& s, float gm, float dm, cudaStream_t st) {
+  constexpr bool FAST = (sizeof(T) == 2);
+  constexpr int LD_IO = INPLACE ? SWIGLU_LD_ALIASED : SWIGLU_LD_RAGGED;
+  auto kernel = swiglu_bwd_ragged_kernel<T, FAST, 32 * SWIGLU_RAGGED_BWD_WARPS, SWIGLU_RAGGED_BWD_CTAS, SWIGLU_LD_RAGGED,
+                                         LD_IO, SWIGLU_ST, ACT>;
+  RaggedShape rs = s;
+  const RaggedLaunch l = ragged_launch<T>(rs, SWIGLU_RAGGED_BWD_WARPS);
+  kernel<<<l.grid, l.block, 0, st>>>(dgate, dup, dout, gate, up, rs, gm, dm);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda(SWIGLU_B200_ERR_LAUNCH, err);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return SWIGLU_B200_OK;
+}
+
 template <class T, int ACT>
 int bwd_typed(const Plan& p, bool inplace, void* dgate, void* dup, const void* dout, const void* gate,
               const void* up, float gm, float dm, cudaStream_t st) {
+  if (p.ragged)
+    return inplace ? launch_bwd_ragged<T, ACT, true>(dgate, dup, dout, gate, up, p.rshape, gm, dm, st)
+                   : launch_bwd_ragged<T, ACT, false>(dgate, dup, dout, gate, up, p.rshape, gm, dm, st);
   if (p.shift) {
     if (p.one_word)
       return inplace ? launch_bwd<T, ACT, 16, false, true, 1>(dgate, dup, dout, gate, up, p.shape, gm, dm, st)
@@ -281,6 +374,11 @@ int recompute_by_width(int bytes, bool aliased, void* h, void* dgate, void* dup,
   }
 #undef SWIGLU_RECOMPUTE_CASE
   return SWIGLU_B200_ERR_ALIGN;
+}
+
+inline int plan_code(const Plan& p) {
+  return p.bytes | (p.rows ? 1 << 8 : 0) | (p.shift ? 1 << 9 : 0) | (p.shift && p.one_word ? 1 << 10 : 0) |
+         (p.ragged ? 1 << 11 : 0) | (p.shape.head << 16) | (p.shape.edge << 24);
 }
 
 inline unsigned long long addr_of(const void* p) { return (unsigned long long)(uintptr_t)p; }
@@ -357,6 +455,9 @@ int fwd_entry(void* out, const void* gate, const void* up, int64_t rows, int64_t
   p.shape.pitch_in = in_row_stride * es;
   p.shape.pitch_out = out_row_stride * es;
   p.shape.pitch_grad = 0;
+  p.rshape.pitch_in = p.shape.pitch_in;
+  p.rshape.pitch_out = p.shape.pitch_out;
+  p.rshape.pitch_grad = 0;
   out = advance(out, p.skip);
   gate = advance(gate, p.skip);
   up = advance(up, p.skip);
@@ -416,6 +517,9 @@ int bwd_entry(void* dgate, void* dup, const void* dout, const void* gate, const 
   p.shape.pitch_in = in_row_stride * es;
   p.shape.pitch_out = dout_row_stride * es;
   p.shape.pitch_grad = grad_row_stride * es;
+  p.rshape.pitch_in = p.shape.pitch_in;
+  p.rshape.pitch_out = p.shape.pitch_out;
+  p.rshape.pitch_grad = p.shape.pitch_grad;
   dgate = advance(dgate, p.skip);
   dup = advance(dup, p.skip);
   dout = advance(dout, p.skip);
@@ -518,8 +622,9 @@ int swiglu_b200_geglu_bwd_recompute(void* h, void* dgate, void* dup, const void*
 
 // Reports, without launching anything, how a forward / backward call with these addresses and strides
 // would be executed: bits 0-7 the access width in bytes, bit 8 pitched-row addressing, bit 9 the
-// skewed-load kernel, bit 10 its one-word variant, bits 16-23 the scalar head elements, bits 24-31 head + tail
-// scalar elements.
+// skewed-load kernel, bit 10 its one-word variant, bit 11 the ragged-row kernel (16-byte accesses with the
+// alignment taken row by row and the second output realigned on the way out), bits 16-23 the scalar head
+// elements, bits 24-31 head + tail scalar elements (both zero for the ragged-row kernel, which peels per row).
 // Negative: the argument error the real call would return, negated.
 int swiglu_b200_plan_fwd(const void* out, const void* gate, const void* up, int64_t rows, int64_t cols,
                          int64_t in_row_stride, int64_t out_row_stride, int dtype) {
@@ -531,7 +636,7 @@ int swiglu_b200_plan_fwd(const void* out, const void* gate, const void* up, int6
   const unsigned long long ins[2] = {addr_of(gate), addr_of(up)};
   const long long pitch[2] = {in_row_stride, out_row_stride};
   const Plan p = make_plan(outs, 1, ins, 2, pitch, 2, rows, cols, es);
-  return p.bytes | (p.rows ? 1 << 8 : 0) | (p.shift ? 1 << 9 : 0) | (p.shift && p.one_word ? 1 << 10 : 0) | (p.shape.head << 16) | (p.shape.edge << 24);
+  return plan_code(p);
 }
 
 int swiglu_b200_plan_bwd(const void* dgate, const void* dup, const void* dout, const void* gate, const void* up,
@@ -547,7 +652,7 @@ int swiglu_b200_plan_bwd(const void* dgate, const void* dup, const void* dout, c
   const unsigned long long ins[3] = {addr_of(dout), addr_of(gate), addr_of(up)};
   const long long pitch[3] = {in_row_stride, grad_row_stride, dout_row_stride};
   const Plan p = make_plan(outs, 2, ins, 3, pitch, 3, rows, cols, es);
-  return p.bytes | (p.rows ? 1 << 8 : 0) | (p.shift ? 1 << 9 : 0) | (p.shift && p.one_word ? 1 << 10 : 0) | (p.shape.head << 16) | (p.shape.edge << 24);
+  return plan_code(p);
 }
 
 }  // extern "C"

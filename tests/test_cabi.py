@@ -140,6 +140,9 @@ def _plan(v):
             "edge": (v >> 24) & 0xff}
 
 
+RAGGED = 0x800  # bit 11: 16-byte accesses with per-row alignment (skewed loads, realigned second store)
+
+
 def test_access_planning_without_a_device():
     """Which access width, addressing and edge handling a call would get, from its addresses alone."""
     f, b = _lib.lib.swiglu_b200_plan_fwd, _lib.lib.swiglu_b200_plan_bwd
@@ -162,19 +165,25 @@ def test_access_planning_without_a_device():
     assert f(O, G + 4, U, 4, 4096, 4096, 4096, F32) & 0x400
     assert f(O, G, U, 4, 4096, 4096, 4096, BF) & 0x400 == 0     # aligned: no skewed loads at all
     assert b(G, U, D + 2, G, U, 16, 512, 512, 512, 512, BF) & 0x400 and not b(G, U, D + 10, G, U, 16, 512, 512, 512, 512, BF) & 0x400
-    # packed gate|up: pitched rows; even half-width keeps 16 bytes, an odd one drops to the element size
-    assert _plan(f(O, G, G + 2 * 5504, 8, 5504, 11008, 5504, BF)) == dict(bytes=16, rows=True, shift=False, head=0, edge=0)
-    assert _plan(f(O, G, G + 2 * 257, 3, 257, 514, 257, BF))["bytes"] == 2
-    assert _plan(f(O, G, G + 4 * 257, 3, 257, 514, 257, F32))["bytes"] == 4
-    assert _plan(f(O, G, G + 2 * 260, 3, 260, 520, 260, BF))["bytes"] == 8
+    # packed gate|up: pitched rows; a half-width that is a multiple of 16 bytes keeps plain 16-byte vectors ...
+    code = f(O, G, G + 2 * 5504, 8, 5504, 11008, 5504, BF)
+    assert _plan(code) == dict(bytes=16, rows=True, shift=False, head=0, edge=0) and not code & RAGGED
+    # ... any other takes the ragged-row kernel: still 16-byte accesses, alignment worked out row by row
+    for code in (f(O, G, G + 2 * 257, 3, 257, 514, 257, BF), f(O, G, G + 4 * 257, 3, 257, 514, 257, F32),
+                 f(O, G, G + 2 * 260, 3, 260, 520, 260, BF), f(O + 6, G + 2, G + 2 + 2 * 5503, 9, 5503, 11006, 5503, BF),
+                 b(G, G + 2 * 5503, D, G, G + 2 * 5503, 9, 5503, 11006, 11006, 5503, BF),
+                 b(O, O + 2 * 1001, D + 4, G, G + 2 * 1001, 9, 1001, 2002, 2002, 1001, BF)):
+        assert code & RAGGED and _plan(code) == dict(bytes=16, rows=True, shift=False, head=0, edge=0)
     # a single row is flat whatever its stride says
     assert not _plan(f(O, G, U, 1, 100, 4000, 100, BF))["rows"]
     # backward in place: outputs are gate/up; dh skewed against them -> skewed loads for dh only
     assert _plan(b(G, U, D + 10, G, U, 16, 512, 512, 512, 512, BF)) == dict(bytes=16, rows=False, shift=True, head=0, edge=0)
     # backward out of place with everything congruent
     assert _plan(b(O, O + (1 << 30), D, G, U, 16, 512, 512, 512, 512, BF)) == dict(bytes=16, rows=False, shift=False, head=0, edge=0)
-    # outputs skewed against each other: no common vector start -> narrower accesses
-    assert _plan(b(O, O + (1 << 30) + 4, D, G, U, 16, 512, 512, 512, 512, BF))["bytes"] == 4
+    # outputs skewed against each other: one long ragged row, the second output realigned on the way out
+    code = b(O, O + (1 << 30) + 4, D, G, U, 16, 512, 512, 512, 512, BF)
+    assert code & RAGGED and _plan(code) == dict(bytes=16, rows=False, shift=False, head=0, edge=0)
+    assert not b(O, O + (1 << 30), D, G, U, 16, 512, 512, 512, 512, BF) & RAGGED
     # argument errors come back negated
     c = _codes()
     assert f(O, G, U, 4, 8, 4, 8, BF) == -c["ERR_SHAPE"]

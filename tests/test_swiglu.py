@@ -204,7 +204,8 @@ def test_matches_reference_vectors(golden_dir):
         gate, up, want = (O.from_numpy_bits(z[f"{dname}|{n}"], dtype) for n in ("gate", "up", "h"))
         got = swiglu_forward(gate.to(DEVICE), up.to(DEVICE))[0].cpu()
         assert torch.equal(torch.isnan(got), torch.isnan(want)), dname
-        assert_ulp(got, want, 1, f"special values {dname}")
+        # fp32: exp and a reciprocal good to 1 ulp each, then two products
+        assert_ulp(got, want, 4 if dtype == torch.float32 else 1, f"special values {dname}")
 
 
 def test_config1_fp32(golden_dir):
