@@ -195,6 +195,9 @@ class LoRAMLP(torch.autograd.Function):
     @staticmethod
     def forward(ctx, X, W_gate, A_gate, B_gate, s_gate, W_up, A_up, B_up, s_up, W_down, A_down, B_down, s_down,
                 activation="silu"):
+        if any(t is None for t in (A_gate, B_gate, A_up, B_up, A_down, B_down)):
+            raise ValueError("LoRAMLP differentiates the six adapter matrices: all of them must be given "
+                             "(use lora_mlp() for a forward pass with a projection that has no adapter)")
         out, e, g = _lora_mlp_forward(X, W_gate, A_gate, B_gate, s_gate, W_up, A_up, B_up, s_up, W_down, A_down,
                                       B_down, s_down, save_eg=True, activation=activation)
         ctx.save_for_backward(X, e, g, A_gate, B_gate, A_up, B_up, A_down, B_down)

@@ -191,11 +191,19 @@ def make_lora_mlp_fused_forward(module) -> Callable:
             raise SkipPatch
     from .lora_mlp import LoRAMLP
 
+    # what the block does when its adapters cannot be folded in at call time: route through the (wrapped)
+    # projections, as the reference's own patched forward does
+    routed = make_swiglu_forward(module) if activation == "silu" else make_geglu_forward(module)
+
     def forward(x):
         # tensors are looked up at call time: optimiser steps, .to() moves and adapter switches are seen
-        wg, ag, bg, sg, _ = _lora_parts(module.gate_proj)
-        wu, au, bu, su, _ = _lora_parts(module.up_proj)
-        wd, ad, bd, sd, _ = _lora_parts(module.down_proj)
+        try:
+            wg, ag, bg, sg, _ = _lora_parts(module.gate_proj)
+            wu, au, bu, su, _ = _lora_parts(module.up_proj)
+            wd, ad, bd, sd, _ = _lora_parts(module.down_proj)
+        except SkipPatch:
+            # adapters disabled or merged after patch() (e.g. inside PEFT's ``with model.disable_adapter():``)
+            return routed(x)
         return LoRAMLP.apply(x, wg, ag, bg, sg, wu, au, bu, su, wd, ad, bd, sd, activation)
 
     return forward

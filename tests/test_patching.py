@@ -53,6 +53,8 @@ class FakeLoraLinear(torch.nn.Module):
 
     def forward(self, x):
         a = self.active_adapters[0]
+        if self.disable_adapters:
+            return self.base_layer(x)
         return self.base_layer(x) + self.scaling[a] * self.lora_B[a](self.lora_A[a](self.lora_dropout[a](x)))
 
 
@@ -140,6 +142,33 @@ def test_patch_validates_before_mutating():
     model = tiny_qwen3()
     patching.patch(model, kernels=["fused_gate_up", "swiglu"])
     assert model._forge_patched_counts == {"swiglu": 2}
+
+
+@pytest.mark.gpu
+def test_fused_lora_forward_survives_adapters_disabled_after_patching():
+    """``with model.disable_adapter():`` after patch(): the one-launch LoRA forward can no longer fold the adapters
+    in, so it must route through the wrapped projections (like the reference's own patched forward) instead of
+    letting its skip signal escape from ``module.forward``."""
+    model = wrap_mlps(tiny_qwen3(layers=2)).to(device="cuda", dtype=torch.bfloat16)
+    ids = torch.randint(0, 512, (2, 32), device="cuda", generator=torch.Generator(device="cuda").manual_seed(2))
+    wrappers = [m for m in model.modules() if isinstance(m, FakeLoraLinear)]
+    for w in wrappers:
+        w.disable_adapters = True
+    with torch.no_grad():
+        want = model(ids).logits
+    for w in wrappers:
+        w.disable_adapters = False
+    patching.patch(model, kernels=["lora_mlp_fused", "swiglu"])
+    assert model._forge_patched_counts == {"lora_mlp_fused": 2}
+    with torch.no_grad():
+        with_adapters = model(ids).logits
+    for w in wrappers:
+        w.disable_adapters = True
+    with torch.no_grad():
+        got = model(ids).logits
+    assert float((got.float() - want.float()).abs().max()) < 1.0
+    assert float(torch.nn.functional.cosine_similarity(got.float().flatten(), want.float().flatten(), dim=0)) > 0.999
+    assert not torch.equal(got, with_adapters)
 
 
 @pytest.mark.gpu
