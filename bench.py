@@ -67,6 +67,8 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-strong-c5", action="store_true", help="skip the strong-scaling sub-record")
     ap.add_argument("--c5-steps", type=int, default=10)
+    ap.add_argument("--no-c4", action="store_true", help="skip the fused-GEMM sub-record")
+    ap.add_argument("--c4-reps", type=int, default=20)
     return ap.parse_args()
 
 
@@ -472,6 +474,66 @@ def run_strong_c5(W, swiglu_forward, swiglu_backward, launch_count, device, rank
 
 
 # ---------------------------------------------------------------------------------------------
+# fused gate/up projection + SwiGLU (benchmark configuration c4), beside the unfused sequence
+# ---------------------------------------------------------------------------------------------
+
+def measured_tensor_peaks():
+    try:
+        d = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+        return float(d["bf16_tflops"]), float(d["bf16_tflops_sustained"]), "measured"
+    except Exception:
+        return 1590.0, 1400.0, "fallback"
+
+
+def run_c4_fused_gemm(device, reps: int):
+    """X bf16 [16384, 4096] ~ N(0,1), W_gate and W_up bf16 [14336, 4096] ~ N(0, 0.02^2), seed 3.  The fused tcgen05
+    kernel (one launch: both projections and the activation) and the unfused sequence it replaces (two cuBLAS
+    GEMMs, then this library's SwiGLU kernel) are timed ALTERNATELY in one loop, each call between its own pair of
+    CUDA events, so both see the same clocks under the power cap.  FLOPs: 4*M*N*K."""
+    from kernel_pocs_b200.fused_mlp import check_status, gate_up_swiglu_forward
+    from kernels.swiglu import swiglu_forward
+
+    m, n, k = 16384, 14336, 4096
+    g = torch.Generator(device=device).manual_seed(3)
+    x = torch.randn(m, k, generator=g, device=device).bfloat16()
+    wg = (0.02 * torch.randn(n, k, generator=g, device=device)).bfloat16()
+    wu = (0.02 * torch.randn(n, k, generator=g, device=device)).bfloat16()
+
+    def fused():
+        return gate_up_swiglu_forward(x, wg, wu)
+
+    def unfused():
+        return swiglu_forward(x @ wg.t(), x @ wu.t())[0]
+
+    for _ in range(3):
+        fused(), unfused()
+    check_status(device)
+    times = {"fused": [], "unfused": []}
+    for _ in range(reps):
+        for name, fn in (("fused", fused), ("unfused", unfused)):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            out = fn()
+            b.record()
+            times[name].append((a, b))
+            del out
+    torch.cuda.synchronize(device)
+    check_status(device)
+    ms = {name: sum(a.elapsed_time(b) for a, b in evs) / len(evs) for name, evs in times.items()}
+    burst, sustained, kind = measured_tensor_peaks()
+    flops = 4.0 * m * n * k
+    tf = flops / (ms["fused"] * 1e-3) / 1e12
+    return {
+        "workload": f"c4: X bf16 [{m}, {k}], W_gate/W_up bf16 [{n}, {k}], seed 3; h = silu(X Wg^T) * (X Wu^T)",
+        "kernel": "swiglu_gemm_fwd (tcgen05 CTA pairs, SwiGLU epilogue)", "reps": reps,
+        "ms": ms["fused"], "tflops": tf, "frac_of_bf16_burst": tf / burst, "frac_of_bf16_sustained": tf / sustained,
+        "peaks": {"bf16_tflops": burst, "bf16_tflops_sustained": sustained, "source": kind},
+        "cublas_x2_plus_swiglu_ms": ms["unfused"], "speedup_over_unfused": ms["unfused"] / ms["fused"],
+        "timing": "alternating calls in one loop, one CUDA-event pair per call, mean",
+    }
+
+
+# ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
 
@@ -650,6 +712,14 @@ def main():
         strong = run_strong_c5(W, swiglu_forward, swiglu_backward, _lib.launch_count, device, rank, world,
                                dist if world > 1 else None, barrier, args.c5_steps)
 
+    # ---- the fused projection (a tensor-core kernel: its own roofline), on rank 0 -----------------
+    c4 = None
+    if not args.no_c4:
+        torch.cuda.empty_cache()
+        if rank == 0:
+            c4 = run_c4_fused_gemm(device, args.c4_reps)
+        barrier()
+
     if rank == 0:
         peak, peak_kind = measured_hbm_peak()
         bwd_avg_s = bwd_total / args.steps * 1e-3
@@ -677,6 +747,7 @@ def main():
             "clocks": sampler.summary(mark0, mark1) if sampler else None,
             "e2e": e2e,
             "strong_c5": strong,
+            "c4_fused_gemm": c4,
             "gpu_launches": launches,
             "wall_s_timed_loop_incl_restores": wall,
         }

@@ -423,6 +423,222 @@ swiglu_gemm_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __g
 
 }  // namespace pair
 
+// ------------------------------------------------------------------------------------------
+// Third kernel: CTA pairs with a 256 x 256 tile of h (SWIGLU_B200_GEMM_TILE=wide; see forced_tile() below for
+// what it gains and loses against the 256 x 128 tile).
+//
+// Same scheme as the pair kernel above, but per 16 contraction elements the leader issues TWO MMAs of N = 256 that
+// share the X operand: one against a 256-row tile of Wg (accumulator columns [0, 256) = gate), one against the same
+// rows of Wu (columns [256, 512) = up); each CTA loads its 128 rows of X and its 128-row half of both weight
+// tiles.  Per K block a CTA pulls 48 KiB through L2 for twice the flops of the 32 KiB of the 256 x 128 tile (a
+// quarter fewer operand bytes per flop: the narrow kernel sits past the knee of what one SM can pull through
+// L2).  The price: one 512-column accumulator, so a tile's epilogue no longer hides behind the next tile's MMAs;
+// sixteen epilogue warps (four per TMEM lane quarter, 64 columns of h each) keep that exposed part short.
+// LoRA adapter blocks work as above: both CTAs load their half of [Bg | 0] for the gate MMA and of [0 | Bu] for
+// the up MMA.
+namespace wide {
+
+#ifndef SWIGLU_GEMM_WIDE_STAGES
+#define SWIGLU_GEMM_WIDE_STAGES 4
+#endif
+constexpr int STAGES = SWIGLU_GEMM_WIDE_STAGES;
+constexpr int STAGE_BYTES = 3 * TILE_BYTES;              // X tile + this CTA's half of the Wg tile + of the Wu tile
+constexpr int BNW = 256;                                 // columns of h per pair tile
+constexpr int TMEM_COLS = 512;
+constexpr int BAND = 8;                                  // row-tiles (of 256 rows) per band
+constexpr int EPI_PARTS = 4;                             // epilogue warps per TMEM lane quarter
+constexpr int PART_COLS = BNW / EPI_PARTS;               // columns of h one epilogue warp takes
+constexpr int EPI_COLS = 16;
+constexpr int W_THREADS = 64 + 128 * EPI_PARTS;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+static_assert(SMEM_BYTES <= 227 * 1024, "exceeds the shared memory of an SM");
+constexpr uint32_t IDESC = pair::IDESC;                  // M = 256, N = 256, both operands K-major
+
+struct TileWalk {
+  long long tiles_m, tiles_n, total;
+  __device__ __forceinline__ TileWalk(long long m, long long n)
+      : tiles_m((m + 2 * BM - 1) / (2 * BM)), tiles_n((n + BNW - 1) / BNW), total(tiles_m * tiles_n) {}
+  __device__ __forceinline__ void at(long long t, int& m0, int& n0) const {
+    const long long per_band = (long long)BAND * tiles_n;
+    const long long band = t / per_band;
+    const long long r = t - band * per_band;
+    const long long rows_in_band = (tiles_m - band * BAND) < BAND ? (tiles_m - band * BAND) : BAND;
+    const long long tn = r / rows_in_band;
+    const long long tm = band * BAND + (r - tn * rows_in_band);
+    m0 = (int)(tm * 2 * BM);
+    n0 = (int)(tn * BNW);
+  }
+};
+
+template <int ACT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W_THREADS, 1)
+swiglu_gemm_fwd_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wg,
+                            const __grid_constant__ CUtensorMap map_wu, const __grid_constant__ CUtensorMap map_xa,
+                            const __grid_constant__ CUtensorMap map_bg, const __grid_constant__ CUtensorMap map_bu,
+                            const GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);  // used in the leader only
+  uint64_t* empty = full + STAGES;                                            // one copy per CTA
+  uint64_t* acc_full = empty + STAGES;                                        // one copy per CTA
+  uint64_t* acc_empty = acc_full + 1;                                         // used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cta_rank();
+  const long long pair_id = blockIdx.x >> 1;
+  const long long n_pairs = gridDim.x >> 1;
+  const TileWalk walk(p.m, p.n);
+  const int main_blocks = (int)((p.k + BK - 1) / BK);
+  const int k_blocks = main_blocks + (p.r > 0 ? (2 * p.r + BK - 1) / BK : 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 2);    // one expect_tx arrival from each CTA's producer
+      mbar_init(&empty[s], 1);   // the leader's commit
+    }
+    mbar_init(acc_full, 1);                 // the leader's commit
+    mbar_init(acc_empty, 8 * EPI_PARTS);    // every epilogue warp of both CTAs
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync();  // both CTAs' barriers exist before anyone arrives on them remotely
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      long long it = 0;
+      bool ok = true;
+      for (long long t = pair_id; t < walk.total && ok; t += n_pairs) {
+        int m0, n0;
+        walk.at(t, m0, n0);
+        const int w_row = n0 + (int)rank * BM;  // this CTA's 128 rows of both weight tiles
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = (int)(it % STAGES);
+          if (it >= STAGES) {
+            ok = wait<false>(&empty[s], (uint32_t)((it / STAGES - 1) & 1), p.status, 100 + s);
+            if (!ok) break;
+          }
+          const uint32_t leader_full = map_to_rank(smem_u32(&full[s]), 0);
+          remote_expect_tx(leader_full, STAGE_BYTES);
+          unsigned char* stage = smem + s * STAGE_BYTES;
+          if (kb < main_blocks) {
+            tma_load_2d_pair(stage, &map_x, kb * BK, m0 + (int)rank * BM, leader_full);
+            tma_load_2d_pair(stage + TILE_BYTES, &map_wg, kb * BK, w_row, leader_full);
+            tma_load_2d_pair(stage + 2 * TILE_BYTES, &map_wu, kb * BK, w_row, leader_full);
+          } else {
+            const int c0 = (kb - main_blocks) * BK;  // column of XA' this block starts at
+            tma_load_2d_pair(stage, &map_xa, c0, m0 + (int)rank * BM, leader_full);
+            tma_load_2d_pair(stage + TILE_BYTES, &map_bg, c0, w_row, leader_full);
+            tma_load_2d_pair(stage + 2 * TILE_BYTES, &map_bu, c0 - p.r, w_row, leader_full);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      long long it = 0, i = 0;
+      bool ok = true;
+      for (long long t = pair_id; t < walk.total && ok; t += n_pairs, ++i) {
+        if (i >= 1) {  // the one accumulator must have been drained by every epilogue warp of both CTAs
+          ok = wait<true>(acc_empty, (uint32_t)((i - 1) & 1), p.status, 400);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = (int)(it % STAGES);
+          ok = wait<false>(&full[s], (uint32_t)((it / STAGES) & 1), p.status, 200 + s);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t a_desc = umma_desc(a_addr);
+          const uint64_t g_desc = umma_desc(a_addr + TILE_BYTES);
+          const uint64_t u_desc = umma_desc(a_addr + 2 * TILE_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            umma_pair(tmem_base, a_desc + 2 * kk, g_desc + 2 * kk, IDESC, (kb | kk) != 0);
+            umma_pair(tmem_base + (uint32_t)BNW, a_desc + 2 * kk, u_desc + 2 * kk, IDESC, (kb | kk) != 0);
+          }
+          commit_both(&empty[s]);
+        }
+        if (ok) commit_both(acc_full);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;           // the TMEM lanes a warp may read: 32 * (warp % 4) ..
+    const int part = (warp - 2) >> 2;       // which 64 columns of the tile
+    const Consts cst(p.gm, p.dm);
+    long long i = 0;
+    bool ok = true;
+    for (long long t = pair_id; t < walk.total && ok; t += n_pairs, ++i) {
+      int m0, n0;
+      walk.at(t, m0, n0);
+      ok = wait<false, 200>(acc_full, (uint32_t)(i & 1), p.status, 300);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int row = m0 + (int)rank * BM + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = part * PART_COLS; c < (part + 1) * PART_COLS; c += EPI_COLS) {
+        uint32_t g[EPI_COLS], u[EPI_COLS];
+        tmem_ld16(t_row + c, g);
+        tmem_ld16(t_row + BNW + c, u);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < p.m && n0 + c < p.n) {  // n is a multiple of 16: a group of 16 columns is in or out
+          uint32_t hv[8], gv[8], uv[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+            const float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+            __nv_bfloat162 hb =
+                __floats2bfloat162_rn(Math<true, ACT>::fwd(g0, u0, cst), Math<true, ACT>::fwd(g1, u1, cst));
+            __nv_bfloat162 gb = __floats2bfloat162_rn(g0, g1);
+            __nv_bfloat162 ub = __floats2bfloat162_rn(u0, u1);
+            hv[j] = *reinterpret_cast<uint32_t*>(&hb);
+            gv[j] = *reinterpret_cast<uint32_t*>(&gb);
+            uv[j] = *reinterpret_cast<uint32_t*>(&ub);
+          }
+          const long long off = (long long)row * p.n + n0 + c;
+          uint4* dst = reinterpret_cast<uint4*>(p.h + off);
+          dst[0] = make_uint4(hv[0], hv[1], hv[2], hv[3]);
+          dst[1] = make_uint4(hv[4], hv[5], hv[6], hv[7]);
+          if (p.gate_out) {
+            uint4* dg = reinterpret_cast<uint4*>(p.gate_out + off);
+            dg[0] = make_uint4(gv[0], gv[1], gv[2], gv[3]);
+            dg[1] = make_uint4(gv[4], gv[5], gv[6], gv[7]);
+            uint4* du = reinterpret_cast<uint4*>(p.up_out + off);
+            du[0] = make_uint4(uv[0], uv[1], uv[2], uv[3]);
+            du[1] = make_uint4(uv[4], uv[5], uv[6], uv[7]);
+          }
+        }
+      }
+      // this warp has drained its part of the accumulator: tell the leader's MMA thread
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) remote_arrive(map_to_rank(smem_u32(acc_empty), 0));
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  settle_before_teardown(p.status);
+  cluster_sync();  // the peer's shared memory and TMEM stay alive until the leader's MMAs are done
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+}  // namespace wide
+
 // ------------------------------------------------------------------------------------------ host
 
 std::atomic<uint64_t> g_gemm_launches{0};
@@ -479,7 +695,53 @@ int pair_clusters(int dev, int* out) {
   return SWIGLU_B200_OK;
 }
 
-// Shared by swiglu_b200_gemm_fwd (r = 0) and swiglu_b200_lora_gemm_fwd (adapters of rank r, pair kernel only).
+// Same for the 256 x 256 tile kernel.
+int wide_clusters(int dev, int* out) {
+  static std::atomic<int> cache[64];
+  if (dev < 64) {
+    const int c = cache[dev].load(std::memory_order_acquire);
+    if (c > 0) {
+      *out = c;
+      return SWIGLU_B200_OK;
+    }
+  }
+  if (cudaFuncSetAttribute(wide::swiglu_gemm_fwd_wide_kernel<ACT_SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           wide::SMEM_BYTES) != cudaSuccess ||
+      cudaFuncSetAttribute(wide::swiglu_gemm_fwd_wide_kernel<ACT_GELU_TANH>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, wide::SMEM_BYTES) != cudaSuccess ||
+      cudaFuncSetAttribute(wide::swiglu_gemm_fwd_wide_kernel<ACT_GELU_ERF>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, wide::SMEM_BYTES) != cudaSuccess)
+    return SWIGLU_B200_ERR_DEVICE;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * 148, 1, 1);
+  cfg.blockDim = dim3(wide::W_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = wide::SMEM_BYTES;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, wide::swiglu_gemm_fwd_wide_kernel<ACT_SILU>, &cfg) != cudaSuccess || n < 1)
+    return SWIGLU_B200_ERR_DEVICE;
+  if (dev < 64) cache[dev].store(n, std::memory_order_release);
+  *out = n;
+  return SWIGLU_B200_OK;
+}
+
+// SWIGLU_B200_GEMM_TILE=wide selects the 256 x 256 pair tile; the 256 x 128 tile is the default.  Measured on
+// X [16384, 4096] x W [14336, 4096]^T x 2: 2.64-2.67 ms against 2.66-2.68 ms each timed alone, 2.85 against 2.81 ms
+// interleaved in one loop; on a 4096-row case under ncu the wide tile takes the L2 throughput from 47 % to 35 % and
+// the SM clock from 1.47 to 1.53 GHz, but the tensor pipe is busy 86-87 % of the active cycles with either tile and
+// the wide tile's exposed epilogue takes the elapsed figure from 83 % to 79 %: a draw.
+int forced_tile() {  // read at every call, so that a test can switch it
+  const char* v = getenv("SWIGLU_B200_GEMM_TILE");
+  return !v ? 0 : v[0] == 'n' ? 1 : v[0] == 'w' ? 2 : 0;
+}
+
+// Shared by swiglu_b200_gemm_fwd (r = 0) and swiglu_b200_lora_gemm_fwd (adapters of rank r, pair kernels only).
 int gemm_fwd_impl(void* h, void* gate_out, void* up_out, const void* x, const void* w_gate, const void* w_up,
                   const void* xa_scaled, const void* b_gate, const void* b_up, int64_t m, int64_t n, int64_t k, int r,
                   float gm, float dm, void* status, int device, void* stream, int act = ACT_SILU) {
@@ -537,11 +799,34 @@ int gemm_fwd_impl(void* h, void* gate_out, void* up_out, const void* x, const vo
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
   if (use_pair_kernel() || r > 0 || act != ACT_SILU) {
+    GemmParams pp{static_cast<__nv_bfloat16*>(h), static_cast<__nv_bfloat16*>(gate_out),
+                  static_cast<__nv_bfloat16*>(up_out), static_cast<int*>(status), m, n, k, gm, dm, r};
+    {
+      int wide_resident = 0;
+      const int rcw = wide_clusters(dev, &wide_resident);
+      if (rcw != SWIGLU_B200_OK) return rcw;
+      const long long wide_tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + wide::BNW - 1) / wide::BNW);
+      const int forced = forced_tile();
+      if (forced == 2) {
+        const long long use = wide_tiles < wide_resident ? wide_tiles : wide_resident;
+        const unsigned grid = (unsigned)(2 * use);
+        if (act == ACT_GELU_TANH)
+          wide::swiglu_gemm_fwd_wide_kernel<ACT_GELU_TANH><<<grid, wide::W_THREADS, wide::SMEM_BYTES, st>>>(
+              map_x, map_wg, map_wu, map_xa, map_bg, map_bu, pp);
+        else if (act == ACT_GELU_ERF)
+          wide::swiglu_gemm_fwd_wide_kernel<ACT_GELU_ERF><<<grid, wide::W_THREADS, wide::SMEM_BYTES, st>>>(
+              map_x, map_wg, map_wu, map_xa, map_bg, map_bu, pp);
+        else
+          wide::swiglu_gemm_fwd_wide_kernel<ACT_SILU><<<grid, wide::W_THREADS, wide::SMEM_BYTES, st>>>(
+              map_x, map_wg, map_wu, map_xa, map_bg, map_bu, pp);
+        if (cudaGetLastError() != cudaSuccess) return SWIGLU_B200_ERR_LAUNCH;
+        g_gemm_launches.fetch_add(1, std::memory_order_relaxed);
+        return SWIGLU_B200_OK;
+      }
+    }
     int clusters = 0;
     const int rc = pair_clusters(dev, &clusters);
     if (rc != SWIGLU_B200_OK) return rc;
-    GemmParams pp{static_cast<__nv_bfloat16*>(h), static_cast<__nv_bfloat16*>(gate_out),
-                  static_cast<__nv_bfloat16*>(up_out), static_cast<int*>(status), m, n, k, gm, dm, r};
     const long long pair_tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
     const long long use = pair_tiles < clusters ? pair_tiles : clusters;
     const unsigned grid = (unsigned)(2 * use);

@@ -73,6 +73,57 @@ def test_forward_matches_fp32_reference(m, n, k, gm, dm):
     assert torch.equal(h, h2)
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (1, 16, 8), (300, 272, 200), (257, 528, 72), (1000, 2064, 1032),
+                                   (2048, 1408, 4096), (4500, 384, 256)])
+@pytest.mark.parametrize("gm,dm", [(1.0, 1.0), (0.7, 1.3)])
+def test_wide_tile_kernel_agrees_with_the_narrow_one(m, n, k, gm, dm, monkeypatch):
+    """The 256 x 256 pair tile (two MMAs per step sharing the X operand, one 512-column accumulator, sixteen
+    epilogue warps) is an option (SWIGLU_B200_GEMM_TILE=wide); forced here on small and ragged shapes.
+    Each output element is accumulated over K in the same order by both kernels, so the bits must agree; the
+    fp32 reference bounds both."""
+    x, wg, wu = make(m, n, k, seed=11)
+    monkeypatch.setenv("SWIGLU_B200_GEMM_TILE", "narrow")
+    want = F.gate_up_swiglu_forward(x, wg, wu, gm, dm, save_preactivations=True)
+    monkeypatch.setenv("SWIGLU_B200_GEMM_TILE", "wide")
+    before = _lib.lib.swiglu_b200_gemm_launch_count()
+    got = F.gate_up_swiglu_forward(x, wg, wu, gm, dm, save_preactivations=True)
+    F.check_status(x.device)
+    assert _lib.lib.swiglu_b200_gemm_launch_count() == before + 1
+    for a, b, what in zip(got, want, ("h", "gate", "up")):
+        assert torch.equal(a, b), what
+    ref_h, ref_g, ref_u = reference(x, wg, wu, gm, dm)
+    assert_close_bf16(got[0], ref_h, "h")
+    assert_close_bf16(got[1], ref_g, "gate pre-activation")
+    h_only = F.gate_up_swiglu_forward(x, wg, wu, gm, dm)
+    F.check_status(x.device)
+    assert torch.equal(h_only, got[0])
+
+
+@pytest.mark.parametrize("r", [8, 16, 40, 64])
+@pytest.mark.parametrize("activation", ["silu", "gelu_tanh", "gelu_exact"])
+def test_wide_tile_kernel_with_adapters_and_gelu(r, activation, monkeypatch):
+    m, n, k = 520, 784, 328
+    g = torch.Generator(device=DEVICE).manual_seed(r)
+    mk = lambda *s, std=1.0: (std * torch.randn(*s, generator=g, device=DEVICE)).bfloat16()
+    x, wg, wu = mk(m, k), mk(n, k, std=k ** -0.5), mk(n, k, std=k ** -0.5)
+    ag, au, bg, bu = mk(r, k, std=k ** -0.5), mk(r, k, std=k ** -0.5), mk(n, r, std=0.3), mk(n, r, std=0.3)
+    outs = {}
+    for tile in ("narrow", "wide"):
+        monkeypatch.setenv("SWIGLU_B200_GEMM_TILE", tile)
+        outs[tile] = F.lora_gate_up_swiglu_forward(x, wg, wu, ag, bg, 2.0, au, bu, 0.5, save_eg=True,
+                                                   activation=activation)
+        F.check_status(x.device)
+    for a, b, what in zip(outs["wide"], outs["narrow"], ("h", "e", "g")):
+        assert torch.equal(a, b), what
+    e_ref = x.float() @ wg.float().t() + (x @ (ag * 2.0).t()).float() @ bg.float().t()
+    g_ref = x.float() @ wu.float().t() + (x @ (au * 0.5).t()).float() @ bu.float().t()
+    assert_close_bf16(outs["wide"][1], e_ref, "e")
+    assert_close_bf16(outs["wide"][2], g_ref, "g")
+    act = {"silu": torch.nn.functional.silu, "gelu_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh"),
+           "gelu_exact": torch.nn.functional.gelu}[activation]
+    assert_close_bf16(outs["wide"][0], act(e_ref) * g_ref, "h")
+
+
 def test_leading_dimensions_and_errors():
     x, wg, wu = make(6 * 20, 64, 32)
     h = F.gate_up_swiglu_forward(x.view(6, 20, 32), wg, wu)
