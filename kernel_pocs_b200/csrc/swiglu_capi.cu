@@ -62,6 +62,9 @@ using namespace swiglu_b200;
 #ifndef SWIGLU_RAGGED_BWD_CTAS
 #define SWIGLU_RAGGED_BWD_CTAS 8
 #endif
+#ifndef SWIGLU_SKEWED_AS_RAGGED
+#define SWIGLU_SKEWED_AS_RAGGED 0
+#endif
 #ifndef SWIGLU_LD_RAGGED
 #define SWIGLU_LD_RAGGED LD_PLAIN  // ragged-row kernels: neighbouring lanes read overlapping lines, so let L1 keep them
 #endif
@@ -166,6 +169,16 @@ Plan make_plan(const unsigned long long* out, int n_out, const unsigned long lon
         p.shift = p.shift || p.skew[k] != 0;
         p.one_word = p.one_word && (p.skew[k] <= 4 || p.skew[k] >= 12);
       }
+#if SWIGLU_SKEWED_AS_RAGGED
+      if (p.shift) {
+        // inputs skewed against the outputs: one long ragged row (window loads) instead of the shuffled loads
+        p = Plan{};
+        p.ragged = true;
+        p.bytes = kWide;
+        p.rshape.rows = 1;
+        p.rshape.cols = n;
+      }
+#endif
     } else {
       // two outputs skewed against each other: one long ragged row
       p.ragged = true;
