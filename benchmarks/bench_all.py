@@ -194,7 +194,9 @@ def run_case(name, args, device, rank, world):
             setups = {"forward": state.clear, "backward": fwd, "full": state.clear}
         elif provider == "liger":
             try:
-                import torch.distributed.tensor  # noqa: F401  (liger looks the submodule up as an attribute)
+                import importlib
+
+                importlib.import_module("torch.distributed.tensor")  # liger looks the submodule up as an attribute
                 from liger_kernel.ops.swiglu import LigerSiLUMulFunction
             except Exception as exc:
                 out_rows.append(unavailable_row(name, provider, exc))

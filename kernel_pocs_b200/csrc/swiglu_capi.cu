@@ -31,12 +31,6 @@ using namespace swiglu_b200;
 #ifndef SWIGLU_SKEW_UNROLL
 #define SWIGLU_SKEW_UNROLL 2  // skewed-load kernels keep words of a second granule per vector in registers
 #endif
-#ifndef SWIGLU_SKEW_FWD_UNROLL
-#define SWIGLU_SKEW_FWD_UNROLL 4  // forward: two inputs, so the usual four tile rows still fit 64 registers
-#endif
-#ifndef SWIGLU_SKEW1_FWD_UNROLL
-#define SWIGLU_SKEW1_FWD_UNROLL 4  // one-word variant (every skew within 4 bytes of a boundary)
-#endif
 #ifndef SWIGLU_SKEW1_BWD_UNROLL
 #define SWIGLU_SKEW1_BWD_UNROLL 3
 #endif
@@ -61,9 +55,6 @@ using namespace swiglu_b200;
 #endif
 #ifndef SWIGLU_RAGGED_BWD_CTAS
 #define SWIGLU_RAGGED_BWD_CTAS 8
-#endif
-#ifndef SWIGLU_SKEWED_AS_RAGGED
-#define SWIGLU_SKEWED_AS_RAGGED 0
 #endif
 #ifndef SWIGLU_LD_RAGGED
 #define SWIGLU_LD_RAGGED LD_PLAIN  // ragged-row kernels: neighbouring lanes read overlapping lines, so let L1 keep them
@@ -169,16 +160,17 @@ Plan make_plan(const unsigned long long* out, int n_out, const unsigned long lon
         p.shift = p.shift || p.skew[k] != 0;
         p.one_word = p.one_word && (p.skew[k] <= 4 || p.skew[k] >= 12);
       }
-#if SWIGLU_SKEWED_AS_RAGGED
-      if (p.shift) {
-        // inputs skewed against the outputs: one long ragged row (window loads) instead of the shuffled loads
+      if (p.shift && n_out == 1) {
+        // Forward with inputs skewed against the output: one long ragged row.  Its window loads beat the shuffled
+        // loads of the flat kernel (width 11009, inputs 2 / 8 / 14 bytes off: 7.04 / 7.01 / 6.84 TB/s against
+        // 6.71 / 6.41 / 6.26); the backward, three inputs wide, is faster with the shuffled loads (6.70 / 6.26 /
+        // 6.13 against 6.16 / 6.06 / 5.93) and keeps them.
         p = Plan{};
         p.ragged = true;
         p.bytes = kWide;
         p.rshape.rows = 1;
         p.rshape.cols = n;
       }
-#endif
     } else {
       // two outputs skewed against each other: one long ragged row
       p.ragged = true;
@@ -234,12 +226,12 @@ RaggedLaunch ragged_launch(RaggedShape& s, long long max_warps) {
 
 // ------------------------------------------------------------------ forward dispatch
 
-template <class T, int ACT, int BYTES, bool ROWS, int SHIFT = 0>
+template <class T, int ACT, int BYTES, bool ROWS>
 int launch_fwd(void* out, const void* gate, const void* up, const Shape& s, float gm, float dm, cudaStream_t st) {
   constexpr bool FAST = (sizeof(T) == 2);
-  constexpr int UNROLL = SHIFT == 2 ? SWIGLU_SKEW_FWD_UNROLL : SHIFT == 1 ? SWIGLU_SKEW1_FWD_UNROLL : SWIGLU_FWD_UNROLL;
+  constexpr int UNROLL = SWIGLU_FWD_UNROLL;
   auto kernel =
-      swiglu_fwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, UNROLL, SWIGLU_LD_RO_FWD, SWIGLU_ST, SHIFT, ACT>;
+      swiglu_fwd_kernel<T, BYTES, FAST, ROWS, SWIGLU_THREADS, UNROLL, SWIGLU_LD_RO_FWD, SWIGLU_ST, ACT>;
   const unsigned grid = grid_for(s.n_vec, SWIGLU_THREADS, UNROLL);
   kernel<<<grid, SWIGLU_THREADS, 0, st>>>(out, gate, up, s, gm, dm);
   cudaError_t err = cudaGetLastError();
@@ -279,9 +271,7 @@ int launch_fwd_ragged(void* out, const void* gate, const void* up, const RaggedS
 template <class T, int ACT>
 int fwd_typed(const Plan& p, void* out, const void* gate, const void* up, float gm, float dm, cudaStream_t st) {
   if (p.ragged) return launch_fwd_ragged<T, ACT>(out, gate, up, p.rshape, gm, dm, st);
-  if (p.shift)
-    return p.one_word ? launch_fwd<T, ACT, 16, false, 1>(out, gate, up, p.shape, gm, dm, st)
-                      : launch_fwd<T, ACT, 16, false, 2>(out, gate, up, p.shape, gm, dm, st);
+  if (p.shift) return SWIGLU_B200_ERR_ALIGN;  // not planned for the forward: skewed inputs take the ragged-row kernel
   return p.rows ? fwd_by_width<T, ACT, true>(p.bytes, out, gate, up, p.shape, gm, dm, st)
                 : fwd_by_width<T, ACT, false>(p.bytes, out, gate, up, p.shape, gm, dm, st);
 }

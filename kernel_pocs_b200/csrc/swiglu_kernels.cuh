@@ -521,7 +521,8 @@ struct Shape {
 };
 
 // ---------------------------------------------------------------------------------------
-// Loads for inputs that are misaligned relative to the outputs (flat layout, 16-byte vectors).
+// Loads for inputs that are misaligned relative to the outputs (flat layout, 16-byte vectors; used by the
+// backward -- the forward reads skewed inputs through the ragged-row kernel further down).
 // Vector i of such an input straddles two aligned 16-byte granules.  Every thread loads the first
 // granule of its vector with one aligned access; the second granule is the first granule of vector
 // i+1, which the next lane of the warp loads anyway, so it arrives by shuffle.  Only the last
@@ -639,8 +640,7 @@ struct Locator {
 // the tile, so each warp-wide access is one contiguous 512- or 1024-byte segment.
 // ---------------------------------------------------------------------------------------
 
-template <class T, int BYTES, bool FAST, bool ROWS, int THREADS, int UNROLL, int LDM, int STM, int SHIFT = 0,
-          int ACT = ACT_SILU>
+template <class T, int BYTES, bool FAST, bool ROWS, int THREADS, int UNROLL, int LDM, int STM, int ACT = ACT_SILU>
 __global__ void __launch_bounds__(THREADS, 2)  // two 512-thread CTAs per SM: at most 64 registers
 swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const void* __restrict__ up, Shape s,
                   float gm, float dm) {
@@ -653,21 +653,11 @@ swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const v
     const long long v0 = tile * TILE + threadIdx.x;
     const bool full = (tile + 1) * TILE <= s.n_vec;
     Vec<BYTES> g[UNROLL], u[UNROLL];
-    constexpr int NW = SHIFT ? SHIFT : 1;  // words taken from the next granule (skewed loads only)
-    Vec<4 * NW> g2[SHIFT ? UNROLL : 1], u2[SHIFT ? UNROLL : 1];  // self-fetched starts of the second granules
     long long oo[UNROLL];
 #pragma unroll
     for (int k = 0; k < UNROLL; ++k) {
       const long long i = v0 + (long long)k * THREADS;
-      if constexpr (SHIFT) {
-        static_assert(!SHIFT || (BYTES == 16 && !ROWS), "skewed loads exist for flat 16-byte streams only");
-        static_assert(SHIFT == 0 || SHIFT == 1 || SHIFT == 2, "one or two words of a neighbouring granule");
-        const bool active = full || i < s.n_vec;
-        const bool edge_lane = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec, first_lane = (threadIdx.x & 31) == 0;
-        oo[k] = i * BYTES;
-        ld_skewed_issue<LDM, NW>(gate, oo[k], s.skew_gate, active, edge_lane, first_lane, g[k], g2[k]);
-        ld_skewed_issue<LDM, NW>(up, oo[k], s.skew_up, active, edge_lane, first_lane, u[k], u2[k]);
-      } else if (full || i < s.n_vec) {
+      if (full || i < s.n_vec) {
         long long oi, og;
         Locator<ROWS, BYTES>::at(s, i, oi, oo[k], og);
         g[k] = Ld<BYTES, LDM>::ld(cbyte(gate) + oi);
@@ -677,11 +667,6 @@ swiglu_fwd_kernel(void* __restrict__ out, const void* __restrict__ gate, const v
 #pragma unroll
     for (int k = 0; k < UNROLL; ++k) {
       const long long i = v0 + (long long)k * THREADS;
-      if constexpr (SHIFT) {
-        const bool edge_lane = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec, first_lane = (threadIdx.x & 31) == 0;
-        g[k] = ld_skewed_finish<NW>(g[k], g2[k], s.skew_gate, edge_lane, first_lane);
-        u[k] = ld_skewed_finish<NW>(u[k], u2[k], s.skew_up, edge_lane, first_lane);
-      }
       if (full || i < s.n_vec) {
         float fg[EPV], fu[EPV], fh[EPV];
         Codec<T>::template unpack<BYTES>(g[k], fg);

@@ -156,14 +156,12 @@ def test_access_planning_without_a_device():
     # every tensor 2 bytes past a boundary: 7 head elements, then vectors
     p = _plan(f(O + 2, G + 2, U + 2, 1, 1000, 1000, 1000, BF))
     assert (p["bytes"], p["shift"], p["head"]) == (16, False, 7) and p["edge"] == 7 + (1000 - 7) % 8
-    # inputs skewed against an aligned output: skewed-load kernel, no head
-    assert _plan(f(O, G + 2, U + 6, 4, 4096, 4096, 4096, BF)) == dict(bytes=16, rows=False, shift=True, head=0, edge=0)
-    assert _plan(f(O, G + 4, U, 4, 4096, 4096, 4096, F32)) == dict(bytes=16, rows=False, shift=True, head=0, edge=0)
-    # ... its one-word variant (bit 10) when no input is more than 4 bytes off: one element of any dtype
-    assert f(O, G + 2, U + 6, 4, 4096, 4096, 4096, BF) & 0x400 == 0
-    assert f(O, G + 2, U + 2, 4, 4096, 4096, 4096, BF) & 0x400
-    assert f(O, G + 4, U, 4, 4096, 4096, 4096, F32) & 0x400
-    assert f(O, G, U, 4, 4096, 4096, 4096, BF) & 0x400 == 0     # aligned: no skewed loads at all
+    # forward, inputs skewed against an aligned output: one long ragged row (window loads)
+    for code in (f(O, G + 2, U + 6, 4, 4096, 4096, 4096, BF), f(O, G + 4, U, 4, 4096, 4096, 4096, F32),
+                 f(O, G + 2, U + 2, 4, 4096, 4096, 4096, BF)):
+        assert code & RAGGED and _plan(code) == dict(bytes=16, rows=False, shift=False, head=0, edge=0)
+    assert not f(O, G, U, 4, 4096, 4096, 4096, BF) & (RAGGED | 0x600)     # aligned: plain vectors
+    # backward: the shuffled-load kernel; its one-word variant (bit 10) when no input is more than 4 bytes off
     assert b(G, U, D + 2, G, U, 16, 512, 512, 512, 512, BF) & 0x400 and not b(G, U, D + 10, G, U, 16, 512, 512, 512, 512, BF) & 0x400
     # packed gate|up: pitched rows; a half-width that is a multiple of 16 bytes keeps plain 16-byte vectors ...
     code = f(O, G, G + 2 * 5504, 8, 5504, 11008, 5504, BF)
