@@ -511,7 +511,7 @@ def run_lora(args, device):
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--configs", nargs="+", default=["c1", "c2", "c3", "c3-fp32", "c3+w11009", "c3+w11009-off1"])
-    ap.add_argument("--providers", nargs="+", default=["b200", "b200-safe", "torch-eager"],
+    ap.add_argument("--providers", nargs="+", default=["b200", "b200-safe", "ref-triton-fast", "torch-eager"],
                     choices=["b200", "b200-safe", "b200-packed", "b200-perseq", "torch-eager", "geglu-tanh", "geglu-erf",
                              "ref-triton-fast", "ref-triton-safe", "ref-triton-packed", "liger"])
     ap.add_argument("--modes", nargs="+", default=["forward", "backward", "full"],

@@ -23,10 +23,12 @@
  *   separate gate/up  : in_row_stride == out_row_stride == cols
  *   packed gate|up    : gate = base, up = base + cols, in_row_stride = 2*cols,
  *                       out_row_stride = cols (and dup = dgate + cols in the backward)
- * The widest access that the base addresses, strides and `cols` allow is chosen per call:
- * 16 bytes for contiguous tensors whatever their alignment, as long as the outputs of a call are
- * aligned alike (inputs that are skewed against them are realigned in registers); for pitched rows
- * and for outputs skewed against each other, the widest power of two that fits, down to one element.
+ * Every combination of base addresses, strides and `cols` is served with wide (16- or 32-byte) accesses:
+ * contiguous tensors as one flat stream whatever their alignment (inputs skewed against the outputs are
+ * realigned in registers); pitched rows whose pitch, width and bases are multiples of 16 bytes as 16-byte
+ * vectors; anything else (the packed layout with an odd half-width, outputs skewed against each other) by
+ * kernels that work out the alignment row by row and realign the second output on the way out.  Only the
+ * up to 15 elements at each ragged end of a row (or of the flat stream) are handled one at a time.
  *
  * Aliasing.  In the backward, dgate may equal gate and dup may equal up exactly (same address,
  * same stride): the in-place mode of the reference (swiglu.py:247-248, 310).  No other

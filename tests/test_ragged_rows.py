@@ -2,7 +2,7 @@
 
 The packed gate|up layout with a half-width that is not a multiple of 16 bytes (and, generally, any
 row pitch, width or base address that is not) is served by kernels that work out the alignment row
-by row: aligned 16-byte accesses for the primary output, skewed loads for the inputs, and a second
+by row: aligned 32-byte accesses for the primary output, window loads for the inputs, and a second
 output (dup) whose vectors are realigned across lanes before they are stored.  These tests drive
 ``swiglu_b200_fwd`` / ``swiglu_b200_bwd`` directly with arbitrary pitches and base offsets and hold
 the results to the flat kernels on contiguous copies of the same data, bit for bit (the flat kernels
@@ -170,3 +170,37 @@ def test_large_packed_odd_half_width_in_place():
     assert grad.data_ptr() == gate_up.data_ptr()
     assert torch.equal(grad[:, :half], want_dg) and torch.equal(grad[:, half:], want_du)
     assert torch.equal(full[0], first_row)
+
+
+def test_long_flat_streams_as_one_ragged_row():
+    """Contiguous tensors that cannot share an alignment are one long ragged row: the forward with inputs skewed
+    against its output, the backward with its two outputs skewed against each other.  2^28 + 5 elements (over two
+    million warp tasks in a single row), against the aligned result of the same data."""
+    n = (1 << 28) + 5
+    g = torch.Generator(device=DEVICE).manual_seed(8)
+    base = [torch.randn(n + 16, generator=g, device=DEVICE).bfloat16() for _ in range(3)]
+    aligned = [b[:n].clone() for b in base]
+    want_h = swiglu_forward(aligned[0], aligned[1], 0.9, 1.1)[0]
+    want_dg, want_du = swiglu_backward(aligned[2], aligned[0], aligned[1], 0.9, 1.1, preserve_inputs=True)
+    stream = torch.cuda.current_stream().cuda_stream
+    code = CODE[torch.bfloat16]
+    # forward: gate 1 element off, up 3 elements off, output aligned
+    gate, up, dout = base[0][1:1 + n], base[1][3:3 + n], base[2][5:5 + n]
+    gate.copy_(aligned[0]), up.copy_(aligned[1]), dout.copy_(aligned[2])
+    out = torch.empty(n, dtype=torch.bfloat16, device=DEVICE)
+    assert _lib.lib.swiglu_b200_plan_fwd(out.data_ptr(), gate.data_ptr(), up.data_ptr(), 1, n, n, n, code) & 0x800
+    _lib.check("fwd", _lib.lib.swiglu_b200_fwd(out.data_ptr(), gate.data_ptr(), up.data_ptr(), 1, n, n, n, code, 0.9, 1.1,
+                                               0, stream))
+    assert torch.equal(out, want_h)
+    del out, want_h
+    # backward: dgate aligned, dup 2 elements off, every input at its own offset
+    grads = torch.full((2 * n + 64,), SENTINEL, dtype=torch.bfloat16, device=DEVICE)
+    dg, du = grads[8:8 + n], grads[n + 26:2 * n + 26]
+    assert (dg.data_ptr() - du.data_ptr()) % 16 != 0
+    assert _lib.lib.swiglu_b200_plan_bwd(dg.data_ptr(), du.data_ptr(), dout.data_ptr(), gate.data_ptr(), up.data_ptr(),
+                                         1, n, n, n, n, code) & 0x800
+    _lib.check("bwd", _lib.lib.swiglu_b200_bwd(dg.data_ptr(), du.data_ptr(), dout.data_ptr(), gate.data_ptr(),
+                                               up.data_ptr(), 1, n, n, n, n, code, 0.9, 1.1, 0, stream))
+    assert torch.equal(dg, want_dg) and torch.equal(du, want_du)
+    assert bool((grads[:8] == SENTINEL).all()) and bool((grads[8 + n:n + 26] == SENTINEL).all())
+    assert bool((grads[2 * n + 26:] == SENTINEL).all())
