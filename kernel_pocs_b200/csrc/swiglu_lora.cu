@@ -47,8 +47,10 @@ constexpr int TN = 64;                          // output columns per tile (one 
 #endif
 constexpr int TILES_PER_RANGE = SWIGLU_LORA_TILES_PER_RANGE;  // 64-column tiles per work item
 constexpr int EG_BYTES = TM * TN * 2;           // 16 KiB
-constexpr int OUT_BUFS_PER_GROUP = 2;           // h tiles of one epilogue group waiting for their bulk store
-constexpr int TMEM_COLS = 256;                  // 2 buffers x (64 gate + 64 up) fp32 columns
+#ifndef SWIGLU_LORA_OUT_BUFS
+#define SWIGLU_LORA_OUT_BUFS 2
+#endif
+constexpr int OUT_BUFS_PER_GROUP = SWIGLU_LORA_OUT_BUFS;  // h tiles of one epilogue group waiting for their bulk store
 #ifndef SWIGLU_LORA_EPI_WARPS
 #define SWIGLU_LORA_EPI_WARPS 16
 #endif
@@ -57,6 +59,12 @@ constexpr int EPI_WARPS = SWIGLU_LORA_EPI_WARPS;  // EPI_WARPS / 4 warps share a
 #define SWIGLU_LORA_GROUPS 2
 #endif
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
+// accumulator buffers in TMEM, (64 gate + 64 up) fp32 columns each: one per epilogue group, at least two
+constexpr int ACC_BUFS = SWIGLU_LORA_GROUPS > 2 ? SWIGLU_LORA_GROUPS : 2;
+constexpr int TMEM_COLS = ACC_BUFS * 128 <= 256 ? 256 : 512;
+#ifndef SWIGLU_LORA_STAGES16
+#define SWIGLU_LORA_STAGES16 4
+#endif
 // kind::f16, D fp32, A and B bf16 K-major, M = 128, N = 64
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
 
@@ -72,12 +80,12 @@ struct Cfg {
   static constexpr int B_BYTES = TN * RK * 2;
   static constexpr int STAGE_BYTES = 2 * EG_BYTES + 2 * B_BYTES;
   static constexpr int GROUPS = RK == 64 ? 1 : SWIGLU_LORA_GROUPS;
-  static constexpr int STAGES = RK == 16 ? 4 : 3;
+  static constexpr int STAGES = RK == 16 ? SWIGLU_LORA_STAGES16 : 3;
   static constexpr int OUT_BUFS = GROUPS * OUT_BUFS_PER_GROUP;
   static constexpr int GROUP_WARPS = EPI_WARPS / GROUPS;
   static constexpr int CW = 64 / (GROUP_WARPS / 4);  // columns of a tile handled by one warp
   static constexpr int SMEM_BYTES = 2 * XA_BYTES + STAGES * STAGE_BYTES + OUT_BUFS * EG_BYTES + 1024 + 256;
-  static_assert(GROUPS == 1 || GROUPS == 2, "one or two epilogue groups");
+  static_assert(GROUPS >= 1 && GROUPS <= 3 && EPI_WARPS % (4 * GROUPS) == 0, "one to three epilogue groups");
   static_assert(CW == 16 || CW == 32, "a warp reads 16 or 32 TMEM columns per accumulator");
   static_assert(SMEM_BYTES <= 227 * 1024, "exceeds the shared memory of an SM");
 };
@@ -123,9 +131,9 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
   unsigned char* outs = ring + STAGES * STAGE_BYTES;
   uint64_t* full = reinterpret_cast<uint64_t*>(outs + OUT_BUFS * EG_BYTES);
   uint64_t* empty = full + STAGES;        // MMA commit + one epilogue thread
-  uint64_t* acc_full = empty + STAGES;    // [2]
-  uint64_t* acc_empty = acc_full + 2;     // [2], every warp of the group that reads the buffer
-  uint64_t* xa_full = acc_empty + 2;
+  uint64_t* acc_full = empty + STAGES;            // [ACC_BUFS]
+  uint64_t* acc_empty = acc_full + ACC_BUFS;      // [ACC_BUFS], every warp of the group that reads the buffer
+  uint64_t* xa_full = acc_empty + ACC_BUFS;
   uint64_t* xa_empty = xa_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xa_empty + 1);
 
@@ -141,9 +149,9 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 2);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < ACC_BUFS; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], GROUP_WARPS);  // with two groups, buffer b is read by group b only
+      mbar_init(&acc_empty[b], GROUP_WARPS);  // with several groups, buffer b is read by group b only
     }
     mbar_init(xa_full, 1);
     mbar_init(xa_empty, 1);
@@ -205,9 +213,9 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
         if (!ok) break;
         for (long long t = t_lo; t < t_hi; ++t, ++it) {
           const int s = (int)(it % STAGES);
-          const int b = (int)(it & 1);
-          if (it >= 2) {
-            ok = mbar_wait(&acc_empty[b], (uint32_t)(((it >> 1) - 1) & 1), p.status, 400 + b);
+          const int b = (int)(it % ACC_BUFS);
+          if (it >= ACC_BUFS) {
+            ok = mbar_wait(&acc_empty[b], (uint32_t)((it / ACC_BUFS - 1) & 1), p.status, 400 + b);
             if (!ok) break;
           }
           ok = mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1), p.status, 200 + s);
@@ -245,15 +253,15 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
       for (long long t = t_lo; t < t_hi; ++t, ++it) {
         if (GROUPS > 1 && (int)(it % GROUPS) != group) continue;
         const int s = (int)(it % STAGES);
-        const int b = (int)(it & 1);
+        const int b = (int)(it % ACC_BUFS);
         unsigned char* e_tile = ring + s * STAGE_BYTES;
         unsigned char* g_tile = e_tile + EG_BYTES;
         // Two h buffers per group: before the group's barrier of this tile its storing thread has waited for
         // the store of the previous tile to finish reading, so the next tile may overwrite that buffer.
-        unsigned char* h_tile = outs + (group * OUT_BUFS_PER_GROUP + (mine & 1)) * EG_BYTES;
+        unsigned char* h_tile = outs + (group * OUT_BUFS_PER_GROUP + (mine % OUT_BUFS_PER_GROUP)) * EG_BYTES;
         ++mine;
         ok = mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1), p.status, 600 + s) &&
-             mbar_wait(&acc_full[b], (uint32_t)((it >> 1) & 1), p.status, 300 + b);
+             mbar_wait(&acc_full[b], (uint32_t)((it / ACC_BUFS) & 1), p.status, 300 + b);
         if (!__all_sync(0xffffffffu, ok)) ok = false;  // warp-uniform, for the warp-wide TMEM loads
         if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -394,10 +402,12 @@ int swiglu_b200_lora_swiglu_fwd(void* h, void* e_out, void* g_out, const void* e
     };
     set(lora_swiglu_kernel<16, false>, Cfg<16>::SMEM_BYTES);
     set(lora_swiglu_kernel<16, true>, Cfg<16>::SMEM_BYTES);
+#ifndef SWIGLU_LORA_ONLY16  // (tuning builds compile the rank-16 layout alone)
     set(lora_swiglu_kernel<32, false>, Cfg<32>::SMEM_BYTES);
     set(lora_swiglu_kernel<32, true>, Cfg<32>::SMEM_BYTES);
     set(lora_swiglu_kernel<64, false>, Cfg<64>::SMEM_BYTES);
     set(lora_swiglu_kernel<64, true>, Cfg<64>::SMEM_BYTES);
+#endif
     if (!attr_ok) return SWIGLU_B200_ERR_DEVICE;
     if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm < 1)
       return SWIGLU_B200_ERR_DEVICE;
@@ -415,10 +425,15 @@ int swiglu_b200_lora_swiglu_fwd(void* h, void* e_out, void* g_out, const void* e
   };
   if (rk == 16)
     save ? launch(lora_swiglu_kernel<16, true>, Cfg<16>::SMEM_BYTES) : launch(lora_swiglu_kernel<16, false>, Cfg<16>::SMEM_BYTES);
+#ifndef SWIGLU_LORA_ONLY16
   else if (rk == 32)
     save ? launch(lora_swiglu_kernel<32, true>, Cfg<32>::SMEM_BYTES) : launch(lora_swiglu_kernel<32, false>, Cfg<32>::SMEM_BYTES);
   else
     save ? launch(lora_swiglu_kernel<64, true>, Cfg<64>::SMEM_BYTES) : launch(lora_swiglu_kernel<64, false>, Cfg<64>::SMEM_BYTES);
+#else
+  else
+    return SWIGLU_B200_ERR_SHAPE;
+#endif
   if (cudaGetLastError() != cudaSuccess) return SWIGLU_B200_ERR_LAUNCH;
   g_lora_launches.fetch_add(1, std::memory_order_relaxed);
   return SWIGLU_B200_OK;
