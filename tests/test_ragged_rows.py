@@ -204,3 +204,24 @@ def test_long_flat_streams_as_one_ragged_row():
     assert torch.equal(dg, want_dg) and torch.equal(du, want_du)
     assert bool((grads[:8] == SENTINEL).all()) and bool((grads[8 + n:n + 26] == SENTINEL).all())
     assert bool((grads[2 * n + 26:] == SENTINEL).all())
+
+
+@pytest.mark.parametrize("approximate", ["tanh", "none"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_geglu_sibling_on_ragged_rows(approximate, dtype):
+    """The GeGLU operator shares the ragged-row kernels (the activation is a template argument): packed layout,
+    odd half-width, misaligned base, in place and out of place, against its own separate-layout result."""
+    from kernels.geglu import geglu_backward, geglu_forward, geglu_packed_backward, geglu_packed_forward
+
+    rows, half, offset = 41, 1001, 3
+    g = torch.Generator(device=DEVICE).manual_seed(17)
+    gate0, up0, dout = (1.5 * torch.randn(rows, half, generator=g, device=DEVICE).to(dtype) for _ in range(3))
+    want_h = geglu_forward(gate0.clone(), up0.clone(), approximate)[0]
+    want_dg, want_du = geglu_backward(dout, gate0.clone(), up0.clone(), approximate, preserve_inputs=True)
+    for preserve in (True, False):
+        src = Pitched(rows, 2 * half, 2 * half, offset, dtype, torch.cat([gate0, up0], dim=1))
+        h, saved = geglu_packed_forward(src.view, approximate)
+        assert torch.equal(h, want_h)
+        grad = geglu_packed_backward(dout, saved, src.view.shape, approximate, preserve_inputs=preserve)
+        assert torch.equal(grad[:, :half], want_dg) and torch.equal(grad[:, half:], want_du)
+        assert src.untouched()

@@ -303,11 +303,12 @@ def test_non_contiguous_inputs(dname):
 
 
 @pytest.mark.parametrize("dname", ["bf16", "fp16", "fp32"])
-@pytest.mark.parametrize("half_width", [1, 5, 128, 257, 1000, 5504])
+@pytest.mark.parametrize("half_width", [1, 3, 5, 128, 257, 1000, 1001, 5503, 5504])
 @pytest.mark.parametrize("preserve_inputs", [False, True])
 def test_packed_widths(dname, half_width, preserve_inputs):
     """Packed gate|up with odd half-widths: the up half of every row is misaligned relative to
-    the gate half, which the reference only exercises at width 257."""
+    the gate half, which the reference only exercises at width 257 (the ragged-row kernels; bases
+    that are misaligned as well are in tests/test_ragged_rows.py)."""
     dtype = DTYPES[dname]
     g = torch.Generator().manual_seed(9)
     rows = 11
