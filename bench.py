@@ -416,7 +416,7 @@ def run_strong_c5(W, swiglu_forward, swiglu_backward, launch_count, device, rank
 
     for _ in range(3):
         restore()
-        step()
+        h, dgate, dup = step()  # kept, as in the timed loop: the allocator then already owns the second h buffer
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     barrier()
     launches0 = launch_count()
@@ -428,8 +428,8 @@ def run_strong_c5(W, swiglu_forward, swiglu_backward, launch_count, device, rank
     barrier()
     launches = launch_count() - launches0
     per_step = sorted(a.elapsed_time(b) for a, b in evs)
-    # the median: freshly allocated multi-gigabyte buffers cost one step of a rank a stall of 10-25 ms now and then
-    # (seen once per run, on one step, at some shard sizes); the mean is reported beside it
+    # the median, so that a one-off host stall inside a step (a cudaMalloc of the caching allocator, say) does not
+    # decide the figure; the mean is reported beside it
     mine_ms = per_step[len(per_step) // 2] if len(per_step) % 2 else 0.5 * (per_step[len(per_step) // 2 - 1] + per_step[len(per_step) // 2])
     mine_mean_ms = sum(per_step) / steps
     probe = min(64, hi - lo)
