@@ -29,7 +29,7 @@ using namespace swiglu_b200;
 #define SWIGLU_BWD_UNROLL 2
 #endif
 #ifndef SWIGLU_SKEW_UNROLL
-#define SWIGLU_SKEW_UNROLL 2  // skewed-load kernels keep words of a second granule per vector in registers
+#define SWIGLU_SKEW_UNROLL 3  // skewed-load kernels keep words of a second granule per vector in registers
 #endif
 #ifndef SWIGLU_SKEW1_BWD_UNROLL
 #define SWIGLU_SKEW1_BWD_UNROLL 3

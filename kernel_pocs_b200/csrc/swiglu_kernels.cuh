@@ -523,12 +523,14 @@ struct Shape {
 // ---------------------------------------------------------------------------------------
 // Loads for inputs that are misaligned relative to the outputs (flat layout, 16-byte vectors; used by the
 // backward -- the forward reads skewed inputs through the ragged-row kernel further down).
-// Vector i of such an input straddles two aligned 16-byte granules.  Every thread loads the first
-// granule of its vector with one aligned access; the second granule is the first granule of vector
-// i+1, which the next lane of the warp loads anyway, so it arrives by shuffle.  Only the last
-// lane of a warp (and the owner of the launch's last vector) fetches its second granule itself.
-// The two granules are then funnel-shifted into place.  Bytes outside the tensor that share a
-// granule with its first or last element are read and discarded.
+// Vector i of such an input straddles two aligned 16-byte granules.  Every thread loads the granule its
+// vector mostly lies in with one aligned access, plus the one or two 32-bit words of the neighbouring granule
+// that complete it: the adjacent lane loads that granule as its own, so the second access hits L1 (skewed
+// inputs are therefore read with plain, L1-allocating loads).  The words are then funnel-shifted into place.
+// Bytes outside the tensor that share a granule with its first or last element are read and discarded.
+// (Passing the neighbouring words between lanes by shuffle instead, with the warp's edge lanes fetching their
+// own, was 4-10 % slower: width 11009, dh/gate/up 2 / 8 / 14 bytes off: 6.71 / 6.26 / 6.09 TB/s against
+// 6.99 / 6.71 / 6.70 now.)
 // ---------------------------------------------------------------------------------------
 
 static __device__ __forceinline__ const char* cbyte(const void* p) { return static_cast<const char*>(p); }
@@ -559,55 +561,44 @@ __device__ __forceinline__ Vec<16> funnel16(const Vec<16>& lo, const Vec<16>& hi
   return o;
 }
 
-// NW = how many 32-bit words of a NEIGHBOURING granule a vector takes besides its main granule.  The main
-// granule is the one the vector starts in when the skew is at most 8 bytes (the words come from the NEXT granule)
-// and the one it ends in otherwise (the words are the last ones of the PREVIOUS granule), so two words always
-// suffice (NW = 2).  NW = 1 serves launches whose inputs are all within 4 bytes of a boundary in either direction
-// (one element off, the common case).  Few words are cheap in registers (the part a lane fetches for itself
-// when it has no neighbour), in shuffles, and leave room for more loads in flight.
+// NW = how many 32-bit words of the NEIGHBOURING granule a vector takes besides its main granule.  The main
+// granule is the one the vector starts in when the skew is at most 8 bytes (the words are the first of the NEXT
+// granule) and the one it ends in otherwise (the last words of the PREVIOUS granule), so two words always suffice
+// (NW = 2).  NW = 1 serves launches whose inputs are all within 4 bytes of a boundary in either direction (one
+// element off, the common case) and leaves registers for one more tile row in flight.
 //
-// Phase 1, with the other loads of the tile: `base` is the input's body pointer (misaligned by `skew`
-// bytes), `off` the byte offset of vector i in the outputs.  Loads the main granule into `lo` and, for the lanes
-// that cannot get the neighbouring words from another lane, those into `own`.  `edge_lane`: lane 31 or the
-// last vector (it has no next lane), `first_lane`: lane 0 (it has no previous lane).
+// Phase 1, with the other loads of the tile: `base` is the input's body pointer (misaligned by `skew` bytes), `off`
+// the byte offset of vector i in the outputs.  LDM is the load mode of an input that is not skewed.
 template <int LDM, int NW>
-__device__ __forceinline__ void ld_skewed_issue(const void* base, long long off, int skew, bool active,
-                                                bool edge_lane, bool first_lane, Vec<16>& lo, Vec<4 * NW>& own) {
+__device__ __forceinline__ void ld_skewed_issue(const void* base, long long off, int skew, bool active, Vec<16>& lo,
+                                                Vec<4 * NW>& nb) {
   lo = Vec<16>{};
-  own = Vec<4 * NW>{};
-  const char* granule = cbyte(base) - skew + off;  // the aligned granule the vector starts in
+  nb = Vec<4 * NW>{};
   if (!active) return;
-  if (skew == 0) {
+  const char* granule = cbyte(base) - skew + off;  // the aligned granule the vector starts in
+  if (skew == 0) {  // uniform over the launch, like the branches below
     lo = Ld<16, LDM>::ld(granule);
   } else if (skew > 8) {
-    lo = Ld<16, LDM>::ld(granule + 16);
-    if (first_lane) own = Ld<4 * NW, LDM>::ld(granule + 16 - 4 * NW);
+    nb = Ld<4 * NW, LD_PLAIN>::ld(granule + 16 - 4 * NW);
+    lo = Ld<16, LD_PLAIN>::ld(granule + 16);
   } else {
-    lo = Ld<16, LDM>::ld(granule);
-    if (edge_lane) own = Ld<4 * NW, LDM>::ld(granule + 16);
+    lo = Ld<16, LD_PLAIN>::ld(granule);
+    nb = Ld<4 * NW, LD_PLAIN>::ld(granule + 16);
   }
 }
 
-// Phase 2, after every load of the tile has been issued (a shuffle waits for its operand, so doing
-// this between the loads would serialise them).  All 32 lanes must call this together.
+// Phase 2, after every load of the tile has been issued.
 template <int NW>
-__device__ __forceinline__ Vec<16> ld_skewed_finish(const Vec<16>& lo, const Vec<4 * NW>& own, int skew,
-                                                    bool edge_lane, bool first_lane) {
-  if (skew == 0) return lo;  // uniform over the launch
+__device__ __forceinline__ Vec<16> ld_skewed_finish(const Vec<16>& lo, const Vec<4 * NW>& nb, int skew) {
+  if (skew == 0) return lo;
   Vec<16> other{};
   if (skew > 8) {
 #pragma unroll
-    for (int i = 0; i < NW; ++i) {
-      other.w[4 - NW + i] = __shfl_up_sync(0xffffffffu, lo.w[4 - NW + i], 1);
-      if (first_lane) other.w[4 - NW + i] = own.w[i];
-    }
+    for (int i = 0; i < NW; ++i) other.w[4 - NW + i] = nb.w[i];
     return funnel16(other, lo, skew);
   }
 #pragma unroll
-  for (int i = 0; i < NW; ++i) {
-    other.w[i] = __shfl_down_sync(0xffffffffu, lo.w[i], 1);
-    if (edge_lane) other.w[i] = own.w[i];
-  }
+  for (int i = 0; i < NW; ++i) other.w[i] = nb.w[i];
   return funnel16(lo, other, skew);
 }
 
@@ -730,11 +721,10 @@ swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const v
       if constexpr (SHIFT) {
         static_assert(!SHIFT || (BYTES == 16 && !ROWS), "skewed loads exist for flat 16-byte streams only");
         const bool active = full || i < s.n_vec;
-        const bool edge_lane = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec, first_lane = (threadIdx.x & 31) == 0;
         og[k] = i * BYTES;
-        ld_skewed_issue<LDM_DH, NW>(dout, og[k], s.skew_dout, active, edge_lane, first_lane, d[k], d2[k]);
-        ld_skewed_issue<LDM_IO, NW>(gate, og[k], s.skew_gate, active, edge_lane, first_lane, g[k], g2[k]);
-        ld_skewed_issue<LDM_IO, NW>(up, og[k], s.skew_up, active, edge_lane, first_lane, u[k], u2[k]);
+        ld_skewed_issue<LDM_DH, NW>(dout, og[k], s.skew_dout, active, d[k], d2[k]);
+        ld_skewed_issue<LDM_IO, NW>(gate, og[k], s.skew_gate, active, g[k], g2[k]);
+        ld_skewed_issue<LDM_IO, NW>(up, og[k], s.skew_up, active, u[k], u2[k]);
       } else if (full || i < s.n_vec) {
         long long oi, oo;
         Locator<ROWS, BYTES>::at(s, i, oi, oo, og[k]);
@@ -749,10 +739,9 @@ swiglu_bwd_kernel(void* dgate, void* dup, const void* __restrict__ dout, const v
     for (int k = 0; k < UNROLL; ++k) {
       const long long i = v0 + (long long)k * THREADS;
       if constexpr (SHIFT) {
-        const bool edge_lane = (threadIdx.x & 31) == 31 || i + 1 >= s.n_vec, first_lane = (threadIdx.x & 31) == 0;
-        d[k] = ld_skewed_finish<NW>(d[k], d2[k], s.skew_dout, edge_lane, first_lane);
-        g[k] = ld_skewed_finish<NW>(g[k], g2[k], s.skew_gate, edge_lane, first_lane);
-        u[k] = ld_skewed_finish<NW>(u[k], u2[k], s.skew_up, edge_lane, first_lane);
+        d[k] = ld_skewed_finish<NW>(d[k], d2[k], s.skew_dout);
+        g[k] = ld_skewed_finish<NW>(g[k], g2[k], s.skew_gate);
+        u[k] = ld_skewed_finish<NW>(u[k], u2[k], s.skew_up);
       }
       if (full || i < s.n_vec) {
         float fd[EPV], fg[EPV], fu[EPV], fdg[EPV], fdu[EPV];
