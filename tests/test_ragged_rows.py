@@ -63,8 +63,8 @@ def test_random_pitches_offsets_and_modes():
         rows = int(rng.choice([1, 2, 3, 7, 33, 70]))
         cols = int(rng.choice(widths)) if rng.random() < 0.8 else int(rng.integers(1, 3000))
         gm, dm = (1.0, 1.0) if rng.random() < 0.5 else (float(rng.uniform(0.5, 1.5)), float(rng.uniform(0.5, 1.5)))
-        extra = lambda: int(rng.choice([0, 0, 1, 3, 8, 13]))
-        off = lambda: int(rng.integers(0, 9))
+        extra = lambda: int(rng.choice([0, 0, 1, 3, 8, 13, 17, 29]))
+        off = lambda: int(rng.integers(0, 34))  # up to 33 elements: every skew against a 32-byte frame occurs
         g = torch.Generator(device=DEVICE).manual_seed(case)
         gate0, up0, dout0 = (1.5 * torch.randn(rows, cols, generator=g, device=DEVICE).to(dtype) for _ in range(3))
         want_h, want_dg, want_du = flat_reference(gate0, up0, dout0, gm, dm)
