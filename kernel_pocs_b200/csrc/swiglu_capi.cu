@@ -43,7 +43,8 @@ using namespace swiglu_b200;
 // Ragged-row kernels: most warps of one CTA, and the resident CTAs per SM the register budget is set for.  Measured
 // on B200 (bf16, packed gate|up, half-widths 5503 and 11009): the forward is latency-bound and gains from 1536
 // resident threads at 40 registers (6.68 TB/s against 5.6 with 1024 threads at 64 registers); the backward, three
-// windows wide, needs its 64 registers (6.2 / 5.6 TB/s; 5.3 / 5.2 at 40 registers) -- small CTAs in both.
+// windows wide, does best with nine CTAs at 56 registers (6.38 / 5.81 TB/s; 6.20 / 5.63 with eight at 64, 6.01 / 5.34
+// with seven, 5.3 / 5.2 at 40 registers) -- small CTAs in both.
 #ifndef SWIGLU_RAGGED_FWD_WARPS
 #define SWIGLU_RAGGED_FWD_WARPS 4
 #endif
@@ -54,7 +55,7 @@ using namespace swiglu_b200;
 #define SWIGLU_RAGGED_BWD_WARPS 4
 #endif
 #ifndef SWIGLU_RAGGED_BWD_CTAS
-#define SWIGLU_RAGGED_BWD_CTAS 8
+#define SWIGLU_RAGGED_BWD_CTAS 9
 #endif
 #ifndef SWIGLU_LD_RAGGED
 #define SWIGLU_LD_RAGGED LD_PLAIN  // ragged-row kernels: neighbouring lanes read overlapping lines, so let L1 keep them
