@@ -12,15 +12,21 @@
 // cost 4*r flops per output, too many for the fp32 pipes at that rate (64 flop per 6 bytes at r = 16); they
 // go to the tcgen05 tensor cores, and all the traffic goes through the TMA engine:
 //
-//   * A CTA owns 128 token rows and walks a range of 64-column tiles.  XAg / XAu tiles (128 rows, rank
-//     padded to 16, 32 or 64 by the loads' zero fill) are loaded once per range.
-//   * Per tile the producer warp loads E, G (128 x 64) and Bg, Bu (64 rows) into a 3- or 4-stage ring.  One
-//     thread issues two M=128, N=64 MMAs per 16 ranks into TMEM (double buffered), which yield the adapter
-//     terms in the row-per-thread layout the epilogue reads.
-//   * Sixteen epilogue warps, as two groups of eight that take alternate tiles (two warps per TMEM lane
-//     quarter, 32 columns each), add the terms to E and G taken from the swizzled shared-memory tiles, apply
-//     SwiGLU in fp32, write h (and e, g in place over the staged tiles) back to shared memory, and one
-//     thread per group stores the tiles with bulk tensor stores, which also clip at the matrix edge.
+//   * Work is cut into tiles of 128 token rows x 64 columns, numbered along the rows of the matrix.  The CTAs
+//     (one per SM) take short runs of consecutive tiles in turn, so that together they read and write one
+//     contiguous band of E, G and h at any moment: the order of the work alone is worth 10 % of bandwidth.
+//   * Per tile one thread loads E, G (128 x 64) and Bg, Bu (64 rows) into a ring of stages that takes all the
+//     shared memory left (3 to 5 stages); XAg / XAu tiles (128 rows, rank padded to 16, 32 or 64 by the loads'
+//     zero fill) change with the row tile and have a small ring of their own.  One thread issues two M=128,
+//     N=64 MMAs per 16 ranks into TMEM (double buffered), which yield the adapter terms in the
+//     row-per-thread layout the epilogue reads.
+//   * Sixteen epilogue warps (four per TMEM lane quarter; all on one tile, or two sets of eight on alternate
+//     tiles) add the terms to E and G taken from the swizzled shared-memory tiles, apply SwiGLU in fp32 and
+//     write the results back into the stage: h over E, or, when e and g are wanted, e and g over E and G and
+//     h into a third tile of the stage.  Each warp reports its part of a tile on the stage's mbarrier; the
+//     warps never wait for one another.
+//   * One thread stores finished tiles with bulk tensor stores, which also clip at the matrix edge, and
+//     returns a stage to the loads when its stores have read it.
 // No load uses cluster multicast.  Every mbarrier wait is bounded; a wait that gives up records its code
 // in the status word, the other waits then leave, and the CTA drains its copies, frees TMEM and returns.
 #include "swiglu_b200.h"
@@ -42,52 +48,83 @@ using swiglu_b200::Math;
 
 constexpr int TM = 128;                         // token rows per CTA tile
 constexpr int TN = 64;                          // output columns per tile (one 128-byte swizzle span)
-#ifndef SWIGLU_LORA_TILES_PER_RANGE
-#define SWIGLU_LORA_TILES_PER_RANGE 4  // finer items balance the SMs better (16 -> 4: +3..6 %)
-#endif
-constexpr int TILES_PER_RANGE = SWIGLU_LORA_TILES_PER_RANGE;  // 64-column tiles per work item
 constexpr int EG_BYTES = TM * TN * 2;           // 16 KiB
-#ifndef SWIGLU_LORA_OUT_BUFS
-#define SWIGLU_LORA_OUT_BUFS 2
-#endif
-constexpr int OUT_BUFS_PER_GROUP = SWIGLU_LORA_OUT_BUFS;  // h tiles of one epilogue group waiting for their bulk store
-#ifndef SWIGLU_LORA_EPI_WARPS
-#define SWIGLU_LORA_EPI_WARPS 16
-#endif
-constexpr int EPI_WARPS = SWIGLU_LORA_EPI_WARPS;  // EPI_WARPS / 4 warps share a TMEM lane quarter
-#ifndef SWIGLU_LORA_GROUPS
-#define SWIGLU_LORA_GROUPS 2
-#endif
-constexpr int THREADS = 64 + 32 * EPI_WARPS;
-// accumulator buffers in TMEM, (64 gate + 64 up) fp32 columns each: one per epilogue group, at least two
-constexpr int ACC_BUFS = SWIGLU_LORA_GROUPS > 2 ? SWIGLU_LORA_GROUPS : 2;
-constexpr int TMEM_COLS = ACC_BUFS * 128 <= 256 ? 256 : 512;
-#ifndef SWIGLU_LORA_STAGES16
-#define SWIGLU_LORA_STAGES16 4
-#endif
+constexpr int EPI_WARPS = 16;
+// warps 0..3: loads, MMA issue, stores, idle; the epilogue warps start at a multiple of four so that
+// warp & 3 is the TMEM lane quarter a warp may read
+constexpr int FIRST_EPI_WARP = 4;
+constexpr int THREADS = 32 * (FIRST_EPI_WARP + EPI_WARPS);
+constexpr int ACC_BUFS = 2;                     // accumulator buffers in TMEM, (64 gate + 64 up) fp32 columns each
+constexpr int TMEM_COLS = 256;
 // kind::f16, D fp32, A and B bf16 K-major, M = 128, N = 64
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
 
-// Shared-memory layout for a rank padded to RK (16, 32 or 64): the narrower the adapter tiles, the more
-// stages of E / G tiles fit, and bytes in flight are what this kernel's bandwidth comes from.
-//
-// GROUPS: the epilogue warps work as this many independent groups, each covering all four TMEM lane quarters
-// and taking every GROUPS-th tile, so that one group's waits, barrier and store issue overlap the other's
-// arithmetic, and a thread handles twice the columns per tile (half the per-tile bookkeeping per element).
-template <int RK>
+// What was tuned by measurement, per padded rank and per kernel (H: h alone is written; EG: e and g as well).
+//   run       Tiles are numbered along the rows of the matrix (row tile major).  CTA b of G takes `run`
+//             consecutive tiles, skips the (G - 1) * run that the other CTAs take, and so on, so that at any
+//             moment the CTAs together read and write one contiguous band of the matrices.
+//   xa_slots  depth of the ring of XA tiles, which change with the row tile: with short runs that is every
+//             tile or two, and the loads of E and G run ahead only as far as this ring lets them.
+//   lag       After it has issued the stores of a tile, the storing thread waits until all but the stores of
+//             its last `lag` tiles have read their shared memory, and returns the stage of the tile `lag`
+//             tiles back to the loads: 0 keeps one tile's stores in flight, 1 two, at the price of a stage
+//             that stays taken for longer.
+//   groups    The epilogue warps work as one set of sixteen on every tile (16 columns per warp) or as two
+//             sets of eight on alternate tiles (32 columns per warp).
+// Measured on M 16384 x N 14336 (and checked on four smaller shapes): rank 16 H 6.57 TB/s and EG 5.9-6.0 TB/s
+// with the settings below; for H run 1 / 4 / 8 give 6.42 / 6.56-6.63 / 6.08, lag 2 6.09, and one long run of
+// tiles / G per CTA 5.3-6.0; rank 64 H 5.63 against 4.45 with lag 1.  The response is not monotonic in any of
+// the four: what is being tuned is how the reads and writes of 148 SMs meet in DRAM.
+struct Tune {
+  int run, xa_slots, lag, groups;
+};
+#ifndef SWIGLU_LORA_TUNE_16_H
+#define SWIGLU_LORA_TUNE_16_H {2, 2, 1, 1}
+#endif
+#ifndef SWIGLU_LORA_TUNE_16_EG
+#define SWIGLU_LORA_TUNE_16_EG {1, 3, 0, 2}
+#endif
+#ifndef SWIGLU_LORA_TUNE_32_H
+#define SWIGLU_LORA_TUNE_32_H {2, 2, 0, 1}
+#endif
+#ifndef SWIGLU_LORA_TUNE_32_EG
+#define SWIGLU_LORA_TUNE_32_EG {1, 2, 0, 2}
+#endif
+#ifndef SWIGLU_LORA_TUNE_64_H
+#define SWIGLU_LORA_TUNE_64_H {2, 2, 0, 1}
+#endif
+#ifndef SWIGLU_LORA_TUNE_64_EG  // (room for one pair of XA tiles only: long runs, few changes of row tile)
+#define SWIGLU_LORA_TUNE_64_EG {8, 1, 0, 2}
+#endif
+template <int RK, bool SAVE>
+constexpr Tune tune() {
+  if (RK == 16) return SAVE ? Tune SWIGLU_LORA_TUNE_16_EG : Tune SWIGLU_LORA_TUNE_16_H;
+  if (RK == 32) return SAVE ? Tune SWIGLU_LORA_TUNE_32_EG : Tune SWIGLU_LORA_TUNE_32_H;
+  return SAVE ? Tune SWIGLU_LORA_TUNE_64_EG : Tune SWIGLU_LORA_TUNE_64_H;
+}
+
+// Shared-memory layout for a rank padded to RK (16, 32 or 64).  A stage holds the E and G tiles, the two
+// adapter tiles and, when e and g are written out (they replace E and G in place), a tile for h; without
+// them h replaces E.  The ring of stages takes all the shared memory that the XA tiles leave.
+template <int RK, bool SAVE>
 struct Cfg {
+  static constexpr Tune T = tune<RK, SAVE>();
+  static constexpr int RUN = T.run, XA_SLOTS = T.xa_slots, LAG = T.lag, GROUPS = T.groups;
   static constexpr int XA_BYTES = TM * RK * 2;
   static constexpr int B_BYTES = TN * RK * 2;
-  static constexpr int STAGE_BYTES = 2 * EG_BYTES + 2 * B_BYTES;
-  static constexpr int GROUPS = RK == 64 ? 1 : SWIGLU_LORA_GROUPS;
-  static constexpr int STAGES = RK == 16 ? SWIGLU_LORA_STAGES16 : 3;
-  static constexpr int OUT_BUFS = GROUPS * OUT_BUFS_PER_GROUP;
+  static constexpr int H_BYTES = SAVE ? EG_BYTES : 0;
+  static constexpr int B_OFFSET = 2 * EG_BYTES + H_BYTES;
+  static constexpr int LOAD_BYTES = 2 * EG_BYTES + 2 * B_BYTES;
+  static constexpr int STAGE_BYTES = B_OFFSET + 2 * B_BYTES;
+  static constexpr int XA_RING_BYTES = XA_SLOTS * 2 * XA_BYTES;
+  static constexpr int STAGES = (227 * 1024 - XA_RING_BYTES - 1024 - 512) / STAGE_BYTES;
+  static constexpr int SMEM_BYTES = XA_RING_BYTES + STAGES * STAGE_BYTES + 1024 + 512;  // alignment slack, barriers
   static constexpr int GROUP_WARPS = EPI_WARPS / GROUPS;
   static constexpr int CW = 64 / (GROUP_WARPS / 4);  // columns of a tile handled by one warp
-  static constexpr int SMEM_BYTES = 2 * XA_BYTES + STAGES * STAGE_BYTES + OUT_BUFS * EG_BYTES + 1024 + 256;
-  static_assert(GROUPS >= 1 && GROUPS <= 3 && EPI_WARPS % (4 * GROUPS) == 0, "one to three epilogue groups");
-  static_assert(CW == 16 || CW == 32, "a warp reads 16 or 32 TMEM columns per accumulator");
-  static_assert(SMEM_BYTES <= 227 * 1024, "exceeds the shared memory of an SM");
+  static_assert(RUN >= 1 && XA_SLOTS >= 1 && (GROUPS == 1 || GROUPS == 2), "settings");
+  static_assert(STAGES >= 3 && STAGES <= 8, "ring depth");
+  static_assert(LAG >= 0 && LAG < STAGES - 1, "stores in flight leave stages for the loads");
+  static_assert((2 + 3 * STAGES + 2 * ACC_BUFS + 2 * XA_SLOTS) * 8 + 8 <= 512, "barriers fit their reserve");
 };
 
 struct LoraParams {
@@ -95,6 +132,7 @@ struct LoraParams {
   long long m, n;
   int r;
   int save;  // also store e and g
+  int run;   // consecutive tiles a CTA takes at a time (Tune::run, less for small problems)
   float s_gate, s_up;
 };
 
@@ -102,15 +140,30 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int 
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y),
                "r"(smem_u32(smem_src)) : "memory");
 }
-// barrier `id` over the `threads` threads of one epilogue group that also ANDs a predicate across them
-__device__ __forceinline__ bool epilogue_all(bool ok, int id, int threads) {
-  uint32_t all;
-  asm volatile("{ .reg .pred p, q; setp.ne.u32 q, %1, 0; bar.red.and.pred p, %2, %3, q; selp.u32 %0, 1, 0, p; }"
-               : "=r"(all) : "r"((uint32_t)ok), "r"(id), "r"(threads) : "memory");
-  return all != 0;
-}
 __device__ __forceinline__ void mbar_arrive(uint64_t* b) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+
+// The tiles of one CTA in the order it takes them: runs of `run` consecutive tiles, gridDim.x runs apart.
+struct Walk {
+  uint32_t tile, tiles, skip;
+  int run, j;
+  __device__ Walk(uint32_t tiles_, int run_)
+      : tile(blockIdx.x * run_), tiles(tiles_), skip((gridDim.x - 1) * run_), run(run_), j(0) {}
+  __device__ bool valid() const { return tile < tiles; }
+  __device__ void next() {
+    ++tile;
+    if (++j == run) {
+      j = 0;
+      tile += skip;
+    }
+  }
+};
+
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t* r) {
+  if constexpr (N == 32) tmem_ld32(taddr, r);
+  else tmem_ld16(taddr, r);
 }
 
 template <int RK, bool SAVE>
@@ -122,39 +175,42 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
                    const __grid_constant__ CUtensorMap map_go, const LoraParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  constexpr int XA_BYTES = Cfg<RK>::XA_BYTES, B_BYTES = Cfg<RK>::B_BYTES, STAGE_BYTES = Cfg<RK>::STAGE_BYTES,
-                STAGES = Cfg<RK>::STAGES, GROUPS = Cfg<RK>::GROUPS, GROUP_WARPS = Cfg<RK>::GROUP_WARPS,
-                CW = Cfg<RK>::CW, OUT_BUFS = Cfg<RK>::OUT_BUFS;
-  unsigned char* xa_g = smem;
-  unsigned char* xa_u = smem + XA_BYTES;
-  unsigned char* ring = smem + 2 * XA_BYTES;
-  unsigned char* outs = ring + STAGES * STAGE_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(outs + OUT_BUFS * EG_BYTES);
-  uint64_t* empty = full + STAGES;        // MMA commit + one epilogue thread
+  using C = Cfg<RK, SAVE>;
+  constexpr int XA_BYTES = C::XA_BYTES, B_BYTES = C::B_BYTES, STAGE_BYTES = C::STAGE_BYTES, STAGES = C::STAGES,
+                B_OFFSET = C::B_OFFSET, GROUPS = C::GROUPS, GROUP_WARPS = C::GROUP_WARPS, CW = C::CW;
+  constexpr int XA_SLOTS = C::XA_SLOTS;
+  unsigned char* xa_ring = smem;                  // slot: XAg tile, XAu tile
+  unsigned char* ring = smem + C::XA_RING_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(ring + STAGES * STAGE_BYTES);  // loads of a stage have landed
+  uint64_t* done = full + STAGES;                 // every warp of the stage's set has written its results
+  uint64_t* empty = done + STAGES;                // the stores of the stage have read it
   uint64_t* acc_full = empty + STAGES;            // [ACC_BUFS]
-  uint64_t* acc_empty = acc_full + ACC_BUFS;      // [ACC_BUFS], every warp of the group that reads the buffer
-  uint64_t* xa_full = acc_empty + ACC_BUFS;
-  uint64_t* xa_empty = xa_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xa_empty + 1);
+  uint64_t* acc_empty = acc_full + ACC_BUFS;      // [ACC_BUFS], every warp of the set that reads the buffer
+  uint64_t* xa_full = acc_empty + ACC_BUFS;       // [XA_SLOTS]
+  uint64_t* xa_empty = xa_full + XA_SLOTS;        // [XA_SLOTS]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xa_empty + XA_SLOTS);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const long long tiles_n = (p.n + TN - 1) / TN;
-  const long long ranges_n = (tiles_n + TILES_PER_RANGE - 1) / TILES_PER_RANGE;
-  const long long items = ((p.m + TM - 1) / TM) * ranges_n;
+  const uint32_t tiles_n = (uint32_t)((p.n + TN - 1) / TN);
+  const uint32_t tiles = (uint32_t)((p.m + TM - 1) / TM) * tiles_n;  // (the host has checked that it fits)
+  const Walk walk0(tiles, p.run);
   const int k_steps = (p.r + 15) / 16;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 2);
+      mbar_init(&done[s], GROUP_WARPS);
+      mbar_init(&empty[s], 1);
     }
     for (int b = 0; b < ACC_BUFS; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], GROUP_WARPS);  // with several groups, buffer b is read by group b only
+      mbar_init(&acc_empty[b], GROUP_WARPS);  // with several sets, buffer b is read by set b only
     }
-    mbar_init(xa_full, 1);
-    mbar_init(xa_empty, 1);
+    for (int x = 0; x < XA_SLOTS; ++x) {
+      mbar_init(&xa_full[x], 1);
+      mbar_init(&xa_empty[x], 1);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -168,112 +224,124 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
-  // Every role walks the same sequence: items (row tile, column range), tiles within the range.
+  // Every role walks the same sequence of tiles; `it` counts them for the ring of stages, `xa_n` counts the
+  // changes of row tile for the ring of XA tiles.
   if (warp == 0) {
     if (lane == 0) {
-      long long it = 0, item_no = 0;
-      bool ok = true;
-      for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++item_no) {
-        const int m0 = (int)(item / ranges_n) * TM;
-        const long long t_lo = (item % ranges_n) * TILES_PER_RANGE;
-        const long long t_hi = (t_lo + TILES_PER_RANGE) < tiles_n ? (t_lo + TILES_PER_RANGE) : tiles_n;
-        if (item_no > 0) {
-          ok = mbar_wait(xa_empty, (uint32_t)((item_no - 1) & 1), p.status, 500);
-          if (!ok) break;
+      uint32_t xa_n = 0, row_tile = ~0u;
+      uint32_t it = 0;
+      for (Walk w = walk0; w.valid(); w.next(), ++it) {
+        const uint32_t m_tile = w.tile / tiles_n;
+        const int m0 = (int)m_tile * TM;
+        const int n0 = (int)(w.tile - m_tile * tiles_n) * TN;
+        if (m_tile != row_tile) {
+          row_tile = m_tile;
+          const int x = (int)(xa_n % XA_SLOTS);
+          if (xa_n >= XA_SLOTS && !mbar_wait(&xa_empty[x], (uint32_t)((xa_n / XA_SLOTS - 1) & 1), p.status, 500 + x))
+            break;
+          mbar_expect_tx(&xa_full[x], 2 * XA_BYTES);
+          tma_load_2d(xa_ring + x * 2 * XA_BYTES, &map_xag, 0, m0, &xa_full[x]);
+          tma_load_2d(xa_ring + x * 2 * XA_BYTES + XA_BYTES, &map_xau, 0, m0, &xa_full[x]);
+          ++xa_n;
         }
-        mbar_expect_tx(xa_full, 2 * XA_BYTES);
-        tma_load_2d(xa_g, &map_xag, 0, m0, xa_full);
-        tma_load_2d(xa_u, &map_xau, 0, m0, xa_full);
-        for (long long t = t_lo; t < t_hi; ++t, ++it) {
-          const int s = (int)(it % STAGES);
-          if (it >= STAGES) {
-            ok = mbar_wait(&empty[s], (uint32_t)((it / STAGES - 1) & 1), p.status, 100 + s);
-            if (!ok) break;
-          }
-          unsigned char* stage = ring + s * STAGE_BYTES;
-          const int n0 = (int)(t * TN);
-          mbar_expect_tx(&full[s], STAGE_BYTES);
-          tma_load_2d(stage, &map_e, n0, m0, &full[s]);
-          tma_load_2d(stage + EG_BYTES, &map_g, n0, m0, &full[s]);
-          tma_load_2d(stage + 2 * EG_BYTES, &map_bg, 0, n0, &full[s]);
-          tma_load_2d(stage + 2 * EG_BYTES + B_BYTES, &map_bu, 0, n0, &full[s]);
-        }
+        const int s = (int)(it % STAGES);
+        if (it >= STAGES && !mbar_wait(&empty[s], (uint32_t)((it / STAGES - 1) & 1), p.status, 100 + s)) break;
+        unsigned char* stage = ring + s * STAGE_BYTES;
+        mbar_expect_tx(&full[s], C::LOAD_BYTES);
+        tma_load_2d(stage, &map_e, n0, m0, &full[s]);
+        tma_load_2d(stage + EG_BYTES, &map_g, n0, m0, &full[s]);
+        tma_load_2d(stage + B_OFFSET, &map_bg, 0, n0, &full[s]);
+        tma_load_2d(stage + B_OFFSET + B_BYTES, &map_bu, 0, n0, &full[s]);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      long long it = 0, item_no = 0;
-      bool ok = true;
-      const uint64_t ag_desc = umma_desc_rows<RK * 2>(smem_u32(xa_g));
-      const uint64_t au_desc = umma_desc_rows<RK * 2>(smem_u32(xa_u));
-      for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++item_no) {
-        const long long t_lo = (item % ranges_n) * TILES_PER_RANGE;
-        const long long t_hi = (t_lo + TILES_PER_RANGE) < tiles_n ? (t_lo + TILES_PER_RANGE) : tiles_n;
-        ok = mbar_wait(xa_full, (uint32_t)(item_no & 1), p.status, 510);
-        if (!ok) break;
-        for (long long t = t_lo; t < t_hi; ++t, ++it) {
-          const int s = (int)(it % STAGES);
-          const int b = (int)(it % ACC_BUFS);
-          if (it >= ACC_BUFS) {
-            ok = mbar_wait(&acc_empty[b], (uint32_t)((it / ACC_BUFS - 1) & 1), p.status, 400 + b);
-            if (!ok) break;
-          }
-          ok = mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1), p.status, 200 + s);
-          if (!ok) break;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t b_addr = smem_u32(ring + s * STAGE_BYTES + 2 * EG_BYTES);
-          const uint64_t bg_desc = umma_desc_rows<RK * 2>(b_addr);
-          const uint64_t bu_desc = umma_desc_rows<RK * 2>(b_addr + B_BYTES);
-          const uint32_t d_gate = tmem_base + (uint32_t)b * 128u;
-          for (int kk = 0; kk < k_steps; ++kk) {
-            umma_bf16(d_gate, ag_desc + 2 * kk, bg_desc + 2 * kk, IDESC, kk != 0);
-            umma_bf16(d_gate + 64, au_desc + 2 * kk, bu_desc + 2 * kk, IDESC, kk != 0);
-          }
-          umma_commit(&acc_full[b]);  // adapter terms of this tile are in TMEM
-          umma_commit(&empty[s]);     // ... and the Bg / Bu tiles of the stage have been read
+      uint32_t xa_n = 0, row_tile = ~0u;
+      uint64_t ag_desc = 0, au_desc = 0;
+      uint32_t it = 0;
+      for (Walk w = walk0; w.valid(); w.next(), ++it) {
+        const uint32_t m_tile = w.tile / tiles_n;
+        if (m_tile != row_tile) {
+          // the XA tiles of the row tile left behind may be replaced once the MMAs issued so far are done
+          if (xa_n > 0) umma_commit(&xa_empty[(xa_n - 1) % XA_SLOTS]);
+          row_tile = m_tile;
+          const int x = (int)(xa_n % XA_SLOTS);
+          if (!mbar_wait(&xa_full[x], (uint32_t)((xa_n / XA_SLOTS) & 1), p.status, 510 + x)) break;
+          ag_desc = umma_desc_rows<RK * 2>(smem_u32(xa_ring + x * 2 * XA_BYTES));
+          au_desc = umma_desc_rows<RK * 2>(smem_u32(xa_ring + x * 2 * XA_BYTES + XA_BYTES));
+          ++xa_n;
         }
-        if (ok) umma_commit(xa_empty);  // the XA tiles may be replaced once these MMAs are done
+        const int s = (int)(it % STAGES);
+        const int b = (int)(it % ACC_BUFS);
+        if (it >= ACC_BUFS && !mbar_wait(&acc_empty[b], (uint32_t)((it / ACC_BUFS - 1) & 1), p.status, 400 + b)) break;
+        if (!mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1), p.status, 200 + s)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t b_addr = smem_u32(ring + s * STAGE_BYTES + B_OFFSET);
+        const uint64_t bg_desc = umma_desc_rows<RK * 2>(b_addr);
+        const uint64_t bu_desc = umma_desc_rows<RK * 2>(b_addr + B_BYTES);
+        const uint32_t d_gate = tmem_base + (uint32_t)b * 128u;
+        for (int kk = 0; kk < k_steps; ++kk) {
+          umma_bf16(d_gate, ag_desc + 2 * kk, bg_desc + 2 * kk, IDESC, kk != 0);
+          umma_bf16(d_gate + 64, au_desc + 2 * kk, bu_desc + 2 * kk, IDESC, kk != 0);
+        }
+        // The adapter terms of this tile are in TMEM.  (The epilogue waits for this before it touches the
+        // stage, and the stage is refilled only after the epilogue: the Bg / Bu tiles need no release.)
+        umma_commit(&acc_full[b]);
       }
     }
-  } else {
+  } else if (warp == 2) {
+    // Stores.  One thread issues the bulk tensor stores of a tile once the tile's warps are done with it.
+    if (lane == 0) {
+      constexpr int LAG = C::LAG;
+      uint32_t it = 0;
+      for (Walk w = walk0; w.valid(); w.next(), ++it) {
+        const uint32_t m_tile = w.tile / tiles_n;
+        const int m0 = (int)m_tile * TM;
+        const int n0 = (int)(w.tile - m_tile * tiles_n) * TN;
+        const int s = (int)(it % STAGES);
+        if (!mbar_wait(&done[s], (uint32_t)((it / STAGES) & 1), p.status, 700 + s)) break;
+        unsigned char* stage = ring + s * STAGE_BYTES;
+        if constexpr (SAVE) {
+          tma_store_2d(&map_h, n0, m0, stage + 2 * EG_BYTES);
+          tma_store_2d(&map_eo, n0, m0, stage);
+          tma_store_2d(&map_go, n0, m0, stage + EG_BYTES);
+        } else {
+          tma_store_2d(&map_h, n0, m0, stage);
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        if (it >= (uint32_t)LAG) {
+          asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(LAG) : "memory");
+          mbar_arrive(&empty[(it - LAG) % STAGES]);
+        }
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+  } else if (warp >= FIRST_EPI_WARP) {
     const int quarter = warp & 3;                   // TMEM lane quarter this warp may read
-    const int slot = (warp - 2) >> 2;               // 0 .. EPI_WARPS/4 - 1
-    const int group = slot % GROUPS;                // epilogue group: takes the tiles with it % GROUPS == group
+    const int slot = (warp - FIRST_EPI_WARP) >> 2;  // 0 .. EPI_WARPS/4 - 1
+    const int group = slot % GROUPS;                // takes the tiles with it % GROUPS == group
     const int part = slot / GROUPS;                 // which CW of the tile's 64 columns this warp handles
     const int row = quarter * 32 + lane;            // row of the tile owned by this thread
-    const bool elected = (part == 0 && quarter == ((2 + 4 * group) & 3) && lane == 0);  // one thread per group
     const Consts one(1.0f, 1.0f);
-    long long it = 0;
-    int mine = 0;                                   // tiles this group has handled
     bool ok = true;
-    for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
-      const int m0 = (int)(item / ranges_n) * TM;
-      const long long t_lo = (item % ranges_n) * TILES_PER_RANGE;
-      const long long t_hi = (t_lo + TILES_PER_RANGE) < tiles_n ? (t_lo + TILES_PER_RANGE) : tiles_n;
-      for (long long t = t_lo; t < t_hi; ++t, ++it) {
+    {
+      uint32_t it = 0;
+      for (Walk w = walk0; w.valid(); w.next(), ++it) {
         if (GROUPS > 1 && (int)(it % GROUPS) != group) continue;
         const int s = (int)(it % STAGES);
         const int b = (int)(it % ACC_BUFS);
         unsigned char* e_tile = ring + s * STAGE_BYTES;
         unsigned char* g_tile = e_tile + EG_BYTES;
-        // Two h buffers per group: before the group's barrier of this tile its storing thread has waited for
-        // the store of the previous tile to finish reading, so the next tile may overwrite that buffer.
-        unsigned char* h_tile = outs + (group * OUT_BUFS_PER_GROUP + (mine % OUT_BUFS_PER_GROUP)) * EG_BYTES;
-        ++mine;
+        unsigned char* h_tile = SAVE ? e_tile + 2 * EG_BYTES : e_tile;  // alone, h takes the place of E
         ok = mbar_wait(&full[s], (uint32_t)((it / STAGES) & 1), p.status, 600 + s) &&
              mbar_wait(&acc_full[b], (uint32_t)((it / ACC_BUFS) & 1), p.status, 300 + b);
         if (!__all_sync(0xffffffffu, ok)) ok = false;  // warp-uniform, for the warp-wide TMEM loads
-        if (ok) {
+        if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)b * 128u + (uint32_t)(part * CW);
         uint32_t lg[CW], lu[CW];
-        if constexpr (CW == 32) {
-          tmem_ld32(t_row, lg);
-          tmem_ld32(t_row + 64, lu);
-        } else {
-          tmem_ld16(t_row, lg);
-          tmem_ld16(t_row + 64, lu);
-        }
+        tmem_ld_cols<CW>(t_row, lg);
+        tmem_ld_cols<CW>(t_row + 64, lu);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         // the adapter terms are in registers: TMEM buffer b can take the MMAs of the tile after next
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -308,30 +376,13 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
             *reinterpret_cast<uint4*>(g_tile + off) = make_uint4(go[0], go[1], go[2], go[3]);
           }
         }
-        }
-        // The shared-memory tiles are complete: make them visible to the bulk stores.  The threads of the
-        // group meet here once per tile and agree on the outcome of their waits, so that none is left at a
-        // later barrier waiting for a thread whose wait gave up.
+        // This warp's part of the tiles is complete: make it visible to the bulk stores and tell the
+        // storing thread.  The warps of a set never wait for one another.
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        // the group's previous store has finished reading its h buffer, which the next tile overwrites
-        if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        ok = epilogue_all(ok, 1 + group, 32 * GROUP_WARPS);
-        if (!ok) break;
-        if (elected) {
-          const int n0 = (int)(t * TN);
-          tma_store_2d(&map_h, n0, m0, h_tile);
-          if constexpr (SAVE) {
-            tma_store_2d(&map_eo, n0, m0, e_tile);
-            tma_store_2d(&map_go, n0, m0, g_tile);
-          }
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          // the stage may be refilled once nothing reads it any more
-          if constexpr (SAVE) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-          mbar_arrive(&empty[s]);
-        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&done[s]);
       }
     }
-    if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -400,13 +451,13 @@ int swiglu_b200_lora_swiglu_fwd(void* h, void* e_out, void* g_out, const void* e
     auto set = [&](auto kernel, int bytes) {
       attr_ok = attr_ok && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
     };
-    set(lora_swiglu_kernel<16, false>, Cfg<16>::SMEM_BYTES);
-    set(lora_swiglu_kernel<16, true>, Cfg<16>::SMEM_BYTES);
+    set(lora_swiglu_kernel<16, false>, Cfg<16, false>::SMEM_BYTES);
+    set(lora_swiglu_kernel<16, true>, Cfg<16, true>::SMEM_BYTES);
 #ifndef SWIGLU_LORA_ONLY16  // (tuning builds compile the rank-16 layout alone)
-    set(lora_swiglu_kernel<32, false>, Cfg<32>::SMEM_BYTES);
-    set(lora_swiglu_kernel<32, true>, Cfg<32>::SMEM_BYTES);
-    set(lora_swiglu_kernel<64, false>, Cfg<64>::SMEM_BYTES);
-    set(lora_swiglu_kernel<64, true>, Cfg<64>::SMEM_BYTES);
+    set(lora_swiglu_kernel<32, false>, Cfg<32, false>::SMEM_BYTES);
+    set(lora_swiglu_kernel<32, true>, Cfg<32, true>::SMEM_BYTES);
+    set(lora_swiglu_kernel<64, false>, Cfg<64, false>::SMEM_BYTES);
+    set(lora_swiglu_kernel<64, true>, Cfg<64, true>::SMEM_BYTES);
 #endif
     if (!attr_ok) return SWIGLU_B200_ERR_DEVICE;
     if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm < 1)
@@ -417,19 +468,27 @@ int swiglu_b200_lora_swiglu_fwd(void* h, void* e_out, void* g_out, const void* e
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return SWIGLU_B200_ERR_DEVICE;
   const long long tiles_n = (n + TN - 1) / TN;
-  const long long items = ((m + TM - 1) / TM) * ((tiles_n + TILES_PER_RANGE - 1) / TILES_PER_RANGE);
-  const unsigned grid = (unsigned)(items < n_sm ? items : n_sm);
-  LoraParams p{static_cast<int*>(status), m, n, (int)r, save ? 1 : 0, s_gate, s_up};
+  const long long tiles = ((m + TM - 1) / TM) * tiles_n;
+  if (tiles > 0x7fffffffLL) return SWIGLU_B200_ERR_SHAPE;  // (tens of terabytes per matrix)
+  // A CTA takes its tiles in runs of Tune::run where that leaves every CTA sixteen runs or more; smaller problems
+  // are dealt in shorter runs, so that the last round of runs does not leave most SMs idle.
+  int run = rk == 16 ? (save ? Cfg<16, true>::RUN : Cfg<16, false>::RUN)
+          : rk == 32 ? (save ? Cfg<32, true>::RUN : Cfg<32, false>::RUN)
+                     : (save ? Cfg<64, true>::RUN : Cfg<64, false>::RUN);
+  while (run > 1 && tiles < 16LL * run * n_sm) run /= 2;
+  const long long runs = (tiles + run - 1) / run;
+  const unsigned grid = (unsigned)(runs < n_sm ? runs : n_sm);
+  LoraParams p{static_cast<int*>(status), m, n, (int)r, save ? 1 : 0, run, s_gate, s_up};
   auto launch = [&](auto kernel, int bytes) {
     kernel<<<grid, THREADS, bytes, st>>>(me, mg, mxg, mxu, mbg, mbu, mh, meo, mgo, p);
   };
   if (rk == 16)
-    save ? launch(lora_swiglu_kernel<16, true>, Cfg<16>::SMEM_BYTES) : launch(lora_swiglu_kernel<16, false>, Cfg<16>::SMEM_BYTES);
+    save ? launch(lora_swiglu_kernel<16, true>, Cfg<16, true>::SMEM_BYTES) : launch(lora_swiglu_kernel<16, false>, Cfg<16, false>::SMEM_BYTES);
 #ifndef SWIGLU_LORA_ONLY16
   else if (rk == 32)
-    save ? launch(lora_swiglu_kernel<32, true>, Cfg<32>::SMEM_BYTES) : launch(lora_swiglu_kernel<32, false>, Cfg<32>::SMEM_BYTES);
+    save ? launch(lora_swiglu_kernel<32, true>, Cfg<32, true>::SMEM_BYTES) : launch(lora_swiglu_kernel<32, false>, Cfg<32, false>::SMEM_BYTES);
   else
-    save ? launch(lora_swiglu_kernel<64, true>, Cfg<64>::SMEM_BYTES) : launch(lora_swiglu_kernel<64, false>, Cfg<64>::SMEM_BYTES);
+    save ? launch(lora_swiglu_kernel<64, true>, Cfg<64, true>::SMEM_BYTES) : launch(lora_swiglu_kernel<64, false>, Cfg<64, false>::SMEM_BYTES);
 #else
   else
     return SWIGLU_B200_ERR_SHAPE;
