@@ -29,8 +29,11 @@ def reference(e, g, xag, xau, bg, bu, sg, su):
     return torch.nn.functional.silu(ef) * gf, ef, gf
 
 
+# The last four shapes have enough tiles for the kernel's longer runs of tiles per CTA (two at every rank, eight
+# at rank 64 with e and g written, four on the 8192 x 11008 case) and for rows of tiles that end inside a run.
 @pytest.mark.parametrize("m,n,r", [(128, 64, 16), (128, 1024, 16), (256, 2048, 8), (1, 8, 8), (200, 200, 24),
-                                   (333, 1096, 32), (1000, 4104, 64), (4096, 14336, 16)])
+                                   (333, 1096, 32), (1000, 4104, 64), (4096, 14336, 16), (4100, 14344, 32),
+                                   (8192, 11008, 64), (16384, 14336, 64), (16300, 9480, 16)])
 @pytest.mark.parametrize("save_eg", [False, True])
 def test_matches_formula(m, n, r, save_eg):
     e, g, xag, xau, bg, bu = operands(m, n, r)
