@@ -639,6 +639,261 @@ swiglu_gemm_fwd_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __g
 
 }  // namespace wide
 
+// ------------------------------------------------------------------------------------------
+// Fourth kernel: CTA pairs, 256 x 256 tile of h computed as TWO 256 x 128 half tiles whose contractions run a few
+// K blocks apart (SWIGLU_B200_GEMM_TILE=staggered).
+//
+// The 256 x 256 tile above shares each X tile between two MMAs, which cuts the operand bytes per flop by a quarter,
+// but its single 512-column accumulator leaves the epilogue exposed.  Here the tile is two independent streams:
+// stream s computes columns [n0 + 128 s, n0 + 128 s + 128) of h exactly as the 256 x 128 kernel does (rank 0 loads
+// the Wg rows, rank 1 the Wu rows, TMEM columns [256 s, 256 s + 128) = gate, [256 s + 128, 256 s + 256) = up), each
+// issued by a thread of its own in the leader CTA.  Both streams read the same X tiles: X has a ring of its own
+// whose slots are released when BOTH streams' MMAs have read them, and the weights of stream 1 are loaded LAG K
+// blocks behind those of stream 0, so stream 1 reaches the end of a tile LAG blocks after stream 0.  When a stream
+// has finished a tile it waits until the epilogue warps have taken its 256 accumulator columns into registers (a
+// fraction of a microsecond); the other stream keeps the tensor pipe fed meanwhile.  No second accumulator buffer
+// is needed, and an X tile crosses L2 once for both halves.
+namespace stag {
+
+#ifndef SWIGLU_GEMM_STAG_SX
+#define SWIGLU_GEMM_STAG_SX 6
+#endif
+#ifndef SWIGLU_GEMM_STAG_SW
+#define SWIGLU_GEMM_STAG_SW 4
+#endif
+#ifndef SWIGLU_GEMM_STAG_LAG
+#define SWIGLU_GEMM_STAG_LAG 2
+#endif
+constexpr int SX = SWIGLU_GEMM_STAG_SX;                  // X ring: prefetch depth + LAG
+constexpr int SW = SWIGLU_GEMM_STAG_SW;                  // each weight ring
+constexpr int LAG = SWIGLU_GEMM_STAG_LAG;                // K blocks stream 1's weights are loaded behind stream 0's
+constexpr int TMEM_COLS = 512;
+constexpr int EPI_WARPS = 16;                            // per CTA: four per TMEM lane quarter, 32 columns of h each
+constexpr int FIRST_EPI_WARP = 4;                        // warps 0..3: loads, stream 0, stream 1, idle
+constexpr int S_THREADS = 32 * (FIRST_EPI_WARP + EPI_WARPS);
+constexpr int RING_BYTES = (SX + 2 * SW) * TILE_BYTES;
+constexpr int SMEM_BYTES = RING_BYTES + 1024 + 512;
+static_assert(SMEM_BYTES <= 227 * 1024, "exceeds the shared memory of an SM");
+static_assert(LAG >= 1 && LAG < SX - 1, "X tiles outlive the lag between the streams");
+constexpr uint32_t IDESC = pair::IDESC;                  // M = 256, N = 256, both operands K-major
+
+using TileWalk = wide::TileWalk;
+
+template <int ACT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(S_THREADS, 1)
+swiglu_gemm_fwd_staggered_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wg,
+                                 const __grid_constant__ CUtensorMap map_wu, const __grid_constant__ CUtensorMap map_xa,
+                                 const __grid_constant__ CUtensorMap map_bg, const __grid_constant__ CUtensorMap map_bu,
+                                 const GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* x_ring = smem;
+  unsigned char* w_ring = smem + SX * TILE_BYTES;  // stream 0's SW slots, then stream 1's
+  uint64_t* x_full = reinterpret_cast<uint64_t*>(smem + RING_BYTES);  // [SX]  used in the leader only
+  uint64_t* x_empty = x_full + SX;                                    // [SX]  one copy per CTA, both streams commit
+  uint64_t* w_full = x_empty + SX;                                    // [2][SW]  used in the leader only
+  uint64_t* w_empty = w_full + 2 * SW;                                // [2][SW]  one copy per CTA
+  uint64_t* acc_full = w_empty + 2 * SW;                              // [2]  one copy per CTA
+  uint64_t* acc_empty = acc_full + 2;                                 // [2]  used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cta_rank();
+  const long long pair_id = blockIdx.x >> 1;
+  const long long n_pairs = gridDim.x >> 1;
+  const TileWalk walk(p.m, p.n);
+  const int main_blocks = (int)((p.k + BK - 1) / BK);
+  const int k_blocks = main_blocks + (p.r > 0 ? (2 * p.r + BK - 1) / BK : 0);  // then the adapter blocks (see above)
+  // tiles of this pair: pair_id, pair_id + n_pairs, ...
+  const long long my_tiles = walk.total > pair_id ? (walk.total - pair_id + n_pairs - 1) / n_pairs : 0;
+  const long long steps = my_tiles * k_blocks;  // K blocks of one stream over all of this pair's tiles
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < SX; ++s) {
+      mbar_init(&x_full[s], 2);    // one expect_tx arrival from each CTA's producer
+      mbar_init(&x_empty[s], 2);   // the commits of both streams
+    }
+    for (int s = 0; s < 2 * SW; ++s) {
+      mbar_init(&w_full[s], 2);
+      mbar_init(&w_empty[s], 1);
+    }
+    for (int h = 0; h < 2; ++h) {
+      mbar_init(&acc_full[h], 1);               // the stream's commit
+      mbar_init(&acc_empty[h], 2 * EPI_WARPS);  // every epilogue warp of both CTAs
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync();  // both CTAs' barriers exist before anyone arrives on them remotely
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // Step g loads X and the stream-0 weights of K block g (counted over all tiles of the pair) and the
+      // stream-1 weights of K block g - LAG.
+      const CUtensorMap* map_w = rank == 0 ? &map_wg : &map_wu;
+      const CUtensorMap* map_b = rank == 0 ? &map_bg : &map_bu;
+      long long t0 = pair_id, t1 = pair_id;  // tiles of the two streams
+      int kb0 = 0, kb1 = 0;
+      int m0 = 0, n0 = 0, m1 = 0, n1 = 0;
+      if (my_tiles > 0) {
+        walk.at(t0, m0, n0);
+        m1 = m0;
+        n1 = n0;
+      }
+      bool ok = true;
+      for (long long g = 0; g < steps + LAG && ok; ++g) {
+        if (g < steps) {
+          const int xs = (int)(g % SX), ws = (int)(g % SW);
+          if (g >= SX) ok = wait<false>(&x_empty[xs], (uint32_t)((g / SX - 1) & 1), p.status, 100 + xs);
+          if (ok && g >= SW) ok = wait<false>(&w_empty[ws], (uint32_t)((g / SW - 1) & 1), p.status, 110 + ws);
+          if (!ok) break;
+          const uint32_t xf = map_to_rank(smem_u32(&x_full[xs]), 0);
+          remote_expect_tx(xf, TILE_BYTES);
+          const uint32_t wf = map_to_rank(smem_u32(&w_full[ws]), 0);
+          remote_expect_tx(wf, TILE_BYTES);
+          if (kb0 < main_blocks) {
+            tma_load_2d_pair(x_ring + xs * TILE_BYTES, &map_x, kb0 * BK, m0 + (int)rank * BM, xf);
+            tma_load_2d_pair(w_ring + ws * TILE_BYTES, map_w, kb0 * BK, n0, wf);
+          } else {
+            const int c0 = (kb0 - main_blocks) * BK;  // column of XA' this block starts at
+            tma_load_2d_pair(x_ring + xs * TILE_BYTES, &map_xa, c0, m0 + (int)rank * BM, xf);
+            tma_load_2d_pair(w_ring + ws * TILE_BYTES, map_b, rank == 0 ? c0 : c0 - p.r, n0, wf);
+          }
+          if (++kb0 == k_blocks) {
+            kb0 = 0;
+            t0 += n_pairs;
+            if (t0 < walk.total) walk.at(t0, m0, n0);
+          }
+        }
+        if (g >= LAG) {
+          const long long g1 = g - LAG;
+          const int ws = (int)(g1 % SW);
+          if (g1 >= SW) ok = wait<false>(&w_empty[SW + ws], (uint32_t)((g1 / SW - 1) & 1), p.status, 120 + ws);
+          if (!ok) break;
+          const uint32_t wf = map_to_rank(smem_u32(&w_full[SW + ws]), 0);
+          remote_expect_tx(wf, TILE_BYTES);
+          if (kb1 < main_blocks) {
+            tma_load_2d_pair(w_ring + (SW + ws) * TILE_BYTES, map_w, kb1 * BK, n1 + BN, wf);
+          } else {
+            const int c0 = (kb1 - main_blocks) * BK;
+            tma_load_2d_pair(w_ring + (SW + ws) * TILE_BYTES, map_b, rank == 0 ? c0 : c0 - p.r, n1 + BN, wf);
+          }
+          if (++kb1 == k_blocks) {
+            kb1 = 0;
+            t1 += n_pairs;
+            if (t1 < walk.total) walk.at(t1, m1, n1);
+          }
+        }
+      }
+    }
+  } else if (warp == 1 || warp == 2) {
+    if (lane == 0 && rank == 0) {
+      const int h = warp - 1;  // the stream this thread issues
+      const uint32_t tmem_d = tmem_base + (uint32_t)h * 256u;
+      long long it = 0;
+      bool ok = true;
+      for (long long i = 0; i < my_tiles && ok; ++i) {
+        if (i >= 1) {  // the accumulator of this stream must have been taken by every epilogue warp of both CTAs
+          ok = wait<true>(&acc_empty[h], (uint32_t)((i - 1) & 1), p.status, 400 + h);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int xs = (int)(it % SX), ws = (int)(it % SW);
+          ok = wait<false>(&x_full[xs], (uint32_t)((it / SX) & 1), p.status, 200 + xs) &&
+               wait<false>(&w_full[h * SW + ws], (uint32_t)((it / SW) & 1), p.status, 210 + h * SW + ws);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint64_t a_desc = umma_desc(smem_u32(x_ring + xs * TILE_BYTES));
+          const uint64_t b_desc = umma_desc(smem_u32(w_ring + (h * SW + ws) * TILE_BYTES));
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) umma_pair(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, IDESC, (kb | kk) != 0);
+          commit_both(&x_empty[xs]);
+          commit_both(&w_empty[h * SW + ws]);
+        }
+        if (ok) commit_both(&acc_full[h]);
+      }
+    }
+  } else if (warp >= FIRST_EPI_WARP) {
+    const int quarter = warp & 3;                    // the TMEM lanes a warp may read: 32 * (warp % 4) ..
+    const int part = (warp - FIRST_EPI_WARP) >> 2;   // which 32 columns of a half tile
+    const Consts cst(p.gm, p.dm);
+    bool ok = true;
+    long long t = pair_id;
+    for (long long i = 0; i < my_tiles && ok; ++i, t += n_pairs) {
+      int m0, n0;
+      walk.at(t, m0, n0);
+      const int row = m0 + (int)rank * BM + quarter * 32 + lane;
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        ok = wait<false, 200>(&acc_full[h], (uint32_t)(i & 1), p.status, 300 + h);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)h * 256u + (uint32_t)(part * 32);
+        uint32_t g[32], u[32];
+        tmem_ld32(t_row, g);
+        tmem_ld32(t_row + BN, u);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        // this warp's part of the accumulator is in registers: tell the stream's thread in the leader
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) remote_arrive(map_to_rank(smem_u32(&acc_empty[h]), 0));
+        const int col0 = n0 + h * BN + part * 32;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          if (row < p.m && col0 + 16 * q < p.n) {  // n is a multiple of 16: a group of 16 columns is in or out
+            uint32_t hv[8], gv[8], uv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float g0 = __uint_as_float(g[16 * q + 2 * j]), g1 = __uint_as_float(g[16 * q + 2 * j + 1]);
+              const float u0 = __uint_as_float(u[16 * q + 2 * j]), u1 = __uint_as_float(u[16 * q + 2 * j + 1]);
+              __nv_bfloat162 hb =
+                  __floats2bfloat162_rn(Math<true, ACT>::fwd(g0, u0, cst), Math<true, ACT>::fwd(g1, u1, cst));
+              __nv_bfloat162 gb = __floats2bfloat162_rn(g0, g1);
+              __nv_bfloat162 ub = __floats2bfloat162_rn(u0, u1);
+              hv[j] = *reinterpret_cast<uint32_t*>(&hb);
+              gv[j] = *reinterpret_cast<uint32_t*>(&gb);
+              uv[j] = *reinterpret_cast<uint32_t*>(&ub);
+            }
+            const long long off = (long long)row * p.n + col0 + 16 * q;
+            uint4* dst = reinterpret_cast<uint4*>(p.h + off);
+            dst[0] = make_uint4(hv[0], hv[1], hv[2], hv[3]);
+            dst[1] = make_uint4(hv[4], hv[5], hv[6], hv[7]);
+            if (p.gate_out) {
+              uint4* dg = reinterpret_cast<uint4*>(p.gate_out + off);
+              dg[0] = make_uint4(gv[0], gv[1], gv[2], gv[3]);
+              dg[1] = make_uint4(gv[4], gv[5], gv[6], gv[7]);
+              uint4* du = reinterpret_cast<uint4*>(p.up_out + off);
+              du[0] = make_uint4(uv[0], uv[1], uv[2], uv[3]);
+              du[1] = make_uint4(uv[4], uv[5], uv[6], uv[7]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  settle_before_teardown(p.status);
+  cluster_sync();  // the peer's shared memory and TMEM stay alive until the leader's MMAs are done
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+}  // namespace stag
+
 // ------------------------------------------------------------------------------------------ host
 
 std::atomic<uint64_t> g_gemm_launches{0};
@@ -731,14 +986,54 @@ int wide_clusters(int dev, int* out) {
   return SWIGLU_B200_OK;
 }
 
-// SWIGLU_B200_GEMM_TILE=wide selects the 256 x 256 pair tile; the 256 x 128 tile is the default.  Measured on
-// X [16384, 4096] x W [14336, 4096]^T x 2: 2.64-2.67 ms against 2.66-2.68 ms each timed alone, 2.85 against 2.81 ms
-// interleaved in one loop; on a 4096-row case under ncu the wide tile takes the L2 throughput from 47 % to 35 % and
-// the SM clock from 1.47 to 1.53 GHz, but the tensor pipe is busy 86-87 % of the active cycles with either tile and
-// the wide tile's exposed epilogue takes the elapsed figure from 83 % to 79 %: a draw.
+// Same for the staggered two-stream kernel.
+int staggered_clusters(int dev, int* out) {
+  static std::atomic<int> cache[64];
+  if (dev < 64) {
+    const int c = cache[dev].load(std::memory_order_acquire);
+    if (c > 0) {
+      *out = c;
+      return SWIGLU_B200_OK;
+    }
+  }
+  if (cudaFuncSetAttribute(stag::swiglu_gemm_fwd_staggered_kernel<ACT_SILU>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, stag::SMEM_BYTES) != cudaSuccess ||
+      cudaFuncSetAttribute(stag::swiglu_gemm_fwd_staggered_kernel<ACT_GELU_TANH>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, stag::SMEM_BYTES) != cudaSuccess ||
+      cudaFuncSetAttribute(stag::swiglu_gemm_fwd_staggered_kernel<ACT_GELU_ERF>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, stag::SMEM_BYTES) != cudaSuccess)
+    return SWIGLU_B200_ERR_DEVICE;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * 148, 1, 1);
+  cfg.blockDim = dim3(stag::S_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = stag::SMEM_BYTES;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, stag::swiglu_gemm_fwd_staggered_kernel<ACT_SILU>, &cfg) != cudaSuccess ||
+      n < 1)
+    return SWIGLU_B200_ERR_DEVICE;
+  if (dev < 64) cache[dev].store(n, std::memory_order_release);
+  *out = n;
+  return SWIGLU_B200_OK;
+}
+
+// Which pair kernel runs.  Default: the staggered two-stream 256 x 256 tile where the problem has at least one tile
+// per resident cluster, else the 256 x 128 tile (twice the tiles for small problems).  SWIGLU_B200_GEMM_TILE =
+// narrow | wide | staggered forces one.  Measured on X [16384, 4096] x W [14336, 4096]^T x 2, the kernels taking
+// turns in one loop so that all see the same power cap: staggered 2.83-2.87 ms, 256 x 128 2.92-2.99, 256 x 256 with
+// one accumulator 3.02, cuBLAS on the stacked weights (no activation) 2.87.  Under ncu on a 4096-row case the
+// 256 x 256 tile takes the L2 throughput from 47 % to 35 % and the SM clock from 1.47 to 1.53 GHz against the
+// 256 x 128 tile, with the tensor pipe busy 86-87 % of the active cycles either way, but its exposed epilogue
+// takes the elapsed figure from 83 % to 79 %; the staggered kernel keeps the saving and hides the epilogue.
 int forced_tile() {  // read at every call, so that a test can switch it
   const char* v = getenv("SWIGLU_B200_GEMM_TILE");
-  return !v ? 0 : v[0] == 'n' ? 1 : v[0] == 'w' ? 2 : 0;
+  return !v ? 0 : v[0] == 'n' ? 1 : v[0] == 'w' ? 2 : v[0] == 's' ? 3 : 0;
 }
 
 // Shared by swiglu_b200_gemm_fwd (r = 0) and swiglu_b200_lora_gemm_fwd (adapters of rank r, pair kernels only).
@@ -807,6 +1102,25 @@ int gemm_fwd_impl(void* h, void* gate_out, void* up_out, const void* x, const vo
       if (rcw != SWIGLU_B200_OK) return rcw;
       const long long wide_tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + wide::BNW - 1) / wide::BNW);
       const int forced = forced_tile();
+      int resident = 0;
+      const int rcs = staggered_clusters(dev, &resident);
+      if (rcs != SWIGLU_B200_OK) return rcs;
+      if (forced == 3 || (forced == 0 && wide_tiles >= resident)) {
+        const long long use = wide_tiles < resident ? wide_tiles : resident;
+        const unsigned grid = (unsigned)(2 * use);
+        if (act == ACT_GELU_TANH)
+          stag::swiglu_gemm_fwd_staggered_kernel<ACT_GELU_TANH><<<grid, stag::S_THREADS, stag::SMEM_BYTES, st>>>(
+              map_x, map_wg, map_wu, map_xa, map_bg, map_bu, pp);
+        else if (act == ACT_GELU_ERF)
+          stag::swiglu_gemm_fwd_staggered_kernel<ACT_GELU_ERF><<<grid, stag::S_THREADS, stag::SMEM_BYTES, st>>>(
+              map_x, map_wg, map_wu, map_xa, map_bg, map_bu, pp);
+        else
+          stag::swiglu_gemm_fwd_staggered_kernel<ACT_SILU><<<grid, stag::S_THREADS, stag::SMEM_BYTES, st>>>(
+              map_x, map_wg, map_wu, map_xa, map_bg, map_bu, pp);
+        if (cudaGetLastError() != cudaSuccess) return SWIGLU_B200_ERR_LAUNCH;
+        g_gemm_launches.fetch_add(1, std::memory_order_relaxed);
+        return SWIGLU_B200_OK;
+      }
       if (forced == 2) {
         const long long use = wide_tiles < wide_resident ? wide_tiles : wide_resident;
         const unsigned grid = (unsigned)(2 * use);

@@ -76,15 +76,17 @@ def test_forward_matches_fp32_reference(m, n, k, gm, dm):
 @pytest.mark.parametrize("m,n,k", [(256, 256, 64), (1, 16, 8), (300, 272, 200), (257, 528, 72), (1000, 2064, 1032),
                                    (2048, 1408, 4096), (4500, 384, 256)])
 @pytest.mark.parametrize("gm,dm", [(1.0, 1.0), (0.7, 1.3)])
-def test_wide_tile_kernel_agrees_with_the_narrow_one(m, n, k, gm, dm, monkeypatch):
-    """The 256 x 256 pair tile (two MMAs per step sharing the X operand, one 512-column accumulator, sixteen
-    epilogue warps) is an option (SWIGLU_B200_GEMM_TILE=wide); forced here on small and ragged shapes.
-    Each output element is accumulated over K in the same order by both kernels, so the bits must agree; the
-    fp32 reference bounds both."""
+@pytest.mark.parametrize("tile", ["wide", "staggered"])
+def test_wide_tile_kernels_agree_with_the_narrow_one(m, n, k, gm, dm, tile, monkeypatch):
+    """The two 256 x 256 pair-tile kernels, forced on small and ragged shapes (SWIGLU_B200_GEMM_TILE): `wide`
+    (two MMAs per step sharing the X operand, one 512-column accumulator, sixteen epilogue warps) and `staggered`
+    (two 256 x 128 streams a few K blocks apart, each issued by its own thread, sharing a ring of X tiles; the
+    default where a problem has a tile per resident cluster).  Each output element is accumulated over K in the
+    same order by all three kernels, so the bits must agree; the fp32 reference bounds them."""
     x, wg, wu = make(m, n, k, seed=11)
     monkeypatch.setenv("SWIGLU_B200_GEMM_TILE", "narrow")
     want = F.gate_up_swiglu_forward(x, wg, wu, gm, dm, save_preactivations=True)
-    monkeypatch.setenv("SWIGLU_B200_GEMM_TILE", "wide")
+    monkeypatch.setenv("SWIGLU_B200_GEMM_TILE", tile)
     before = _lib.lib.swiglu_b200_gemm_launch_count()
     got = F.gate_up_swiglu_forward(x, wg, wu, gm, dm, save_preactivations=True)
     F.check_status(x.device)
@@ -101,16 +103,17 @@ def test_wide_tile_kernel_agrees_with_the_narrow_one(m, n, k, gm, dm, monkeypatc
 
 @pytest.mark.parametrize("r", [8, 16, 40, 64])
 @pytest.mark.parametrize("activation", ["silu", "gelu_tanh", "gelu_exact"])
-def test_wide_tile_kernel_with_adapters_and_gelu(r, activation, monkeypatch):
+@pytest.mark.parametrize("wide", ["wide", "staggered"])
+def test_wide_tile_kernels_with_adapters_and_gelu(r, activation, wide, monkeypatch):
     m, n, k = 520, 784, 328
     g = torch.Generator(device=DEVICE).manual_seed(r)
     mk = lambda *s, std=1.0: (std * torch.randn(*s, generator=g, device=DEVICE)).bfloat16()
     x, wg, wu = mk(m, k), mk(n, k, std=k ** -0.5), mk(n, k, std=k ** -0.5)
     ag, au, bg, bu = mk(r, k, std=k ** -0.5), mk(r, k, std=k ** -0.5), mk(n, r, std=0.3), mk(n, r, std=0.3)
     outs = {}
-    for tile in ("narrow", "wide"):
+    for tile in ("narrow", wide):
         monkeypatch.setenv("SWIGLU_B200_GEMM_TILE", tile)
-        outs[tile] = F.lora_gate_up_swiglu_forward(x, wg, wu, ag, bg, 2.0, au, bu, 0.5, save_eg=True,
+        outs["wide" if tile == wide else tile] = F.lora_gate_up_swiglu_forward(x, wg, wu, ag, bg, 2.0, au, bu, 0.5, save_eg=True,
                                                    activation=activation)
         F.check_status(x.device)
     for a, b, what in zip(outs["wide"], outs["narrow"], ("h", "e", "g")):
@@ -281,7 +284,8 @@ def test_full_size_projection_workload():
 def test_tensor_core_kernels_on_random_shapes():
     """Forward projection (plain, with adapters, with a GELU gate) and both backward GEMMs on 48 seeded random
     shapes: ragged row counts, widths that end inside a tile, contractions that end inside a K block, every rank
-    layout of the adapter steps, both backward tile widths."""
+    layout of the adapter steps, both backward tile widths, and the forward by its default choice of kernel, by
+    the staggered two-stream kernel and by the 256 x 128 one in turn."""
     import os
     import random
 
@@ -291,8 +295,14 @@ def test_tensor_core_kernels_on_random_shapes():
     g = torch.Generator(device=DEVICE).manual_seed(77)
     mk = lambda *s, std=1.0: (std * torch.randn(*s, generator=g, device=DEVICE)).bfloat16()
     saved = os.environ.get("SWIGLU_B200_GEMM_BWD_TILE")
+    saved_fwd = os.environ.get("SWIGLU_B200_GEMM_TILE")
     try:
         for case in range(48):
+            forward_tile = (None, "staggered", "narrow")[case % 3]
+            if forward_tile is None:
+                os.environ.pop("SWIGLU_B200_GEMM_TILE", None)
+            else:
+                os.environ["SWIGLU_B200_GEMM_TILE"] = forward_tile
             m = rng.choice([1, 7, 127, 128, 129, 255, 257, 300, 511, 777, 1024, 1500])
             n = 16 * rng.randint(1, 75)
             k = 16 * rng.randint(1, 50)
@@ -326,10 +336,11 @@ def test_tensor_core_kernels_on_random_shapes():
             assert_close_bf16(dwg, dgate.float().t() @ xf, what + " dw_gate")
             assert_close_bf16(dwu, dup.float().t() @ xf, what + " dw_up")
     finally:
-        if saved is None:
-            os.environ.pop("SWIGLU_B200_GEMM_BWD_TILE", None)
-        else:
-            os.environ["SWIGLU_B200_GEMM_BWD_TILE"] = saved
+        for name, value in (("SWIGLU_B200_GEMM_BWD_TILE", saved), ("SWIGLU_B200_GEMM_TILE", saved_fwd)):
+            if value is None:
+                os.environ.pop(name, None)
+            else:
+                os.environ[name] = value
 
 
 def test_status_ring_reports_a_failed_launch():
