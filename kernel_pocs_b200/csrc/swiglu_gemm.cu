@@ -68,6 +68,23 @@ struct GemmParams {
   int r;  // rank of the LoRA adapters added to both projections (pair kernel only), 0 for none
 };
 
+// Sixteen bf16 results of one row: one 32-byte store (a whole sector) where the outputs allow it, else two of 16.
+__device__ __forceinline__ void store_16_results(__nv_bfloat16* dst, const uint32_t (&v)[8], bool aligned32) {
+  if (aligned32) {
+    asm volatile("st.global.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+                 "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+  } else {
+    uint4* d = reinterpret_cast<uint4*>(dst);
+    d[0] = make_uint4(v[0], v[1], v[2], v[3]);
+    d[1] = make_uint4(v[4], v[5], v[6], v[7]);
+  }
+}
+// n is a multiple of 16, so a group of 16 results starts on a 32-byte boundary whenever the base does
+__device__ __forceinline__ bool outputs_aligned32(const void* h, const void* gate_out, const void* up_out) {
+  return ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(gate_out) |
+           reinterpret_cast<uintptr_t>(up_out)) & 31) == 0;
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 swiglu_gemm_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wg,
                        const __grid_constant__ CUtensorMap map_wu, const GemmParams p) {
@@ -146,6 +163,7 @@ swiglu_gemm_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     const int quarter = warp & 3;
     const int row = m0 + quarter * 32 + lane;
     const Consts cst(p.gm, p.dm);
+    const bool aligned32 = outputs_aligned32(p.h, p.gate_out, p.up_out);
     const bool ok = mbar_wait(acc_ready, 0, p.status, 300);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
@@ -171,16 +189,10 @@ swiglu_gemm_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
           }
           const long long off = (long long)row * p.n + n0 + c;
           // n is a multiple of 16 (checked on the host), so a 16-column group is all in or all out
-          uint4* dst = reinterpret_cast<uint4*>(p.h + off);
-          dst[0] = make_uint4(hv[0], hv[1], hv[2], hv[3]);
-          dst[1] = make_uint4(hv[4], hv[5], hv[6], hv[7]);
+          store_16_results(p.h + off, hv, aligned32);
           if (p.gate_out) {
-            uint4* dg = reinterpret_cast<uint4*>(p.gate_out + off);
-            dg[0] = make_uint4(gv[0], gv[1], gv[2], gv[3]);
-            dg[1] = make_uint4(gv[4], gv[5], gv[6], gv[7]);
-            uint4* du = reinterpret_cast<uint4*>(p.up_out + off);
-            du[0] = make_uint4(uv[0], uv[1], uv[2], uv[3]);
-            du[1] = make_uint4(uv[4], uv[5], uv[6], uv[7]);
+            store_16_results(p.gate_out + off, gv, aligned32);
+            store_16_results(p.up_out + off, uv, aligned32);
           }
         }
       }
@@ -352,6 +364,7 @@ swiglu_gemm_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __g
   } else {
     const int quarter = warp & 3;
     const Consts cst(p.gm, p.dm);
+    const bool aligned32 = outputs_aligned32(p.h, p.gate_out, p.up_out);
     long long i = 0;
     bool ok = true;
     for (long long t = pair_id; t < walk.total && ok; t += n_pairs, ++i) {
@@ -391,16 +404,10 @@ swiglu_gemm_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __g
               uv[j] = *reinterpret_cast<uint32_t*>(&ub);
             }
             const long long off = (long long)row * p.n + n0 + c + 16 * q;
-            uint4* dst = reinterpret_cast<uint4*>(p.h + off);
-            dst[0] = make_uint4(hv[0], hv[1], hv[2], hv[3]);
-            dst[1] = make_uint4(hv[4], hv[5], hv[6], hv[7]);
+            store_16_results(p.h + off, hv, aligned32);
             if (p.gate_out) {
-              uint4* dg = reinterpret_cast<uint4*>(p.gate_out + off);
-              dg[0] = make_uint4(gv[0], gv[1], gv[2], gv[3]);
-              dg[1] = make_uint4(gv[4], gv[5], gv[6], gv[7]);
-              uint4* du = reinterpret_cast<uint4*>(p.up_out + off);
-              du[0] = make_uint4(uv[0], uv[1], uv[2], uv[3]);
-              du[1] = make_uint4(uv[4], uv[5], uv[6], uv[7]);
+              store_16_results(p.gate_out + off, gv, aligned32);
+              store_16_results(p.up_out + off, uv, aligned32);
             }
           }
         }
@@ -577,6 +584,7 @@ swiglu_gemm_fwd_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __g
     const int quarter = warp & 3;           // the TMEM lanes a warp may read: 32 * (warp % 4) ..
     const int part = (warp - 2) >> 2;       // which 64 columns of the tile
     const Consts cst(p.gm, p.dm);
+    const bool aligned32 = outputs_aligned32(p.h, p.gate_out, p.up_out);
     long long i = 0;
     bool ok = true;
     for (long long t = pair_id; t < walk.total && ok; t += n_pairs, ++i) {
@@ -608,16 +616,10 @@ swiglu_gemm_fwd_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __g
             uv[j] = *reinterpret_cast<uint32_t*>(&ub);
           }
           const long long off = (long long)row * p.n + n0 + c;
-          uint4* dst = reinterpret_cast<uint4*>(p.h + off);
-          dst[0] = make_uint4(hv[0], hv[1], hv[2], hv[3]);
-          dst[1] = make_uint4(hv[4], hv[5], hv[6], hv[7]);
+          store_16_results(p.h + off, hv, aligned32);
           if (p.gate_out) {
-            uint4* dg = reinterpret_cast<uint4*>(p.gate_out + off);
-            dg[0] = make_uint4(gv[0], gv[1], gv[2], gv[3]);
-            dg[1] = make_uint4(gv[4], gv[5], gv[6], gv[7]);
-            uint4* du = reinterpret_cast<uint4*>(p.up_out + off);
-            du[0] = make_uint4(uv[0], uv[1], uv[2], uv[3]);
-            du[1] = make_uint4(uv[4], uv[5], uv[6], uv[7]);
+            store_16_results(p.gate_out + off, gv, aligned32);
+            store_16_results(p.up_out + off, uv, aligned32);
           }
         }
       }
@@ -828,6 +830,7 @@ swiglu_gemm_fwd_staggered_kernel(const __grid_constant__ CUtensorMap map_x, cons
     const int quarter = warp & 3;                    // the TMEM lanes a warp may read: 32 * (warp % 4) ..
     const int part = (warp - FIRST_EPI_WARP) >> 2;   // which 32 columns of a half tile
     const Consts cst(p.gm, p.dm);
+    const bool aligned32 = outputs_aligned32(p.h, p.gate_out, p.up_out);
     bool ok = true;
     long long t = pair_id;
     for (long long i = 0; i < my_tiles && ok; ++i, t += n_pairs) {
@@ -866,16 +869,10 @@ swiglu_gemm_fwd_staggered_kernel(const __grid_constant__ CUtensorMap map_x, cons
               uv[j] = *reinterpret_cast<uint32_t*>(&ub);
             }
             const long long off = (long long)row * p.n + col0 + 16 * q;
-            uint4* dst = reinterpret_cast<uint4*>(p.h + off);
-            dst[0] = make_uint4(hv[0], hv[1], hv[2], hv[3]);
-            dst[1] = make_uint4(hv[4], hv[5], hv[6], hv[7]);
+            store_16_results(p.h + off, hv, aligned32);
             if (p.gate_out) {
-              uint4* dg = reinterpret_cast<uint4*>(p.gate_out + off);
-              dg[0] = make_uint4(gv[0], gv[1], gv[2], gv[3]);
-              dg[1] = make_uint4(gv[4], gv[5], gv[6], gv[7]);
-              uint4* du = reinterpret_cast<uint4*>(p.up_out + off);
-              du[0] = make_uint4(uv[0], uv[1], uv[2], uv[3]);
-              du[1] = make_uint4(uv[4], uv[5], uv[6], uv[7]);
+              store_16_results(p.gate_out + off, gv, aligned32);
+              store_16_results(p.up_out + off, uv, aligned32);
             }
           }
         }
@@ -1024,8 +1021,10 @@ int staggered_clusters(int dev, int* out) {
 }
 
 // Which pair kernel runs.  Default: the staggered two-stream 256 x 256 tile where the problem has at least one tile
-// per resident cluster, else the 256 x 128 tile (twice the tiles for small problems).  SWIGLU_B200_GEMM_TILE =
-// narrow | wide | staggered forces one.  Measured on X [16384, 4096] x W [14336, 4096]^T x 2, the kernels taking
+// per resident cluster and the pre-activations are not written out, else the 256 x 128 tile (twice the tiles for
+// small problems; and with three outputs per element a half tile's epilogue outlasts the few K blocks between the
+// two streams, which then wait for it: 3.20 against 2.96 ms).  SWIGLU_B200_GEMM_TILE = narrow | wide | staggered
+// forces one.  Measured on X [16384, 4096] x W [14336, 4096]^T x 2, the kernels taking
 // turns in one loop so that all see the same power cap: staggered 2.83-2.87 ms, 256 x 128 2.92-2.99, 256 x 256 with
 // one accumulator 3.02, cuBLAS on the stacked weights (no activation) 2.87.  Under ncu on a 4096-row case the
 // 256 x 256 tile takes the L2 throughput from 47 % to 35 % and the SM clock from 1.47 to 1.53 GHz against the
@@ -1105,7 +1104,7 @@ int gemm_fwd_impl(void* h, void* gate_out, void* up_out, const void* x, const vo
       int resident = 0;
       const int rcs = staggered_clusters(dev, &resident);
       if (rcs != SWIGLU_B200_OK) return rcs;
-      if (forced == 3 || (forced == 0 && wide_tiles >= resident)) {
+      if (forced == 3 || (forced == 0 && wide_tiles >= resident && !gate_out)) {
         const long long use = wide_tiles < resident ? wide_tiles : resident;
         const unsigned grid = (unsigned)(2 * use);
         if (act == ACT_GELU_TANH)
