@@ -21,7 +21,7 @@ Providers
     b200-packed  this library, packed gate|up layout
     b200-perseq  this library, one call per sequence of the variable-length batch (c3 configurations only)
     torch-eager  the PyTorch composite (torch_swiglu_reference + autograd) on the same GPU
-    ref-triton-fast, ref-triton-safe, ref-triton-packed
+    ref-triton-fast, ref-triton-safe, ref-triton-packed, ref-triton-geglu-tanh, ref-triton-geglu-erf
                  the reference's own Triton kernels (its swiglu_forward / swiglu_backward and the packed
                  twins, in-place and preserve_inputs), from the unmodified copy that
                  benchmarks/fetch_reference.py places under baseline/_ref; reported as unavailable when
@@ -124,13 +124,13 @@ def clone_like(t: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def reference_ops():
+def reference_ops(op="swiglu"):
     """The reference's launch wrappers (Triton kernels underneath) from the copy under baseline/_ref."""
     try:
         import fetch_reference
     except ImportError:
         from benchmarks import fetch_reference
-    return fetch_reference.load()
+    return fetch_reference.load(op)
 
 
 def unavailable_row(name, provider, exc):
@@ -152,7 +152,7 @@ def run_case(name, args, device, rank, world):
         ops = own_ops
         if provider.startswith("ref-triton-"):
             try:
-                ops = reference_ops()
+                ops = reference_ops("geglu" if provider.startswith("ref-triton-geglu-") else "swiglu")
             except Exception as exc:  # copy absent, or triton not importable
                 out_rows.append(unavailable_row(name, provider, exc))
                 continue
@@ -168,7 +168,8 @@ def run_case(name, args, device, rank, world):
             # before the timed kernels start
             if packed:
                 gate_up.copy_(gate_up0)
-            elif provider in ("b200", "b200-perseq", "ref-triton-fast", "liger") or provider.startswith("geglu-"):
+            elif (provider in ("b200", "b200-perseq", "ref-triton-fast", "liger") or provider.startswith("geglu-")
+                  or provider.startswith("ref-triton-geglu-")):
                 gate.copy_(gate0)
                 up.copy_(up0)
             else:
@@ -226,10 +227,13 @@ def run_case(name, args, device, rank, world):
                 fwd()
 
             setups = {"forward": liger_restore, "backward": liger_bwd_setup, "full": liger_restore}
-        elif provider.startswith("geglu-"):
-            from kernels.geglu import geglu_backward, geglu_forward
+        elif provider.startswith("geglu-") or provider.startswith("ref-triton-geglu-"):
+            if provider.startswith("ref-triton-"):  # the reference's own Triton GeGLU, in-place backward
+                geglu_backward, geglu_forward = ops.geglu_backward, ops.geglu_forward
+            else:
+                from kernels.geglu import geglu_backward, geglu_forward
 
-            approximate = "tanh" if provider == "geglu-tanh" else "none"
+            approximate = "tanh" if provider.endswith("-tanh") else "none"
 
             def fwd():
                 geglu_forward(gate, up, approximate)
@@ -513,7 +517,8 @@ def main():
     ap.add_argument("--configs", nargs="+", default=["c1", "c2", "c3", "c3-fp32", "c3+w11009", "c3+w11009-off1"])
     ap.add_argument("--providers", nargs="+", default=["b200", "b200-safe", "ref-triton-fast", "torch-eager"],
                     choices=["b200", "b200-safe", "b200-packed", "b200-perseq", "torch-eager", "geglu-tanh", "geglu-erf",
-                             "ref-triton-fast", "ref-triton-safe", "ref-triton-packed", "liger"])
+                             "ref-triton-fast", "ref-triton-safe", "ref-triton-packed", "ref-triton-geglu-tanh",
+                             "ref-triton-geglu-erf", "liger"])
     ap.add_argument("--modes", nargs="+", default=["forward", "backward", "full"],
                     choices=["forward", "backward", "full"])
     ap.add_argument("--warmup", type=int, default=20)
