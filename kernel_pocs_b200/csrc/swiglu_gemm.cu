@@ -1021,10 +1021,11 @@ int staggered_clusters(int dev, int* out) {
 }
 
 // Which pair kernel runs.  Default: the staggered two-stream 256 x 256 tile where the problem has at least one tile
-// per resident cluster and the pre-activations are not written out, else the 256 x 128 tile (twice the tiles for
-// small problems; and with three outputs per element a half tile's epilogue outlasts the few K blocks between the
-// two streams, which then wait for it: 3.20 against 2.96 ms).  SWIGLU_B200_GEMM_TILE = narrow | wide | staggered
-// forces one.  Measured on X [16384, 4096] x W [14336, 4096]^T x 2, the kernels taking
+// per resident cluster, else the 256 x 128 tile (twice the tiles for small problems).  SWIGLU_B200_GEMM_TILE =
+// narrow | wide | staggered forces one.  (When the pre-activations are written too, a half tile's epilogue, now
+// with three outputs per element, outlasts the few K blocks between the two streams and they wait for it: the
+// staggered tile then gains 1 % over the 256 x 128 one instead of 5 %, 2.97 against 3.00 ms; with 16-byte stores
+// it lost, 3.28 against 3.04 ms.)  Measured on X [16384, 4096] x W [14336, 4096]^T x 2, the kernels taking
 // turns in one loop so that all see the same power cap: staggered 2.83-2.87 ms, 256 x 128 2.92-2.99, 256 x 256 with
 // one accumulator 3.02, cuBLAS on the stacked weights (no activation) 2.87.  Under ncu on a 4096-row case the
 // 256 x 256 tile takes the L2 throughput from 47 % to 35 % and the SM clock from 1.47 to 1.53 GHz against the
@@ -1104,7 +1105,7 @@ int gemm_fwd_impl(void* h, void* gate_out, void* up_out, const void* x, const vo
       int resident = 0;
       const int rcs = staggered_clusters(dev, &resident);
       if (rcs != SWIGLU_B200_OK) return rcs;
-      if (forced == 3 || (forced == 0 && wide_tiles >= resident && !gate_out)) {
+      if (forced == 3 || (forced == 0 && wide_tiles >= resident)) {
         const long long use = wide_tiles < resident ? wide_tiles : resident;
         const unsigned grid = (unsigned)(2 * use);
         if (act == ACT_GELU_TANH)
