@@ -471,7 +471,7 @@ int swiglu_b200_lora_swiglu_fwd(void* h, void* e_out, void* g_out, const void* e
   const long long tiles = ((m + TM - 1) / TM) * tiles_n;
   if (tiles > 0x7fffffffLL) return SWIGLU_B200_ERR_SHAPE;  // (tens of terabytes per matrix)
   // A CTA takes its tiles in runs of Tune::run where that leaves every CTA sixteen runs or more; smaller problems
-  // are dealt in shorter runs, so that the last round of runs does not leave most SMs idle.
+  // are dealt in shorter runs, so that the last wave of runs does not leave most SMs idle.
   int run = rk == 16 ? (save ? Cfg<16, true>::RUN : Cfg<16, false>::RUN)
           : rk == 32 ? (save ? Cfg<32, true>::RUN : Cfg<32, false>::RUN)
                      : (save ? Cfg<64, true>::RUN : Cfg<64, false>::RUN);
