@@ -309,7 +309,7 @@ lora_swiglu_kernel(const __grid_constant__ CUtensorMap map_e, const __grid_const
           tma_store_2d(&map_h, n0, m0, stage);
         }
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        if (it >= (uint32_t)LAG) {
+        if (LAG == 0 || it >= (uint32_t)LAG) {
           asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(LAG) : "memory");
           mbar_arrive(&empty[(it - LAG) % STAGES]);
         }
@@ -470,12 +470,16 @@ int swiglu_b200_lora_swiglu_fwd(void* h, void* e_out, void* g_out, const void* e
   const long long tiles_n = (n + TN - 1) / TN;
   const long long tiles = ((m + TM - 1) / TM) * tiles_n;
   if (tiles > 0x7fffffffLL) return SWIGLU_B200_ERR_SHAPE;  // (tens of terabytes per matrix)
-  // A CTA takes its tiles in runs of Tune::run where that leaves every CTA sixteen runs or more; smaller problems
-  // are dealt in shorter runs, so that the last wave of runs does not leave most SMs idle.
+  // A CTA takes its tiles in runs of Tune::run, or of that halved (and halved again ...) where the tiles of the
+  // busiest CTA would otherwise exceed the best such split by more than 4 %: long runs share their XA tiles, but
+  // on a small problem the last wave of long runs leaves most SMs idle.
   int run = rk == 16 ? (save ? Cfg<16, true>::RUN : Cfg<16, false>::RUN)
           : rk == 32 ? (save ? Cfg<32, true>::RUN : Cfg<32, false>::RUN)
                      : (save ? Cfg<64, true>::RUN : Cfg<64, false>::RUN);
-  while (run > 1 && tiles < 16LL * run * n_sm) run /= 2;
+  auto busiest = [&](int c) { return ((tiles + c - 1) / c + n_sm - 1) / n_sm * c; };  // tiles of the busiest CTA
+  long long least = busiest(run);
+  for (int c = run / 2; c >= 1; c /= 2) least = busiest(c) < least ? busiest(c) : least;
+  while (run > 1 && busiest(run) * 100 > least * 104) run /= 2;
   const long long runs = (tiles + run - 1) / run;
   const unsigned grid = (unsigned)(runs < n_sm ? runs : n_sm);
   LoraParams p{static_cast<int*>(status), m, n, (int)r, save ? 1 : 0, run, s_gate, s_up};
