@@ -1021,7 +1021,11 @@ int staggered_clusters(int dev, int* out) {
 }
 
 // Which pair kernel runs.  Default: the staggered two-stream 256 x 256 tile where the problem has at least one tile
-// per resident cluster, else the 256 x 128 tile (twice the tiles for small problems).  SWIGLU_B200_GEMM_TILE =
+// per resident cluster and its rounds of tiles over the resident clusters, at 0.97 of the time of two 256 x 128
+// tiles each (0.95 in long runs under the power cap, level in short bursts), take no longer than the rounds of
+// 256 x 128 tiles; else the 256 x 128 tile (twice the tiles: a finer last round, which decides for problems of a
+// few rounds: at N 14336, K 4096 the rule picks the staggered tile for 512, 1536 and from 6144 rows on, which is
+// where it measured faster, by 2 to 7 %, and the 256 x 128 tile for 1024, 2048, 3072 and 4096 rows).  SWIGLU_B200_GEMM_TILE =
 // narrow | wide | staggered forces one.  (When the pre-activations are written too, a half tile's epilogue, now
 // with three outputs per element, outlasts the few K blocks between the two streams and they wait for it: the
 // staggered tile then gains 1 % over the 256 x 128 one instead of 5 %, 2.97 against 3.00 ms; with 16-byte stores
@@ -1105,7 +1109,14 @@ int gemm_fwd_impl(void* h, void* gate_out, void* up_out, const void* x, const vo
       int resident = 0;
       const int rcs = staggered_clusters(dev, &resident);
       if (rcs != SWIGLU_B200_OK) return rcs;
-      if (forced == 3 || (forced == 0 && wide_tiles >= resident)) {
+      // rounds of tiles over the resident clusters: a 256 x 256 tile takes 0.97 of two 256 x 128 ones
+      int narrow_resident = 0;
+      const int rcn = pair_clusters(dev, &narrow_resident);
+      if (rcn != SWIGLU_B200_OK) return rcn;
+      const long long narrow_tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + BN - 1) / BN);
+      const long long rounds_s = (wide_tiles + resident - 1) / resident;
+      const long long rounds_n = (narrow_tiles + narrow_resident - 1) / narrow_resident;
+      if (forced == 3 || (forced == 0 && wide_tiles >= resident && 194 * rounds_s <= 100 * rounds_n)) {
         const long long use = wide_tiles < resident ? wide_tiles : resident;
         const unsigned grid = (unsigned)(2 * use);
         if (act == ACT_GELU_TANH)
