@@ -18,6 +18,7 @@ needs less.
 Providers
     b200         this library, in-place backward (the operator's default)
     b200-safe    this library, preserve_inputs=True
+    b200-graph   the launches of b200-safe captured once in CUDA graphs and replayed (launch-bound small shapes)
     b200-packed  this library, packed gate|up layout
     b200-perseq  this library, one call per sequence of the variable-length batch (c3 configurations only)
     torch-eager  the PyTorch composite (torch_swiglu_reference + autograd) on the same GPU
@@ -276,6 +277,31 @@ def run_case(name, args, device, rank, world):
                 bwd()
 
             setups = {m: restore for m in ("forward", "backward", "full")}
+        elif provider == "b200-graph":
+            # the same launches (preserve_inputs, so that a replay needs no restore) captured once in CUDA graphs
+            # and replayed: what a launch-bound loop over small shapes gains
+            def capture(step):
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    for _ in range(3):
+                        step()
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    step()
+                return graph
+
+            def both():
+                own_ops.swiglu_forward(gate, up)
+                own_ops.swiglu_backward(dh, gate, up, preserve_inputs=True)
+
+            graphs = {"forward": capture(lambda: own_ops.swiglu_forward(gate, up)),
+                      "backward": capture(lambda: own_ops.swiglu_backward(dh, gate, up, preserve_inputs=True)),
+                      "full": capture(both)}
+            fwd, bwd, full = graphs["forward"].replay, graphs["backward"].replay, graphs["full"].replay
+            setups = {m: (lambda: None) for m in ("forward", "backward", "full")}
         elif provider == "b200-perseq":
             # one call per sequence of the variable-length batch (row slices of the packed token axis): what a
             # caller that walks cu_seqlens does; the op is row-independent, so the results are those of one call
@@ -543,7 +569,7 @@ def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--configs", nargs="+", default=["c1", "c2", "c3", "c3-fp32", "c3+w11009", "c3+w11009-off1"])
     ap.add_argument("--providers", nargs="+", default=["b200", "b200-safe", "ref-triton-fast", "torch-eager"],
-                    choices=["b200", "b200-safe", "b200-packed", "b200-perseq", "torch-eager", "geglu-tanh", "geglu-erf",
+                    choices=["b200", "b200-safe", "b200-graph", "b200-packed", "b200-perseq", "torch-eager", "geglu-tanh", "geglu-erf",
                              "ref-triton-fast", "ref-triton-safe", "ref-triton-packed", "ref-triton-geglu-tanh",
                              "ref-triton-geglu-erf", "liger"])
     ap.add_argument("--modes", nargs="+", default=["forward", "backward", "full"],
