@@ -36,16 +36,17 @@ def test_bench_line_has_every_contract_key():
 def test_bench_all_runs_every_kind_of_provider():
     proc = subprocess.run(
         [sys.executable, str(ROOT / "benchmarks" / "bench_all.py"), "--configs", "c1", "--providers", "b200", "b200-safe",
-         "b200-packed", "ref-triton-fast", "ref-triton-packed", "torch-eager", "geglu-tanh", "liger", "--rep", "3",
+         "b200-packed", "b200-graph", "ref-triton-fast", "ref-triton-packed", "ref-triton-geglu-erf", "torch-eager",
+         "geglu-tanh", "liger", "--rep", "3",
          "--warmup", "1", "--save", "/tmp/swiglu_bench_all_test.json"],
         capture_output=True, text=True, timeout=900, cwd=ROOT)
     assert proc.returncode == 0, proc.stderr[-2000:]
     rows = json.loads(Path("/tmp/swiglu_bench_all_test.json").read_text())["rows"]
     own = [r for r in rows if r["provider"].startswith("b200") and "unavailable" not in r]
-    assert {r["mode"] for r in own} == {"forward", "backward", "full"} and len(own) == 9
+    assert {r["mode"] for r in own} == {"forward", "backward", "full"} and len(own) == 12
     for r in own:
         assert r["gbs_per_gpu"] > 0 and r["peak_mib"] > 0 and "call_allocates_mib" in r
     # comparators either ran or say why not; they never take the script down
-    for provider in ("ref-triton-fast", "ref-triton-packed", "liger"):
+    for provider in ("ref-triton-fast", "ref-triton-packed", "ref-triton-geglu-erf", "liger"):
         mine = [r for r in rows if r["provider"] == provider]
         assert mine and (all("unavailable" in r for r in mine) or len(mine) == 3)
