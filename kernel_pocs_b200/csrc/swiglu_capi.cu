@@ -188,6 +188,7 @@ Plan make_plan(const unsigned long long* out, int n_out, const unsigned long lon
       p.bytes = b;
       p.shape.vecs_per_row = cols * es / b;
       p.shape.n_vec = rows * p.shape.vecs_per_row;
+      swiglu_b200::set_row_divisor(p.shape);
     } else {
       p.ragged = true;
       p.bytes = kWide;

@@ -546,6 +546,9 @@ template <> struct Math<true, ACT_GELU_ERF> {
 struct Shape {
   long long n_vec;         // vectors in the body
   long long vecs_per_row;  // ROWS only
+  // ROWS only: i / vecs_per_row == __umulhi(i, div_mul) >> div_shift for every i < 2^31 (div_mul == 0: not
+  // available, divide); see set_row_divisor().
+  unsigned div_mul, div_shift;
   long long pitch_in;      // bytes between rows of gate / up                (ROWS only)
   long long pitch_out;     // bytes between rows of h (fwd) or dh (bwd)      (ROWS only)
   long long pitch_grad;    // bytes between rows of dgate / dup              (ROWS, bwd only)
@@ -555,6 +558,20 @@ struct Shape {
   // the outputs' bodies start on one (0..15, a multiple of the element size).
   int skew_gate, skew_up, skew_dout;
 };
+
+// Division of a vector index by vecs_per_row as a multiplication: with p = 31 + ceil(log2 d) and
+// m = ceil(2^p / d) (which fits 32 bits), floor(i / d) = (i * m) >> p for every 0 <= i < 2^31 (Granlund and
+// Montgomery's invariant-divisor scheme).  Left at zero, i.e. "divide", where that range does not cover the launch.
+inline void set_row_divisor(Shape& s) {
+  s.div_mul = s.div_shift = 0;
+  const unsigned long long d = (unsigned long long)s.vecs_per_row;
+  if (d < 2 || d >= (1ull << 31) || s.n_vec >= (1ll << 31)) return;
+  unsigned lg = 0;
+  while ((1ull << lg) < d) ++lg;
+  const unsigned p = 31 + lg;
+  s.div_mul = (unsigned)(((1ull << p) + d - 1) / d);
+  s.div_shift = p - 32;
+}
 
 // ---------------------------------------------------------------------------------------
 // Loads for inputs that are misaligned relative to the outputs (flat layout, 16-byte vectors; used by the
@@ -647,7 +664,11 @@ struct Locator {
       off_in = off_out = off_grad = i * BYTES;
     } else {
       long long row, cv;
-      if (s.n_vec <= 0xffffffffLL) {  // uniform branch; 32-bit division is several times cheaper
+      if (s.div_mul != 0) {  // uniform branch; a multiplication and a shift instead of a division
+        const unsigned r = __umulhi((unsigned)i, s.div_mul) >> s.div_shift;
+        row = r;
+        cv = (long long)((unsigned)i - r * (unsigned)s.vecs_per_row);
+      } else if (s.n_vec <= 0xffffffffLL) {  // 32-bit division is several times cheaper than 64-bit
         unsigned r = (unsigned)i / (unsigned)s.vecs_per_row;
         row = r;
         cv = (long long)((unsigned)i - r * (unsigned)s.vecs_per_row);
