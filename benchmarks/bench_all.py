@@ -482,9 +482,26 @@ def run_lora(args, device):
         e2.copy_(e)
         g2.copy_(gg)
 
+    # the reference's own Triton kernel for this step (experiments/v3, fused_lora_swiglu), when its copy is there
+    try:
+        ref_v3 = reference_ops("lora_v3")
+        ref_v3.fused_lora_swiglu(e[:256], gg[:256], xag[:256], xau[:256], bg, bu, 2.0, 2.0)  # first JIT
+        torch.cuda.synchronize()
+        ref_rows = (
+            ("ref-triton-lora-epilogue", lambda: ref_v3.fused_lora_swiglu(e, gg, xag, xau, bg, bu, 2.0, 2.0),
+             3 * m * n * 2, "forward", lambda: None),
+            ("ref-triton-lora-epilogue+save",
+             lambda: ref_v3.fused_lora_swiglu(e, gg, xag, xau, bg, bu, 2.0, 2.0, save_eg=True),
+             5 * m * n * 2, "forward", lambda: None))
+    except Exception as exc:
+        ref_rows = ()
+        rows.append(unavailable_row("lora", "ref-triton-lora-epilogue", exc))
+        print(f"{'lora':>16} {'ref-triton-lora-epilogue':>24} unavailable: {rows[-1]['unavailable']}", flush=True)
+
     for provider, fn, nbytes, mode, setup in (
             ("b200-lora-epilogue", fused, 3 * m * n * 2, "forward", lambda: None),
             ("b200-lora-epilogue+save", fused_save, 5 * m * n * 2, "forward", lambda: None),
+            *ref_rows,
             ("addmm_x2+b200-swiglu", unfused, 3 * m * n * 2, "forward", lambda: None),
             ("b200-bwd-recompute", recompute, 6 * m * n * 2, "backward", reseed),
             ("b200-fwd+b200-bwd", fwd_then_bwd, 8 * m * n * 2, "backward", reseed)):
@@ -497,7 +514,7 @@ def run_lora(args, device):
         rows.append(r_)
         print(f"{'lora':>16} {provider:>24} {mode:>8} bf16 M{m} N{n} r{r} {mean:9.4f} ms  {r_['gbs_per_gpu']:8.1f} GB/s  "
               f"{100 * r_['frac_of_measured_copy']:6.1f}% of {kind} {peak:.0f}  {r_['tokens_per_s'] / 1e6:8.3f} Mtok/s", flush=True)
-        if provider.startswith("b200-lora-epilogue"):
+        if "lora-epilogue" in provider:
             ms = time_back_to_back(fn)
             check_status(device)
             r_["ms_back_to_back"] = ms

@@ -2,7 +2,8 @@
 (kernels/lora_mlp/experiments/v3/lora_mlp_kernel_v3.py:141-200), evaluated in fp32 PyTorch on the same bf16
 operands:  e = E + s_gate * (XAg @ Bg^T),  g = G + s_up * (XAu @ Bu^T),  h = silu(e) * g.
 The reference's own implementation of this step is a Triton kernel and cannot run without a GPU, so no
-vectors produced by it exist: parity for this operator is against the formula (as in the reference's own test,
+vectors produced by it exist (tests/test_reference_triton.py compares with it directly where its copy and a
+GPU are there): parity for this operator is against the formula (as in the reference's own test,
 kernels/lora_mlp/tests/test_lora_mlp.py, which compares with a PyTorch composite), with the bound used for
 the fused GEMM: one bf16 rounding plus accumulation noise,  |err| <= 2^-7 |ref| + 2^-9 rms(ref)."""
 import pytest

@@ -194,3 +194,43 @@ def test_geglu_large_bf16_block_against_the_triton_kernels(ref_geglu, approximat
         assert int((~ref_ok).sum()) <= got.numel() // 100000, f"{name}: the reference is off in too many elements"
         apart = O.ulp_distance(got, want)
         assert int(apart[ref_ok].max()) <= 3, f"geglu[{approximate}] {name} vs the reference's Triton kernel"
+
+
+# ---- the LoRA + SwiGLU epilogue (reference kernels/lora_mlp/experiments/v3/lora_mlp_kernel_v3.py:141-200) ----
+
+@pytest.fixture(scope="module")
+def ref_lora():
+    if not fetch_reference.available("lora_v3"):
+        pytest.skip("baseline/_ref/kernels/lora_mlp/experiments/v3 is absent (benchmarks/fetch_reference.py creates it)")
+    try:
+        module = fetch_reference.load("lora_v3")
+        e = torch.randn(64, 64, device="cuda").bfloat16()
+        a = torch.randn(64, 16, device="cuda").bfloat16()
+        module.fused_lora_swiglu(e, e.clone(), a, a.clone(), a.clone(), a.clone())
+        torch.cuda.synchronize()
+    except Exception as exc:
+        pytest.skip(f"the reference's Triton LoRA epilogue does not run here: {type(exc).__name__}: {exc}")
+    return module
+
+
+@pytest.mark.parametrize("m,n,r", [(128, 64, 16), (200, 200, 24), (333, 1096, 32), (1000, 4104, 64), (4096, 14336, 16)])
+@pytest.mark.parametrize("save_eg", [False, True])
+def test_lora_epilogue_against_the_triton_kernel(ref_lora, m, n, r, save_eg):
+    """Same bf16 operands through the reference's fused_lora_swiglu and this library's.  Both accumulate the rank-r
+    products in fp32 and round e, g and h once, but sum the ranks in different orders, so they are held to one
+    bf16 rounding of each other plus accumulation noise (the bound the fused-GEMM tests use against fp32)."""
+    from kernel_pocs_b200.fused_mlp import check_status
+    from kernel_pocs_b200.lora_mlp import fused_lora_swiglu
+    from tests.test_fused_gemm import assert_close_bf16
+
+    g = torch.Generator(device="cuda").manual_seed(41)
+    mk = lambda *shape, std=1.0: (std * torch.randn(*shape, generator=g, device="cuda")).bfloat16()
+    e, gg, xag, xau, bg, bu = mk(m, n, std=1.5), mk(m, n), mk(m, r), mk(m, r), mk(n, r, std=0.3), mk(n, r, std=0.3)
+    want = ref_lora.fused_lora_swiglu(e, gg, xag, xau, bg, bu, 2.0, 0.5, save_eg=save_eg)
+    got = fused_lora_swiglu(e, gg, xag, xau, bg, bu, 2.0, 0.5, save_eg=save_eg)
+    check_status(e.device)
+    for name, a, b in zip(("h", "e", "g"), got, want):
+        if b is None:
+            assert a is None
+        else:
+            assert_close_bf16(a, b.float(), f"{name} vs the reference's Triton kernel")
