@@ -415,9 +415,23 @@ def run_c4(args, device):
 
     burst, sustained, kind = tensor_peak()
     rows = []
+    # the reference's own attempt at this fusion: its autotuned Triton dual GEMM (experiments/v2), without adapters
+    ref_providers = ()
+    try:
+        ref_v2 = reference_ops("lora_v2")
+
+        def ref_dual_gemm():
+            ref_v2.fused_gate_up_swiglu(x, wg, None, None, 1.0, wu, None, None, 1.0)
+
+        ref_dual_gemm()  # JIT and autotuning
+        torch.cuda.synchronize()
+        ref_providers = (("ref-triton-dual-gemm", {"forward": ref_dual_gemm}),)
+    except Exception as exc:
+        rows.append(unavailable_row("c4", "ref-triton-dual-gemm", exc))
+        print(f"{'c4':>16} {'ref-triton-dual-gemm':>18} unavailable: {rows[-1]['unavailable']}", flush=True)
     for provider, fns in (("b200-fused-gemm", {"forward": fused_fwd, "full": fused_full}),
                           ("cublas+b200-swiglu", {"forward": unfused_fwd, "full": unfused_full}),
-                          ("cublas-2gemm-only", {"forward": cublas_fwd})):
+                          ("cublas-2gemm-only", {"forward": cublas_fwd}), *ref_providers):
         for mode, fn in fns.items():
             if mode not in args.modes:
                 continue

@@ -3,11 +3,11 @@
     python benchmarks/fetch_reference.py --reference /path/to/kernel-POCs
 
 Copies ``kernels/swiglu/{__init__,swiglu}.py``, ``kernels/geglu/{__init__,geglu}.py`` and
-``kernels/lora_mlp/experiments/v3/lora_mlp_kernel_v3.py`` of a checkout of Forge-researchlab/kernel-POCs,
+``kernels/lora_mlp/experiments/{v2/lora_mlp_kernel_v2,v3/lora_mlp_kernel_v3}.py`` of a checkout of Forge-researchlab/kernel-POCs,
 unmodified, to ``baseline/_ref/kernels/`` under this repository.  That directory is
 git-ignored: the copies are comparators that are timed beside this library (benchmarks/bench_all.py providers
 ``ref-triton-fast``, ``ref-triton-safe``, ``ref-triton-packed``, ``ref-triton-geglu-tanh``, ``ref-triton-geglu-erf``,
-and ``ref-triton-lora-epilogue`` of the ``lora`` section;
+``ref-triton-lora-epilogue`` of the ``lora`` section and ``ref-triton-dual-gemm`` of the ``c4`` section;
 bench.py --impl reference; tests/test_reference_triton.py), never product source, and nothing under
 kernel_pocs_b200/ imports them.  Without the copies those providers report ``unavailable`` and the tests skip.
 
@@ -30,11 +30,13 @@ OPERATORS = {
     "swiglu": ("swiglu", ("__init__.py", "swiglu.py"), "swiglu.py"),
     "geglu": ("geglu", ("__init__.py", "geglu.py"), "geglu.py"),
     "lora_v3": ("lora_mlp/experiments/v3", ("lora_mlp_kernel_v3.py",), "lora_mlp_kernel_v3.py"),
+    "lora_v2": ("lora_mlp/experiments/v2", ("lora_mlp_kernel_v2.py",), "lora_mlp_kernel_v2.py"),
 }
-# lora_mlp_kernel_v3.py imports two names of a vendored third-party baseline at module level, for its full-MLP
-# class; its fused_lora_swiglu, the function compared here, uses neither.  The baseline is not copied: load()
-# puts an empty stand-in module under that import path instead.
-_STAND_INS = {"lora_v3": {"reference": (), "reference.unsloth_baseline": ("swiglu_DWf_DW_dfg_kernel", "matmul_lora")}}
+# The two lora_mlp experiment files import names of a vendored third-party baseline at module level, for their
+# full-MLP classes; fused_lora_swiglu (v3) and fused_gate_up_swiglu (v2), the functions compared here, use none of
+# them.  The baseline is not copied: load() puts an empty stand-in module under that import path instead.
+_BASELINE_NAMES = {"reference": (), "reference.unsloth_baseline": ("swiglu_DWf_DW_dfg_kernel", "matmul_lora")}
+_STAND_INS = {"lora_v3": _BASELINE_NAMES, "lora_v2": _BASELINE_NAMES}
 
 
 def fetch(reference: Path) -> Path:

@@ -234,3 +234,38 @@ def test_lora_epilogue_against_the_triton_kernel(ref_lora, m, n, r, save_eg):
             assert a is None
         else:
             assert_close_bf16(a, b.float(), f"{name} vs the reference's Triton kernel")
+
+
+# ---- the fused gate/up projection (reference kernels/lora_mlp/experiments/v2/lora_mlp_kernel_v2.py:145-209) ----
+
+@pytest.mark.parametrize("with_adapters", [False, True])
+def test_fused_projection_against_the_triton_dual_gemm(with_adapters):
+    """The reference's own attempt at this fusion, an autotuned Triton dual GEMM with the adapters and SwiGLU in its
+    epilogue, on the same bf16 operands: both accumulate in fp32 and round h, e and g once, in different orders
+    of summation, so they are held to the bound the fused-GEMM tests use against the fp32 product."""
+    if not fetch_reference.available("lora_v2"):
+        pytest.skip("baseline/_ref/kernels/lora_mlp/experiments/v2 is absent (benchmarks/fetch_reference.py creates it)")
+    from kernel_pocs_b200 import fused_mlp as F
+    from tests.test_fused_gemm import assert_close_bf16
+
+    m, n, k, r = 640, 1040, 520, 16
+    g = torch.Generator(device="cuda").manual_seed(43)
+    mk = lambda *shape, std=1.0: (std * torch.randn(*shape, generator=g, device="cuda")).bfloat16()
+    x, wg, wu = mk(m, k), mk(n, k, std=k ** -0.5), mk(n, k, std=k ** -0.5)
+    ag, au, bg, bu = mk(r, k, std=k ** -0.5), mk(r, k, std=k ** -0.5), mk(n, r, std=0.3), mk(n, r, std=0.3)
+    try:
+        ref = fetch_reference.load("lora_v2")
+        if with_adapters:
+            want = ref.fused_gate_up_swiglu(x, wg, ag, bg, 2.0, wu, au, bu, 0.5, save_pre_act=True)
+        else:
+            want = ref.fused_gate_up_swiglu(x, wg, None, None, 1.0, wu, None, None, 1.0, save_pre_act=True)
+        torch.cuda.synchronize()
+    except Exception as exc:
+        pytest.skip(f"the reference's Triton dual GEMM does not run here: {type(exc).__name__}: {exc}")
+    if with_adapters:
+        got = F.lora_gate_up_swiglu_forward(x, wg, wu, ag, bg, 2.0, au, bu, 0.5, save_eg=True)
+    else:
+        got = F.gate_up_swiglu_forward(x, wg, wu, save_preactivations=True)
+    F.check_status(x.device)
+    for name, a, b in zip(("h", "e", "g"), got, want):
+        assert_close_bf16(a, b.float(), f"{name} vs the reference's Triton dual GEMM")
