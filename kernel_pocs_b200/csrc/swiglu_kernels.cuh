@@ -368,6 +368,7 @@ struct GeluConst {
   static constexpr float kLog2e = 1.4426950408889634f;
   static constexpr float kInvSqrt2 = 0.7071067811865476f;
   static constexpr float kInvSqrt2Pi = 0.3989422804014327f;
+  static constexpr float kErfcT = 0.28284271247461906f;  // 0.4 / sqrt 2: t = 1 / (1 + 0.4 * |x| / sqrt 2)
 };
 
 template <> struct Math<true, ACT_GELU_TANH> {
@@ -429,6 +430,22 @@ template <> struct Math<false, ACT_GELU_TANH> {
   }
 };
 
+// 0.5 * P(t) of the erfc fit described at Math<true, ACT_GELU_ERF> (the halved coefficients are exact).
+struct GeluErfcPoly {
+  static __device__ __forceinline__ float half_p(float t) {
+    float p = 0.5f * 0.0502124303f;
+    p = fmaf(p, t, 0.5f * -0.182717498f);
+    p = fmaf(p, t, 0.5f * 0.168813753f);
+    p = fmaf(p, t, 0.5f * -0.00540429202f);
+    p = fmaf(p, t, 0.5f * 0.14135102f);
+    p = fmaf(p, t, 0.5f * 0.168557698f);
+    p = fmaf(p, t, 0.5f * 0.207841563f);
+    p = fmaf(p, t, 0.5f * 0.225669582f);
+    p = fmaf(p, t, 0.5f * 0.225675864f);
+    return p;
+  }
+};
+
 // Exact form, fp32 I/O.  0.5 * erfc(|x| / sqrt 2) = 0.5 * t * P(t) * exp(-x^2 / 2) with the fit described at
 // Math<true, ACT_GELU_ERF> below (relative error 2.5e-7 evaluated in fp32), but with the factors an fp32
 // result needs: the exponent of exp(-x^2 / 2) carried in two parts (the rounding of x^2 alone would be a
@@ -437,30 +454,21 @@ template <> struct Math<false, ACT_GELU_TANH> {
 // (forward 4.5 TB/s).
 template <> struct Math<false, ACT_GELU_ERF> {
   static __device__ __forceinline__ void cdf_pdf(float x, float& cdf, float& pdf) {
-    const float y = fabsf(x) * GeluConst::kInvSqrt2;
     float t;
-    asm("rcp.approx.f32 %0, %1;" : "=f"(t) : "f"(fmaf(y, 0.4f, 1.0f)));
+    asm("rcp.approx.f32 %0, %1;" : "=f"(t) : "f"(fmaf(fabsf(x), GeluConst::kErfcT, 1.0f)));
     // exp(-x^2 / 2) = 2^(th + tl): x^2 = hi + lo exactly, th the rounded product of hi and -log2(e) / 2, tl what
-    // that rounding, the constant's own rounding and lo leave over (a few 1e-6 at most; 0 where hi overflowed)
+    // that rounding, the constant's own rounding and lo leave over (a few 1e-6 at most).  Where hi overflowed tl
+    // is NaN and the minimum drops it (2^th is 0 there).
     const float hi = x * x;
     const float th = hi * -0.7213475108146667f;
     float tl = fmaf(hi, -0.7213475108146667f, -th);
     tl = fmaf(hi, -9.629815167500055e-09f, tl);
     tl = fmaf(fmaf(x, x, -hi), -0.7213475108146667f, tl);
-    tl = hi < 3.0e38f ? tl : 0.0f;
+    tl = fminf(tl, 1.0e-3f);
     float ex;
     asm("ex2.approx.f32 %0, %1;" : "=f"(ex) : "f"(th));
     ex = fmaf(ex, 0.6931471805599453f * tl, ex);
-    float p = 0.0502124303f;
-    p = fmaf(p, t, -0.182717498f);
-    p = fmaf(p, t, 0.168813753f);
-    p = fmaf(p, t, -0.00540429202f);
-    p = fmaf(p, t, 0.14135102f);
-    p = fmaf(p, t, 0.168557698f);
-    p = fmaf(p, t, 0.207841563f);
-    p = fmaf(p, t, 0.225669582f);
-    p = fmaf(p, t, 0.225675864f);
-    const float half_erfc = (0.5f * t) * p * ex;  // 0.5 * erfc(|x| / sqrt 2)
+    const float half_erfc = t * GeluErfcPoly::half_p(t) * ex;  // 0.5 * erfc(|x| / sqrt 2)
     cdf = x < 0.0f ? half_erfc : 1.0f - half_erfc;
     pdf = GeluConst::kInvSqrt2Pi * ex;
   }
@@ -492,20 +500,10 @@ template <> struct Math<false, ACT_GELU_ERF> {
 // factor is shared with the Gaussian density of the derivative.
 template <> struct Math<true, ACT_GELU_ERF> {
   static __device__ __forceinline__ void cdf_pdf(float x, float& cdf, float& pdf) {
-    const float y = fabsf(x) * GeluConst::kInvSqrt2;
     float t, ex;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(y, 0.4f, 1.0f)));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(fabsf(x), GeluConst::kErfcT, 1.0f)));
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"((x * x) * (-0.5f * GeluConst::kLog2e)));
-    float p = 0.0502124303f;
-    p = fmaf(p, t, -0.182717498f);
-    p = fmaf(p, t, 0.168813753f);
-    p = fmaf(p, t, -0.00540429202f);
-    p = fmaf(p, t, 0.14135102f);
-    p = fmaf(p, t, 0.168557698f);
-    p = fmaf(p, t, 0.207841563f);
-    p = fmaf(p, t, 0.225669582f);
-    p = fmaf(p, t, 0.225675864f);
-    const float half_erfc = (0.5f * t) * p * ex;  // 0.5 * erfc(|x| / sqrt 2)
+    const float half_erfc = t * GeluErfcPoly::half_p(t) * ex;  // 0.5 * erfc(|x| / sqrt 2)
     cdf = x < 0.0f ? half_erfc : 1.0f - half_erfc;
     pdf = GeluConst::kInvSqrt2Pi * ex;
   }
