@@ -619,6 +619,11 @@ def main():
     time.sleep(0.3 if sampler else 0.0)
 
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    # no collector pause between the two launches of a step: the device would idle inside the step's events
+    import gc
+
+    gc.collect()
+    gc.disable()
     barrier()
     mark0 = sampler.mark() if sampler else 0
     launches0 = _lib.launch_count()
@@ -628,6 +633,7 @@ def main():
         step(evs[k])
     barrier()
     wall = time.perf_counter() - wall0
+    gc.enable()
     launches = _lib.launch_count() - launches0
     mark1 = sampler.mark() if sampler else 0
 
